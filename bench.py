@@ -1,0 +1,407 @@
+#!/usr/bin/env python
+"""Headline benchmark of the W4A16 matmul path on B200.
+
+Workload (N=1): one decode token (M=1) through the W4A16 linears of a 64-layer 27B-class dense
+decoder -- per layer qkv (K=5120,N=7168), o_proj (6144,5120), gate_up (5120,34816) and down
+(17408,5120); int4 sym g128 weights, f16 scales and activations -- i.e. the decode-GEMV shapes
+of the baseline's single-GPU sweep laid out as the 64-layer stack, 11.07 GB of weights per step, so
+every launch streams from HBM (the stack is ~88x the L2).  A step is replayed as one CUDA graph of
+256 GEMV launches, the way the reference replays its decode chain.
+
+  value     whole-job GB/s = algorithmic bytes of the step / device time (inputs resident in HBM)
+  e2e       same metric through the host-buffer step call: H2D of the token's activations from pinned
+            memory + graph replay + D2H of the result + sync, every step (wall clock)
+  roofline  the GEMV kernel against the measured HBM copy bandwidth
+  cpu_baseline  the CPU oracle (restatement of the reference quant lane) timed on this host
+
+With --gpus N>1 (torchrun) the same stack is tensor-parallel: qkv/gate_up column-parallel, o_proj/down
+row-parallel with an f16 all-reduce; total work is fixed ("strong" scaling).
+`--impl reference` times the reference's CPU algorithm for the same workload on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from llm170_b200 import synth  # noqa: E402
+
+LAYER_ORDER = ["qkv", "o_proj", "gate_up", "down"]
+METRIC = "W4A16 decode GEMV HBM GB/s (M=1), 27B-class 64-layer linear stack"
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def layer_shapes(world: int):
+    """(name, K, N, kind) per rank for tensor-parallel degree `world` (world=1: the full layer)."""
+    out = {}
+    for nm, (k, n) in synth.DENSE_27B.items():
+        if nm in ("qkv", "gate_up"):
+            out[nm] = (k, n // world, "col")
+        else:
+            out[nm] = (k // world, n, "row")
+    return out
+
+
+def step_bytes(m: int = 1) -> int:
+    return sum(synth.decode_bytes(n, k, m) for (k, n) in synth.DENSE_27B.values())
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference_arm(args, rank: int):
+    """The reference's CPU algorithm (oracle restatement of crates/core/src/quant/lane.rs) on all host
+    threads; each step is a bounded sample of the workload: `sample_layers` full layers at M=1."""
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    cores = os.cpu_count() or 1
+    sample_layers = 2
+    lins = {}
+    for li in range(sample_layers):
+        for nm, (k, n) in synth.DENSE_27B.items():
+            rows = min(n, 4096)  # generate a row sample of each linear, scaled below
+            lins[(li, nm)] = synth.make_linear(rows, k, 128, seed=4000 + li * 10 + len(nm)) + (rows, k, n)
+    xs = {k: synth.make_acts(1, k, seed=k) for k in (5120, 6144, 17408)}
+
+    def one_step():
+        t0 = time.perf_counter()
+        scaled = 0.0
+        for li in range(sample_layers):
+            for nm in LAYER_ORDER:
+                q, s, rows, k, n = lins[(li, nm)]
+                t1 = time.perf_counter()
+                oracle.linear_lane(q, s, xs[k], 1, rows, k, 128, nthreads=cores)
+                scaled += (time.perf_counter() - t1) * (n / rows)
+        return scaled, time.perf_counter() - t0
+
+    for _ in range(args.warmup):
+        one_step()
+    tot = 0.0
+    for _ in range(args.steps):
+        tot += one_step()[0]
+    per_layer_s = tot / (args.steps * sample_layers)
+    gbs = (step_bytes() / 64) / per_layer_s / 1e9
+    ms_step = per_layer_s * 64 * 1e3
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16 x int4 -> f32", "data": "synthetic",
+        "config": {"workload": "decode M=1, 27B-class dense linear stack, int4 sym g128 (CPU lane algorithm)",
+                   "layers": 64, "l2": "inputs larger than cache"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{sample_layers} layers per step, first 4096 rows of each linear, "
+                                   "time scaled to full rows and to 64 layers"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-shape / M sweep extras")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from llm170_b200.w4a16_dec import W4a16Dec
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the W4A16 path has no CPU fallback "
+                         "(use --impl reference for the CPU baseline)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    peaks, peak_kind = load_peaks()
+
+    dec = W4a16Dec(local_rank)
+    L = args.layers
+    shapes = layer_shapes(world)
+    t_build = time.time()
+    for li in range(L):
+        for nm in LAYER_ORDER:
+            k_full, n_full = synth.DENSE_27B[nm]
+            k, n, kind = shapes[nm]
+            # each rank generates only its own shard (seeded per layer, linear and rank)
+            q, s = synth.make_linear_cuda(n, k, 128, seed=4_000_000 + li * 1000 + LAYER_ORDER.index(nm) * 16 + rank,
+                                          device=device)
+            dec.upload_lin_g_dev(f"l{li}.{nm}", q, s, n, k, 128)
+            del q, s
+    torch.cuda.synchronize()
+    t_build = time.time() - t_build
+
+    # activations: fixed device buffers, one per distinct K (values N(0,1) f16)
+    g = torch.Generator(device=device)
+    g.manual_seed(1)
+    xb = {nm: torch.randn((8, shapes[nm][0]), generator=g, device=device, dtype=torch.float32).to(torch.float16)
+          for nm in LAYER_ORDER}
+    yb = {nm: torch.empty((8, shapes[nm][1]), device=device, dtype=torch.float16) for nm in LAYER_ORDER}
+    x_host = torch.empty((1, shapes["qkv"][0]), dtype=torch.float16).pin_memory()
+    x_host.copy_(xb["qkv"][:1].cpu())
+    y_host = torch.empty((1, shapes["down"][1]), dtype=torch.float16).pin_memory()
+
+    st = torch.cuda.ExternalStream(dec.stream_ptr(), device=device)
+
+    def enqueue_step(m: int):
+        for li in range(L):
+            for nm in LAYER_ORDER:
+                dec.sk_single_dev(f"l{li}.{nm}", xb[nm][:m], out=yb[nm][:m], t=m, out_f16=True)
+                if world > 1 and shapes[nm][2] == "row":
+                    dist.all_reduce(yb[nm][:m])
+
+    graphs = {}
+
+    def make_graph(m: int):
+        with torch.cuda.stream(st):
+            enqueue_step(m)                       # warm scratch before capture
+            st.synchronize()
+            if world > 1:
+                return None
+            c0 = dec.launch_count()
+            dec.capture_begin()
+            enqueue_step(m)
+            gexec = dec.capture_end()
+            return gexec, dec.launch_count() - c0
+
+    def run_steps(m: int, n_steps: int):
+        """Device time (ms) of n_steps steps on the decoder stream."""
+        with torch.cuda.stream(st):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for _ in range(n_steps):
+                if graphs.get(m):
+                    dec.graph_launch(graphs[m][0])
+                else:
+                    enqueue_step(m)
+            e1.record(st)
+            e1.synchronize()
+            return e0.elapsed_time(e1)
+
+    graphs[1] = make_graph(1)
+    launches_per_step = graphs[1][1] if graphs[1] else L * len(LAYER_ORDER)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    run_steps(1, args.warmup)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    ms = run_steps(1, args.steps)
+    barrier()
+    clocks = sampler.stop()
+    if world > 1:
+        tms = torch.tensor([ms], device=device)
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms = float(tms.item())
+    ms_per_step = ms / args.steps
+    bytes_step = step_bytes(1) * L
+    value = bytes_step / (ms_per_step * 1e-3) / 1e9
+
+    # ---- e2e: host buffers, H2D + graph + D2H + sync every step (wall clock, max over ranks) --------
+    e2e = None
+    if graphs[1]:
+        gx = graphs[1][0]
+        xdev, ydev = xb["qkv"][:1], yb["down"][:1]
+        for _ in range(max(3, args.warmup)):
+            dec.graph_step_host(gx, x_host, xdev, ydev, y_host)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            dec.graph_step_host(gx, x_host, xdev, ydev, y_host)
+        e2e_s = (time.perf_counter() - t0) / args.steps
+        e2e = {"value": bytes_step / e2e_s / 1e9, "unit": "GB/s", "ms_per_step": e2e_s * 1e3,
+               "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2}
+    else:
+        # multi-GPU: same step issued eagerly between a pinned H2D and a D2H
+        with torch.cuda.stream(st):
+            def e2e_step():
+                xb["qkv"][:1].copy_(x_host, non_blocking=True)
+                enqueue_step(1)
+                y_host.copy_(yb["down"][:1], non_blocking=True)
+                st.synchronize()
+            for _ in range(3):
+                e2e_step()
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                e2e_step()
+            e2e_s = (time.perf_counter() - t0) / args.steps
+        te = torch.tensor([e2e_s], device=device)
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_s = float(te.item())
+        e2e = {"value": bytes_step / e2e_s / 1e9, "unit": "GB/s", "ms_per_step": e2e_s * 1e3,
+               "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": y_host.numel() * 2 * world}
+
+    # ---- extras (rank 0, N=1): per-shape and M sweep, each rotating over all layers (> L2) ------------
+    extras = {}
+    if world == 1 and not args.no_extras:
+        with torch.cuda.stream(st):
+            for m in (1, 2, 4, 8):
+                per = {}
+                for nm in LAYER_ORDER:
+                    k, n, _ = shapes[nm]
+                    def shape_pass():
+                        for li in range(L):
+                            dec.sk_single_dev(f"l{li}.{nm}", xb[nm][:m], out=yb[nm][:m], t=m, out_f16=True)
+                    shape_pass()
+                    st.synchronize()
+                    dec.capture_begin()
+                    shape_pass()
+                    gsh = dec.capture_end()
+                    for _ in range(3):
+                        dec.graph_launch(gsh)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    reps = 5
+                    e0.record(st)
+                    for _ in range(reps):
+                        dec.graph_launch(gsh)
+                    e1.record(st)
+                    e1.synchronize()
+                    us = e0.elapsed_time(e1) * 1e3 / (reps * L)
+                    dec.graph_destroy(gsh)
+                    b = synth.decode_bytes(n, k, m)
+                    per[nm] = {"us": round(us, 3), "GBps": round(b / us / 1e3, 1),
+                               "frac_measured_hbm": round(b / us / 1e3 / peaks["hbm_gbs"], 4)}
+                extras[f"M{m}"] = per
+
+    # ---- CPU baseline (rank 0, N=1): the oracle on a bounded sample ----------------------------------
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import oracle
+        oracle.build()
+        cores = os.cpu_count() or 1
+        sample_layers = min(L, 8)
+        host = []
+        for li in range(sample_layers):
+            for nm in LAYER_ORDER:
+                k, n, _ = shapes[nm]
+                q, s = dec.unpack_lin(f"l{li}.{nm}")
+                host.append((q.cpu().numpy().view(np.uint32), s.cpu().numpy().view(np.uint16),
+                             xb[nm][:1].cpu().numpy().view(np.uint16), n, k, nm, li))
+        t0 = time.perf_counter()
+        maxerr = 0.0
+        for q, s, x, n, k, nm, li in host:
+            ref = oracle.linear_lane(q, s, x, 1, n, k, 128, nthreads=cores)
+            if li == 0:  # parity spot check of the exact tensors that were timed on the GPU
+                got = dec.sk_single_dev(f"l{li}.{nm}", xb[nm][:1], t=1).cpu().numpy()
+                maxerr = max(maxerr, float(np.abs(got - ref).max()))
+        cpu_s = time.perf_counter() - t0
+        cpu_gbs = step_bytes(1) * sample_layers / cpu_s / 1e9
+        cpu_baseline = {"value": cpu_gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                        "sample": f"{sample_layers} of {L} layers (all four linears, all rows, M=1), "
+                                  f"{cpu_s:.1f} s of CPU work", "max_abs_err_gpu_vs_cpu_layer0": maxerr}
+
+    if rank == 0:
+        ach = value  # GB/s over all GEMV launches of the timed region
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16 x int4 -> f32", "data": "synthetic",
+            "config": {"workload": "decode M=1, 27B-class dense linear stack (qkv 5120x7168, o_proj 6144x5120, "
+                                   "gate_up 5120x34816, down 17408x5120), int4 sym g128, f16 scales",
+                       "layers": L, "parallelism": f"tp{world}" if world > 1 else "single",
+                       "l2": f"inputs larger than L2 ({bytes_step / 1e9:.2f} GB of weights per step)",
+                       "launch": "cuda graph replay" if graphs[1] else "eager + NCCL all-reduce",
+                       "build_s": round(t_build, 1)},
+            "roofline": {"bound": "hbm", "kernel": "gemv_w4a16_kernel<128>", "achieved": ach,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                         "peak_kind": peak_kind, "frac_of_nominal_8TBps": ach / 8000.0,
+                         "traffic": None, "launches_per_step": launches_per_step,
+                         "avg_launch_us": ms_per_step * 1e3 / launches_per_step,
+                         "algorithmic_bytes_per_launch": bytes_step / launches_per_step},
+            "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
+            "cpu_baseline": cpu_baseline, "extras": extras,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    dec.close()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,146 @@
+/*
+ * libw4a16_b200 -- C ABI of the B200-native W4A16 matmul path.
+ *
+ * Drop-in boundary for the linear / MoE call sites of LLM170's crates/backend-gpu: every entry
+ * point below names the reference interface it replaces (file:line inside the reference tree).
+ * Conventions shared by all calls:
+ *   - plain pointers and sizes only; `stream` is a cudaStream_t passed as void* (NULL = the
+ *     decoder's own stream, like `cc.stream` in the reference);
+ *   - return 0 on success, non-zero on error; the message is read with w4a16_last_error().  The
+ *     reference returns Result<_, String> from every call and never panics across the boundary
+ *     (crates/backend-gpu/src/rawcuda/ffi.rs:18-40);
+ *   - a decoder is bound to one device and is not thread-safe (the reference's W4a16Dec is Send
+ *     but not Sync: crates/backend-gpu/src/rawcuda/w4a16_dec/mod.rs:626);
+ *   - weights and scratch are owned by the decoder; activations and outputs by the caller;
+ *   - forward calls launch asynchronously, allocate nothing once warmed, and may be captured in a
+ *     CUDA graph (crates/backend-gpu/src/rawcuda/ctx/graph.rs:4-65).
+ * Weight format at the boundary (compressed-tensors pack-quantized, crates/core/src/w4a16.rs:124-175):
+ *   q: little-endian u32 [n][k/8], element i of a row = nibble at bits 4*(i&7) of word i>>3, value q+8
+ *   s: f16 (or bf16) [n][k/group], group in {128, 32};  dequantised weight = (nibble-8)*scale.
+ */
+#ifndef W4A16_B200_H
+#define W4A16_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define W4A16_API __attribute__((visibility("default")))
+#else
+#define W4A16_API
+#endif
+
+typedef struct w4a16_dec w4a16_dec;
+
+/* Output element type of a forward call. The reference writes f32 (dst of lin_forward). */
+#define W4A16_OUT_F32 0
+#define W4A16_OUT_F16 1
+
+/* ---- lifetime ---------------------------------------------------------------------------- */
+
+/* W4a16Dec::new_dev (crates/backend-gpu/src/rawcuda/w4a16_dec/mod.rs:654) + CudaCtx::new_dev
+ * (crates/backend-gpu/src/rawcuda/ctx/mod.rs:101-178): binds the
+ * device's primary context, creates the decoder stream and the split-K scratch. */
+W4A16_API int w4a16_dec_new(int device, w4a16_dec** out);
+/* CudaCtx::free_all (crates/backend-gpu/src/rawcuda/ctx/mem.rs:19): frees weights, scratch, stream. */
+W4A16_API void w4a16_dec_free(w4a16_dec* dec);
+/* Text of the last error on `dec` (or of the last failed w4a16_dec_new when dec is NULL): the
+ * String of the reference's Err (crates/backend-gpu/src/rawcuda/ffi.rs:18-40). */
+W4A16_API const char* w4a16_last_error(const w4a16_dec* dec);
+/* The decoder's stream (CudaCtx.stream, crates/backend-gpu/src/rawcuda/ctx/mod.rs:60-75), as a
+ * cudaStream_t. */
+W4A16_API void* w4a16_stream(w4a16_dec* dec);
+/* CudaCtx::sync (crates/backend-gpu/src/rawcuda/ctx/mod.rs:407). */
+W4A16_API int w4a16_sync(w4a16_dec* dec);
+/* Kernels launched by forward calls since creation: the launch counter the reference keeps in
+ * HOST_LAUNCH_CALLS (crates/backend-gpu/src/rawcuda/ctx/mod.rs:10-11,311-315). */
+W4A16_API unsigned long long w4a16_launch_count(w4a16_dec* dec);
+/* Kernel-selection knobs, the analogue of the reference's LLM170_* environment flags
+ * (crates/diag/src/flag.rs:3-27). Keys: "gemv_ctas_per_sm", "gemv_ksplit" (0 = automatic). */
+W4A16_API int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value);
+
+/* ---- weights ----------------------------------------------------------------------------- */
+
+/* gptq4::check_shapes (crates/backend-gpu/src/rawcuda/gptq4.rs:31-58): validates lengths (in
+ * elements: q u32 words, s u16, x u16) against n, k, t, group. Needs no device. 0 = accepted. */
+W4A16_API int w4a16_check_shapes(size_t t, size_t qlen, size_t slen, size_t xlen, size_t n, size_t k, size_t group);
+
+/* W4a16Dec::upload_lin_g (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:15-65) followed by
+ * the repack of upload_lin_marlin (:99-179): copies q (n*k/2 bytes) and s (n*(k/group)*2 bytes)
+ * from HOST memory, re-tiles them on the device into the library's single resident layout and
+ * registers the linear under `name`, replacing (and freeing) a previous one of that name. */
+W4A16_API int w4a16_upload_lin_g(w4a16_dec* dec, const char* name, const void* q, size_t q_bytes, const void* s,
+                       size_t s_bytes, int n, int k, int group, int scale_bf16);
+/* Same, with q and s already in DEVICE memory in the boundary format (used when weights are
+ * produced on the device; the reference has no such variant). */
+W4A16_API int w4a16_upload_lin_g_dev(w4a16_dec* dec, const char* name, const void* q_dev, const void* s_dev, int n,
+                           int k, int group, int scale_bf16);
+/* W4a16Dec::lin_spec (crates/backend-gpu/src/rawcuda/w4a16_dec/mod.rs:1193): n and k, plus the
+ * group size; non-zero if `name` is unknown. */
+W4A16_API int w4a16_lin_spec(w4a16_dec* dec, const char* name, int* n, int* k, int* group);
+/* Frees one linear (what replacing a name does in
+ * crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:52-55). */
+W4A16_API int w4a16_drop_lin(w4a16_dec* dec, const char* name);
+/* Bytes of device memory held by weights (weights_bytes,
+ * crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:51). */
+W4A16_API size_t w4a16_weights_bytes(w4a16_dec* dec);
+
+/* Inverse of the re-tiling: writes the boundary-format q (u32 [n][k/8]) and s (f16 [n][k/group])
+ * back into DEVICE buffers. Role of the `unrepack` helper in crates/core/src/marlin.rs:75-105. */
+W4A16_API int w4a16_unpack_lin(w4a16_dec* dec, const char* name, void* q_dev, void* s_dev, void* stream);
+/* Element-wise dequantisation of a resident linear into a DEVICE buffer [n][k]:
+ * out_kind W4A16_OUT_F32 -> (nibble-8)*scale exactly as crates/core/src/matmul/cpu.rs:167-194;
+ * W4A16_OUT_F16 -> that value rounded once to f16, the operand the tensor-core GEMM multiplies. */
+W4A16_API int w4a16_dequant_lin(w4a16_dec* dec, const char* name, void* out_dev, int out_kind, void* stream);
+
+/* ---- linear forward ---------------------------------------------------------------------- */
+
+/* W4a16Dec::lin_forward (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/mod.rs:121-144):
+ * dst[t][n] = x16[t][k] * W^T. x16 is f16 row-major on the device, dst f32 or f16. Chooses the
+ * split-K GEMV for t <= 8 and the tensor-core GEMM above (the reference switches at t > 8 too:
+ * crates/backend-gpu/src/rawcuda/w4a16_dec/prefill.rs:81-345). */
+W4A16_API int w4a16_lin_forward(w4a16_dec* dec, const char* name, const void* x16_dev, void* dst_dev, int t,
+                      int out_kind, void* stream);
+/* W4a16Dec::sk_single_dev (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:89-127):
+ * the decode GEMV on one linear, t in 1..8. */
+W4A16_API int w4a16_sk_single_dev(w4a16_dec* dec, const char* name, const void* x16_dev, void* out_dev, int t,
+                        int out_kind, void* stream);
+/* W4a16Dec::sk_multi_dev (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:23-57): up to
+ * four linears that share x and k (q|k|v, gate|up) in ONE launch; outs[i] is [t][n_i]. */
+W4A16_API int w4a16_sk_multi_dev(w4a16_dec* dec, const char* const* names, int n_seg, const void* x16_dev,
+                       void* const* outs_dev, int t, int out_kind, void* stream);
+/* Host-buffer form of lin_forward: copies x from HOST (pinned or pageable) memory, runs the
+ * linear, copies dst back and synchronises. The end-to-end call a host engine makes per step
+ * (the reference's host round trip: Gptq4::gemm, crates/backend-gpu/src/rawcuda/gptq4.rs:99-189,
+ * with the weights already resident as in W4a16Dec). */
+W4A16_API int w4a16_lin_forward_host(w4a16_dec* dec, const char* name, const void* x16_host, void* dst_host, int t,
+                           int out_kind);
+/* Gptq4::gemm (crates/backend-gpu/src/rawcuda/gptq4.rs:99-189): everything from HOST memory --
+ * uploads q and s, runs x[t][k] through the linear, returns f32 [t][n], frees the weights. */
+W4A16_API int w4a16_gptq4_gemm(w4a16_dec* dec, const void* x16_host, int t, const void* q_host, const void* s_host,
+                     int n, int k, int group, int scale_bf16, float* out_host);
+
+/* ---- graph capture ----------------------------------------------------------------------- */
+
+/* CudaCtx::capture_begin / capture_end / graph_instantiate / graph_launch / graph destroy
+ * (crates/backend-gpu/src/rawcuda/ctx/graph.rs:4-85) on the decoder's stream. A forward call
+ * that would have to grow scratch during capture fails instead; run it once un-captured first
+ * (the reference's warm_for_capture, crates/backend-gpu/src/rawcuda/ctx/mod.rs:379-384). */
+W4A16_API int w4a16_capture_begin(w4a16_dec* dec);
+W4A16_API int w4a16_capture_end(w4a16_dec* dec, void** graph_exec_out);
+W4A16_API int w4a16_graph_launch(w4a16_dec* dec, void* graph_exec);
+W4A16_API int w4a16_graph_destroy(w4a16_dec* dec, void* graph_exec);
+/* One host-driven step over a captured chain, the shape of W4a16Dec::forward_device_argmax
+ * (crates/backend-gpu/src/rawcuda/w4a16_dec/graphs.rs:202): copies x_bytes from HOST x_host to
+ * DEVICE x_dev, replays the graph, copies y_bytes from DEVICE y_dev to HOST y_host, synchronises. */
+W4A16_API int w4a16_graph_step_host(w4a16_dec* dec, void* graph_exec, const void* x_host, void* x_dev,
+                                    size_t x_bytes, const void* y_dev, void* y_host, size_t y_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* W4A16_B200_H */

@@ -1,0 +1,65 @@
+"""ctypes loader for ``libw4a16_b200.so`` (the C ABI declared in ``include/w4a16_b200.h``).
+
+There is no CPU fallback: if the shared library is missing, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import re
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(HERE, "libw4a16_b200.so")
+HEADER = os.path.join(os.path.dirname(HERE), "include", "w4a16_b200.h")
+
+_lib = None
+
+_vp, _i, _sz = C.c_void_p, C.c_int, C.c_size_t
+_SIGS = {
+    "w4a16_dec_new": (_i, [_i, C.POINTER(_vp)]),
+    "w4a16_dec_free": (None, [_vp]),
+    "w4a16_last_error": (C.c_char_p, [_vp]),
+    "w4a16_stream": (_vp, [_vp]),
+    "w4a16_sync": (_i, [_vp]),
+    "w4a16_launch_count": (C.c_ulonglong, [_vp]),
+    "w4a16_set_tuning": (_i, [_vp, C.c_char_p, _i]),
+    "w4a16_check_shapes": (_i, [_sz] * 7),
+    "w4a16_upload_lin_g": (_i, [_vp, C.c_char_p, _vp, _sz, _vp, _sz, _i, _i, _i, _i]),
+    "w4a16_upload_lin_g_dev": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _i, _i]),
+    "w4a16_lin_spec": (_i, [_vp, C.c_char_p, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
+    "w4a16_drop_lin": (_i, [_vp, C.c_char_p]),
+    "w4a16_weights_bytes": (_sz, [_vp]),
+    "w4a16_unpack_lin": (_i, [_vp, C.c_char_p, _vp, _vp, _vp]),
+    "w4a16_dequant_lin": (_i, [_vp, C.c_char_p, _vp, _i, _vp]),
+    "w4a16_lin_forward": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
+    "w4a16_sk_single_dev": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
+    "w4a16_sk_multi_dev": (_i, [_vp, C.POINTER(C.c_char_p), _i, _vp, C.POINTER(_vp), _i, _i, _vp]),
+    "w4a16_lin_forward_host": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i]),
+    "w4a16_gptq4_gemm": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "w4a16_capture_begin": (_i, [_vp]),
+    "w4a16_capture_end": (_i, [_vp, C.POINTER(_vp)]),
+    "w4a16_graph_launch": (_i, [_vp, _vp]),
+    "w4a16_graph_destroy": (_i, [_vp, _vp]),
+    "w4a16_graph_step_host": (_i, [_vp, _vp, _vp, _vp, _sz, _vp, _vp, _sz]),
+}
+
+
+def declared_symbols() -> list[str]:
+    """Every entry point the public header declares."""
+    text = open(HEADER).read()
+    return sorted(set(re.findall(r"W4A16_API\s+[\w\s\*]+?\b(w4a16_\w+)\s*\(", text)))
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(SO_PATH):
+            raise RuntimeError(
+                f"{SO_PATH} is missing: build it with `python -m llm170_b200.build` "
+                "(there is no CPU fallback for the W4A16 path)")
+        L = C.CDLL(SO_PATH)
+        for name, (res, args) in _SIGS.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib

@@ -1,0 +1,621 @@
+// Host side of libw4a16_b200: the decoder object (weight residency, scratch, kernel selection) and
+// the extern "C" entry points declared in include/w4a16_b200.h.
+//
+// Mirrors the parts of the reference's W4a16Dec that sit on the W4A16 matmul path:
+// weight maps (crates/backend-gpu/src/rawcuda/w4a16_dec/mod.rs:547-556), upload + repack
+// (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:15-179), path selection
+// (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/mod.rs:121-144), split-K launch policy
+// (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:3-127) and graph capture
+// (crates/backend-gpu/src/rawcuda/ctx/graph.rs:4-85).
+#include "dec.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/w4a16_b200.h"
+
+namespace {
+thread_local std::string g_create_error;
+}
+
+namespace w4 {
+
+int Dec::fail(const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    err = buf;
+    return 1;
+}
+
+int Dec::cuda_fail(const char* what, cudaError_t e) {
+    return fail("w4a16: %s: %s", what, cudaGetErrorString(e));
+}
+
+bool Dec::capturing(cudaStream_t st) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return cs != cudaStreamCaptureStatusNone;
+}
+
+// Grow-only scratch. Never grows while `st` is capturing (allocation is illegal there).
+int Dec::ensure_scratch(size_t part_floats, int grid_x, cudaStream_t st) {
+    if (part_floats <= part_cap && (size_t)grid_x <= counters_cap) {
+        return 0;
+    }
+    if (capturing(st)) {
+        return fail("w4a16: scratch too small during graph capture; run the call once before capturing");
+    }
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        return cuda_fail("sync before scratch growth", e);
+    }
+    if (part_floats > part_cap) {
+        if (part) {
+            cudaFree(part);
+            part = nullptr;
+            part_cap = 0;
+        }
+        e = cudaMalloc(&part, part_floats * sizeof(float));
+        if (e != cudaSuccess) {
+            return cuda_fail("alloc split-K scratch", e);
+        }
+        part_cap = part_floats;
+    }
+    if ((size_t)grid_x > counters_cap) {
+        if (counters) {
+            cudaFree(counters);
+            counters = nullptr;
+            counters_cap = 0;
+        }
+        const size_t cap = (size_t)grid_x < 4096 ? 4096 : (size_t)grid_x;
+        e = cudaMalloc(&counters, cap * sizeof(unsigned));
+        if (e != cudaSuccess) {
+            return cuda_fail("alloc split-K tickets", e);
+        }
+        cudaMemset(counters, 0, cap * sizeof(unsigned));
+        counters_cap = cap;
+    }
+    return 0;
+}
+
+void Dec::free_lin(Lin& l) {
+    if (l.qt) {
+        cudaFree(l.qt);
+    }
+    if (l.st) {
+        cudaFree(l.st);
+    }
+    weights_bytes -= l.bytes;
+    l = Lin{};
+}
+
+int Dec::upload_common(const char* name, const void* q_dev, const void* s_dev, int n, int k, int group,
+                       int scale_bf16) {
+    // q_dev/s_dev: boundary format already on the device
+    Lin l;
+    l.n = n;
+    l.k = k;
+    l.group = group;
+    const size_t qb = (size_t)n * (size_t)(k / 2), sb = (size_t)n * (size_t)(k / group) * 2;
+    cudaError_t e = cudaMalloc(&l.qt, qb);
+    if (e != cudaSuccess) {
+        return cuda_fail("alloc weights", e);
+    }
+    e = cudaMalloc(&l.st, sb);
+    if (e != cudaSuccess) {
+        cudaFree(l.qt);
+        return cuda_fail("alloc scales", e);
+    }
+    cudaMemsetAsync(err_flag, 0, sizeof(int), stream);
+    launch_repack_q((const uint32_t*)q_dev, l.qt, n, k, stream);
+    launch_repack_s((const uint16_t*)s_dev, l.st, n, k, group, scale_bf16, err_flag, stream);
+    int bad = 0;
+    e = cudaMemcpyAsync(&bad, err_flag, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) {
+        e = cudaStreamSynchronize(stream);
+    }
+    if (e != cudaSuccess || bad) {
+        cudaFree(l.qt);
+        cudaFree(l.st);
+        if (e != cudaSuccess) {
+            return cuda_fail("repack", e);
+        }
+        return fail("w4a16 upload %s: a bf16 scale is not representable in f16", name);
+    }
+    l.bytes = qb + sb;
+    auto it = lins.find(name);
+    if (it != lins.end()) {
+        free_lin(it->second);
+        lins.erase(it);
+    }
+    weights_bytes += l.bytes;
+    lins[name] = l;
+    return 0;
+}
+
+int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, int t, int out_kind,
+              cudaStream_t st) {
+    if (t < 1 || t > GEMV_MAX_M) {
+        return fail("w4a16 gemv: t=%d outside 1..%d", t, GEMV_MAX_M);
+    }
+    if (nseg < 1 || nseg > GEMV_MAX_SEG) {
+        return fail("w4a16 gemv: %d segments outside 1..%d", nseg, GEMV_MAX_SEG);
+    }
+    GemvArgs a{};
+    a.nseg = nseg;
+    a.k = ls[0]->k;
+    a.group = ls[0]->group;
+    for (int i = 0; i < nseg; ++i) {
+        if (ls[i]->k != a.k || ls[i]->group != a.group) {
+            return fail("w4a16 gemv: segments must share k and group");
+        }
+        a.seg[i].qt = (const uint4*)ls[i]->qt;
+        a.seg[i].st = (const uint32_t*)ls[i]->st;
+        a.seg[i].out = outs[i];
+        a.seg[i].n = ls[i]->n;
+    }
+    a.m = t;
+    a.out_f16 = out_kind == W4A16_OUT_F16;
+    a.x = (const uint16_t*)x;
+    const int grid_x = gemv_plan_ctas(a);
+    int ks = tune_gemv_ksplit > 0 ? tune_gemv_ksplit
+                                  : gemv_pick_ksplit(grid_x, a.k, a.group, t, sm_count, tune_gemv_ctas_per_sm);
+    const int unit = a.group > TILE_K ? a.group : TILE_K;
+    if (ks > a.k / unit) {
+        ks = a.k / unit;
+    }
+    while (gemv_smem_bytes(a.k, a.group, t, ks) > 96 * 1024 && ks < a.k / unit) {
+        ++ks;
+    }
+    if (gemv_smem_bytes(a.k, a.group, t, ks) > 96 * 1024) {
+        return fail("w4a16 gemv: k=%d too large for t=%d", a.k, t);
+    }
+    a.ksplit = ks;
+    if (int rc = ensure_scratch(gemv_part_floats(grid_x, ks), grid_x, st)) {
+        return rc;
+    }
+    a.part = part;
+    a.counters = counters;
+    cudaError_t e = launch_gemv(a, grid_x, st);
+    if (e != cudaSuccess) {
+        return cuda_fail("launch gemv", e);
+    }
+    launches++;
+    return 0;
+}
+
+}  // namespace w4
+
+using w4::Dec;
+using w4::Lin;
+
+struct w4a16_dec {
+    Dec d;
+};
+
+static cudaStream_t pick_stream(w4a16_dec* dec, void* stream) {
+    return stream ? (cudaStream_t)stream : dec->d.stream;
+}
+
+extern "C" {
+
+int w4a16_dec_new(int device, w4a16_dec** out) {
+    if (!out) {
+        g_create_error = "w4a16_dec_new: null out pointer";
+        return 1;
+    }
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        g_create_error = std::string("w4a16_dec_new: no CUDA device: ") + cudaGetErrorString(e);
+        cudaGetLastError();
+        return 1;
+    }
+    if (device < 0 || device >= count) {
+        g_create_error = "w4a16_dec_new: device ordinal out of range";
+        return 1;
+    }
+    e = cudaSetDevice(device);
+    if (e != cudaSuccess) {
+        g_create_error = std::string("w4a16_dec_new: cudaSetDevice: ") + cudaGetErrorString(e);
+        return 1;
+    }
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) {
+        g_create_error = std::string("w4a16_dec_new: device properties: ") + cudaGetErrorString(e);
+        return 1;
+    }
+    if (prop.major != 10) {
+        g_create_error = "w4a16_dec_new: this library is built for sm_100a (B200) only";
+        return 1;
+    }
+    w4a16_dec* dec = new w4a16_dec();
+    Dec& d = dec->d;
+    d.device = device;
+    d.sm_count = prop.multiProcessorCount;
+    e = cudaStreamCreateWithFlags(&d.stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) {
+        e = cudaMalloc(&d.err_flag, sizeof(int));
+    }
+    if (e == cudaSuccess) {
+        e = w4::gemv_init_device();
+    }
+    if (e != cudaSuccess) {
+        g_create_error = std::string("w4a16_dec_new: ") + cudaGetErrorString(e);
+        delete dec;
+        return 1;
+    }
+    if (d.ensure_scratch(1 << 20, 4096, d.stream)) {
+        g_create_error = d.err;
+        delete dec;
+        return 1;
+    }
+    *out = dec;
+    return 0;
+}
+
+void w4a16_dec_free(w4a16_dec* dec) {
+    if (!dec) {
+        return;
+    }
+    Dec& d = dec->d;
+    cudaSetDevice(d.device);
+    cudaDeviceSynchronize();
+    for (auto& kv : d.lins) {
+        d.free_lin(kv.second);
+    }
+    d.lins.clear();
+    if (d.part) {
+        cudaFree(d.part);
+    }
+    if (d.counters) {
+        cudaFree(d.counters);
+    }
+    if (d.err_flag) {
+        cudaFree(d.err_flag);
+    }
+    if (d.xh) {
+        cudaFree(d.xh);
+    }
+    if (d.yh) {
+        cudaFree(d.yh);
+    }
+    if (d.stream) {
+        cudaStreamDestroy(d.stream);
+    }
+    delete dec;
+}
+
+const char* w4a16_last_error(const w4a16_dec* dec) {
+    return dec ? dec->d.err.c_str() : g_create_error.c_str();
+}
+
+void* w4a16_stream(w4a16_dec* dec) { return dec ? (void*)dec->d.stream : nullptr; }
+
+int w4a16_sync(w4a16_dec* dec) {
+    cudaError_t e = cudaStreamSynchronize(dec->d.stream);
+    return e == cudaSuccess ? 0 : dec->d.cuda_fail("sync", e);
+}
+
+unsigned long long w4a16_launch_count(w4a16_dec* dec) { return dec->d.launches; }
+
+int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
+    Dec& d = dec->d;
+    if (!strcmp(key, "gemv_ctas_per_sm")) {
+        if (value < 1 || value > 32) {
+            return d.fail("w4a16 tuning: gemv_ctas_per_sm must be 1..32");
+        }
+        d.tune_gemv_ctas_per_sm = value;
+        return 0;
+    }
+    if (!strcmp(key, "gemv_ksplit")) {
+        if (value < 0 || value > 1024) {
+            return d.fail("w4a16 tuning: gemv_ksplit must be 0..1024");
+        }
+        d.tune_gemv_ksplit = value;
+        return 0;
+    }
+    return d.fail("w4a16 tuning: unknown key %s", key);
+}
+
+int w4a16_check_shapes(size_t t, size_t qlen, size_t slen, size_t xlen, size_t n, size_t k, size_t group) {
+    // crates/backend-gpu/src/rawcuda/gptq4.rs:31-48. The reference's extra t==1 limit
+    // (k <= group*256, its GEMV keeps scales in shared memory, :51-56) does not apply here.
+    if ((group != 128 && group != 32) || k % group != 0 || t == 0 || qlen != n * (k / 8) ||
+        slen != n * (k / group) || xlen != t * k) {
+        return 1;
+    }
+    return 0;
+}
+
+static int validate_upload(Dec& d, const char* name, size_t q_bytes, size_t s_bytes, int n, int k, int group) {
+    if (!name || !*name) {
+        return d.fail("w4a16 upload: empty name");
+    }
+    if (n <= 0 || k <= 0 || (group != 128 && group != 32) || k % group != 0) {
+        return d.fail("w4a16 upload %s: unsupported n=%d k=%d group=%d", name, n, k, group);
+    }
+    if (q_bytes != (size_t)n * (size_t)(k / 2) || s_bytes != (size_t)n * (size_t)(k / group) * 2) {
+        return d.fail("w4a16 upload %s: q=%zu s=%zu bytes do not match n=%d k=%d g%d", name, q_bytes, s_bytes, n, k,
+                      group);
+    }
+    if (!w4::shape_ok(n, k, group)) {
+        return d.fail("w4a16 upload %s: tiled layout needs n%%16==0 and k%%64==0 (n=%d k=%d)", name, n, k);
+    }
+    return 0;
+}
+
+int w4a16_upload_lin_g(w4a16_dec* dec, const char* name, const void* q, size_t q_bytes, const void* s,
+                       size_t s_bytes, int n, int k, int group, int scale_bf16) {
+    Dec& d = dec->d;
+    cudaSetDevice(d.device);
+    if (int rc = validate_upload(d, name, q_bytes, s_bytes, n, k, group)) {
+        return rc;
+    }
+    void *dq = nullptr, *ds = nullptr;
+    cudaError_t e = cudaMalloc(&dq, q_bytes);
+    if (e != cudaSuccess) {
+        return d.cuda_fail("alloc upload staging", e);
+    }
+    e = cudaMalloc(&ds, s_bytes);
+    if (e != cudaSuccess) {
+        cudaFree(dq);
+        return d.cuda_fail("alloc upload staging", e);
+    }
+    e = cudaMemcpyAsync(dq, q, q_bytes, cudaMemcpyHostToDevice, d.stream);
+    if (e == cudaSuccess) {
+        e = cudaMemcpyAsync(ds, s, s_bytes, cudaMemcpyHostToDevice, d.stream);
+    }
+    int rc = 0;
+    if (e != cudaSuccess) {
+        rc = d.cuda_fail("copy weights to device", e);
+    } else {
+        rc = d.upload_common(name, dq, ds, n, k, group, scale_bf16);
+    }
+    cudaStreamSynchronize(d.stream);
+    cudaFree(dq);
+    cudaFree(ds);
+    return rc;
+}
+
+int w4a16_upload_lin_g_dev(w4a16_dec* dec, const char* name, const void* q_dev, const void* s_dev, int n,
+                           int k, int group, int scale_bf16) {
+    Dec& d = dec->d;
+    cudaSetDevice(d.device);
+    if (n <= 0 || k <= 0) {
+        return d.fail("w4a16 upload: bad shape");
+    }
+    if (int rc = validate_upload(d, name, (size_t)n * (size_t)(k / 2),
+                                 (group == 128 || group == 32) && k % group == 0
+                                     ? (size_t)n * (size_t)(k / group) * 2
+                                     : 0,
+                                 n, k, group)) {
+        return rc;
+    }
+    // order after whatever produced q/s on the legacy default stream
+    cudaDeviceSynchronize();
+    return d.upload_common(name, q_dev, s_dev, n, k, group, scale_bf16);
+}
+
+static Lin* find_lin(Dec& d, const char* name) {
+    auto it = d.lins.find(name ? name : "");
+    if (it == d.lins.end()) {
+        d.fail("w4a16: unknown linear %s", name ? name : "(null)");
+        return nullptr;
+    }
+    return &it->second;
+}
+
+int w4a16_lin_spec(w4a16_dec* dec, const char* name, int* n, int* k, int* group) {
+    Lin* l = find_lin(dec->d, name);
+    if (!l) {
+        return 1;
+    }
+    if (n) *n = l->n;
+    if (k) *k = l->k;
+    if (group) *group = l->group;
+    return 0;
+}
+
+int w4a16_drop_lin(w4a16_dec* dec, const char* name) {
+    Dec& d = dec->d;
+    auto it = d.lins.find(name ? name : "");
+    if (it == d.lins.end()) {
+        return d.fail("w4a16: unknown linear %s", name ? name : "(null)");
+    }
+    cudaSetDevice(d.device);
+    cudaDeviceSynchronize();
+    d.free_lin(it->second);
+    d.lins.erase(it);
+    return 0;
+}
+
+size_t w4a16_weights_bytes(w4a16_dec* dec) { return dec->d.weights_bytes; }
+
+int w4a16_unpack_lin(w4a16_dec* dec, const char* name, void* q_dev, void* s_dev, void* stream) {
+    Dec& d = dec->d;
+    Lin* l = find_lin(d, name);
+    if (!l) {
+        return 1;
+    }
+    cudaStream_t st = pick_stream(dec, stream);
+    w4::launch_unpack_q(l->qt, (uint32_t*)q_dev, l->n, l->k, st);
+    w4::launch_unpack_s(l->st, (uint16_t*)s_dev, l->n, l->k, l->group, st);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : d.cuda_fail("unpack", e);
+}
+
+int w4a16_dequant_lin(w4a16_dec* dec, const char* name, void* out_dev, int out_kind, void* stream) {
+    Dec& d = dec->d;
+    Lin* l = find_lin(d, name);
+    if (!l) {
+        return 1;
+    }
+    w4::launch_dequant(l->qt, l->st, out_dev, l->n, l->k, l->group, out_kind == W4A16_OUT_F16,
+                       pick_stream(dec, stream));
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : d.cuda_fail("dequant", e);
+}
+
+int w4a16_sk_single_dev(w4a16_dec* dec, const char* name, const void* x16_dev, void* out_dev, int t,
+                        int out_kind, void* stream) {
+    Dec& d = dec->d;
+    Lin* l = find_lin(d, name);
+    if (!l) {
+        return 1;
+    }
+    const Lin* ls[1] = {l};
+    void* outs[1] = {out_dev};
+    return d.gemv(ls, 1, x16_dev, outs, t, out_kind, pick_stream(dec, stream));
+}
+
+int w4a16_sk_multi_dev(w4a16_dec* dec, const char* const* names, int n_seg, const void* x16_dev,
+                       void* const* outs_dev, int t, int out_kind, void* stream) {
+    Dec& d = dec->d;
+    if (n_seg < 1 || n_seg > w4::GEMV_MAX_SEG) {
+        return d.fail("w4a16 sk_multi: %d segments outside 1..%d", n_seg, w4::GEMV_MAX_SEG);
+    }
+    const Lin* ls[w4::GEMV_MAX_SEG];
+    for (int i = 0; i < n_seg; ++i) {
+        ls[i] = find_lin(d, names[i]);
+        if (!ls[i]) {
+            return 1;
+        }
+    }
+    return d.gemv(ls, n_seg, x16_dev, outs_dev, t, out_kind, pick_stream(dec, stream));
+}
+
+int w4a16_lin_forward(w4a16_dec* dec, const char* name, const void* x16_dev, void* dst_dev, int t,
+                      int out_kind, void* stream) {
+    Dec& d = dec->d;
+    Lin* l = find_lin(d, name);
+    if (!l) {
+        return 1;
+    }
+    if (t < 1) {
+        return d.fail("w4a16 lin_forward %s: t=%d", name, t);
+    }
+    cudaStream_t st = pick_stream(dec, stream);
+    if (t <= w4::GEMV_MAX_M) {
+        const Lin* ls[1] = {l};
+        void* outs[1] = {dst_dev};
+        return d.gemv(ls, 1, x16_dev, outs, t, out_kind, st);
+    }
+    return d.gemm(l, x16_dev, dst_dev, t, out_kind, st);
+}
+
+int w4a16_lin_forward_host(w4a16_dec* dec, const char* name, const void* x16_host, void* dst_host, int t,
+                           int out_kind) {
+    Dec& d = dec->d;
+    Lin* l = find_lin(d, name);
+    if (!l) {
+        return 1;
+    }
+    if (t < 1) {
+        return d.fail("w4a16 lin_forward_host %s: t=%d", name, t);
+    }
+    const size_t xb = (size_t)t * l->k * 2;
+    const size_t yb = (size_t)t * l->n * (out_kind == W4A16_OUT_F16 ? 2 : 4);
+    if (xb > d.xh_cap) {
+        cudaDeviceSynchronize();
+        if (d.xh) cudaFree(d.xh);
+        d.xh = nullptr;
+        d.xh_cap = 0;
+        cudaError_t e = cudaMalloc(&d.xh, xb);
+        if (e != cudaSuccess) return d.cuda_fail("alloc x staging", e);
+        d.xh_cap = xb;
+    }
+    if (yb > d.yh_cap) {
+        cudaDeviceSynchronize();
+        if (d.yh) cudaFree(d.yh);
+        d.yh = nullptr;
+        d.yh_cap = 0;
+        cudaError_t e = cudaMalloc(&d.yh, yb);
+        if (e != cudaSuccess) return d.cuda_fail("alloc y staging", e);
+        d.yh_cap = yb;
+    }
+    cudaError_t e = cudaMemcpyAsync(d.xh, x16_host, xb, cudaMemcpyHostToDevice, d.stream);
+    if (e != cudaSuccess) return d.cuda_fail("copy x to device", e);
+    if (int rc = w4a16_lin_forward(dec, name, d.xh, d.yh, t, out_kind, d.stream)) {
+        return rc;
+    }
+    e = cudaMemcpyAsync(dst_host, d.yh, yb, cudaMemcpyDeviceToHost, d.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(d.stream);
+    return e == cudaSuccess ? 0 : d.cuda_fail("copy y to host", e);
+}
+
+int w4a16_gptq4_gemm(w4a16_dec* dec, const void* x16_host, int t, const void* q_host, const void* s_host,
+                     int n, int k, int group, int scale_bf16, float* out_host) {
+    Dec& d = dec->d;
+    if (n <= 0 || k <= 0 || t <= 0 || (group != 128 && group != 32) || k % group != 0) {
+        return d.fail("gptq4: shape contract violated n=%d k=%d t=%d group=%d", n, k, t, group);
+    }
+    static const char* TMP = "\x01gptq4.tmp";
+    if (int rc = w4a16_upload_lin_g(dec, TMP, q_host, (size_t)n * (k / 2), s_host, (size_t)n * (k / group) * 2, n,
+                                    k, group, scale_bf16)) {
+        return rc;
+    }
+    int rc = w4a16_lin_forward_host(dec, TMP, x16_host, out_host, t, W4A16_OUT_F32);
+    std::string keep = d.err;
+    w4a16_drop_lin(dec, TMP);
+    if (rc) d.err = keep;
+    return rc;
+}
+
+int w4a16_capture_begin(w4a16_dec* dec) {
+    cudaError_t e = cudaStreamBeginCapture(dec->d.stream, cudaStreamCaptureModeThreadLocal);
+    return e == cudaSuccess ? 0 : dec->d.cuda_fail("cudaStreamBeginCapture", e);
+}
+
+int w4a16_capture_end(w4a16_dec* dec, void** graph_exec_out) {
+    Dec& d = dec->d;
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(d.stream, &g);
+    if (e != cudaSuccess) {
+        return d.cuda_fail("cudaStreamEndCapture", e);
+    }
+    cudaGraphExec_t ex = nullptr;
+    e = cudaGraphInstantiate(&ex, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) {
+        return d.cuda_fail("cudaGraphInstantiate", e);
+    }
+    e = cudaGraphUpload(ex, d.stream);
+    if (e != cudaSuccess) {
+        cudaGraphExecDestroy(ex);
+        return d.cuda_fail("cudaGraphUpload", e);
+    }
+    *graph_exec_out = (void*)ex;
+    return 0;
+}
+
+int w4a16_graph_launch(w4a16_dec* dec, void* graph_exec) {
+    cudaError_t e = cudaGraphLaunch((cudaGraphExec_t)graph_exec, dec->d.stream);
+    return e == cudaSuccess ? 0 : dec->d.cuda_fail("cudaGraphLaunch", e);
+}
+
+int w4a16_graph_destroy(w4a16_dec* dec, void* graph_exec) {
+    cudaError_t e = cudaGraphExecDestroy((cudaGraphExec_t)graph_exec);
+    return e == cudaSuccess ? 0 : dec->d.cuda_fail("cudaGraphExecDestroy", e);
+}
+
+int w4a16_graph_step_host(w4a16_dec* dec, void* graph_exec, const void* x_host, void* x_dev,
+                          size_t x_bytes, const void* y_dev, void* y_host, size_t y_bytes) {
+    Dec& d = dec->d;
+    cudaError_t e = cudaMemcpyAsync(x_dev, x_host, x_bytes, cudaMemcpyHostToDevice, d.stream);
+    if (e == cudaSuccess) e = cudaGraphLaunch((cudaGraphExec_t)graph_exec, d.stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(y_host, y_dev, y_bytes, cudaMemcpyDeviceToHost, d.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(d.stream);
+    return e == cudaSuccess ? 0 : d.cuda_fail("graph step", e);
+}
+
+}  // extern "C"

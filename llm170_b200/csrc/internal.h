@@ -1,0 +1,58 @@
+// Internal declarations shared by the translation units of libw4a16_b200.so.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "layout.cuh"
+
+namespace w4 {
+
+// ---- repack.cu -------------------------------------------------------------------------------
+void launch_repack_q(const uint32_t* q_orig, uint32_t* qt, int n, int k, cudaStream_t st);
+// err_flag (device int, may be null) is set to 1 if a bf16 scale is not exactly an f16 value.
+void launch_repack_s(const uint16_t* s_orig, uint16_t* stl, int n, int k, int group, int scale_bf16,
+                     int* err_flag, cudaStream_t st);
+void launch_unpack_q(const uint32_t* qt, uint32_t* q_orig, int n, int k, cudaStream_t st);
+void launch_unpack_s(const uint16_t* stl, uint16_t* s_orig, int n, int k, int group, cudaStream_t st);
+// out: f32 [n][k] (out_f16 == 0) or f16 [n][k] (out_f16 == 1, round-to-nearest-even of the f32 value)
+void launch_dequant(const uint32_t* qt, const uint16_t* stl, void* out, int n, int k, int group,
+                    int out_f16, cudaStream_t st);
+
+// ---- gemv.cu ---------------------------------------------------------------------------------
+constexpr int GEMV_MAX_SEG = 4;
+constexpr int GEMV_MAX_M = 8;
+constexpr int GEMV_WARPS = 8;  // row blocks per CTA
+
+struct GemvSeg {
+    const uint4* qt;
+    const uint32_t* st;  // scale pairs, one u32 = (row j, row j+8)
+    void* out;           // [m][n] f32 or f16
+    int n;               // rows of this segment
+    int cta0;            // first grid.x index of this segment
+};
+
+struct GemvArgs {
+    GemvSeg seg[GEMV_MAX_SEG];
+    int nseg;
+    int k;
+    int group;
+    int m;
+    int out_f16;
+    int ksplit;
+    const uint16_t* x;  // f16 [m][k]
+    float* part;        // [ksplit][grid_x][GEMV_WARPS*16][GEMV_MAX_M] partial sums (ksplit > 1)
+    unsigned* counters; // [grid_x], zero on entry, left zero on exit
+};
+
+// Total CTAs along x for the segments in `a` (fills seg[].cta0).
+int gemv_plan_ctas(GemvArgs& a);
+// Smallest and preferred split-K for a plan (see gemv.cu).
+int gemv_pick_ksplit(int grid_x, int k, int group, int m, int sm_count, int target_ctas_per_sm);
+size_t gemv_smem_bytes(int k, int group, int m, int ksplit);
+size_t gemv_part_floats(int grid_x, int ksplit);
+cudaError_t launch_gemv(const GemvArgs& a, int grid_x, cudaStream_t st);
+// Raises the dynamic shared-memory limit of the GEMV kernels on the current device.
+cudaError_t gemv_init_device();
+
+}  // namespace w4

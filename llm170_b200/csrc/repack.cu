@@ -1,0 +1,183 @@
+// Re-tiling of compressed-tensors int4 weights into the T64 device layout (see layout.cuh), its
+// inverse, and the element-wise dequantiser used by the parity tests.
+//
+// Replaces the host repacker of the reference (crates/core/src/marlin.rs:2-67, called from
+// crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:99-179): here the original bytes are copied
+// to the device once and re-tiled by a kernel, so load time is bounded by the H2D copy.
+#include <cuda_fp16.h>
+
+#include "internal.h"
+
+namespace w4 {
+
+namespace {
+
+__device__ __forceinline__ uint32_t spread4(uint32_t four_nibbles) {
+    // four_nibbles = e0 | e1<<4 | e2<<8 | e3<<12  ->  positions 0, 4, 2, 6
+    const uint32_t e0 = four_nibbles & 0xFu, e1 = (four_nibbles >> 4) & 0xFu;
+    const uint32_t e2 = (four_nibbles >> 8) & 0xFu, e3 = (four_nibbles >> 12) & 0xFu;
+    return e0 | (e1 << 16) | (e2 << 8) | (e3 << 24);
+}
+
+__device__ __forceinline__ uint32_t gather4(uint32_t word) {
+    // inverse of spread4 for the row-r0 positions (0,4,2,6)
+    return (word & 0xFu) | (((word >> 16) & 0xFu) << 4) | (((word >> 8) & 0xFu) << 8) |
+           (((word >> 24) & 0xFu) << 12);
+}
+
+struct WordCoord {
+    int r0, kbase;
+};
+
+__device__ __forceinline__ WordCoord coord_of(size_t widx, int nkb) {
+    const int w = (int)(widx & 3);
+    const int lane = (int)((widx >> 2) & 31);
+    const size_t tile = widx >> 7;
+    const int kb = (int)(tile % (size_t)nkb);
+    const int rb = (int)(tile / (size_t)nkb);
+    const int g = lane >> 2, t = lane & 3, p = w >> 1, h = w & 1;
+    WordCoord c;
+    c.r0 = rb * TILE_ROWS + g;
+    c.kbase = kb * TILE_K + 32 * p + 8 * t + 4 * h;
+    return c;
+}
+
+__global__ void repack_q_kernel(const uint32_t* __restrict__ q, uint32_t* __restrict__ qt, int n, int k) {
+    const size_t total = (size_t)n * (size_t)(k / 8);
+    const int nkb = k / TILE_K, k8 = k / 8;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const WordCoord c = coord_of(i, nkb);
+        const int sh = 4 * (c.kbase & 7);
+        const uint32_t a = (q[(size_t)c.r0 * k8 + (c.kbase >> 3)] >> sh) & 0xFFFFu;
+        const uint32_t b = (q[(size_t)(c.r0 + 8) * k8 + (c.kbase >> 3)] >> sh) & 0xFFFFu;
+        qt[i] = spread4(a) | (spread4(b) << 4);
+    }
+}
+
+__global__ void unpack_q_kernel(const uint32_t* __restrict__ qt, uint32_t* __restrict__ q, int n, int k) {
+    // one thread per ORIGINAL word (8 consecutive k of one row) = two packed words (h = 0, 1)
+    const size_t total = (size_t)n * (size_t)(k / 8);
+    const int k8 = k / 8;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const int row = (int)(i / (size_t)k8), kw = (int)(i % (size_t)k8);
+        int pos0, pos1;
+        const size_t w0 = word_index(row, kw * 8, k, &pos0);
+        const size_t w1 = word_index(row, kw * 8 + 4, k, &pos1);
+        const uint32_t lo = gather4(qt[w0] >> (4 * (pos0 & 1)));
+        const uint32_t hi = gather4(qt[w1] >> (4 * (pos1 & 1)));
+        q[i] = lo | (hi << 16);
+    }
+}
+
+__device__ __forceinline__ uint16_t bf16_to_f16_exact(uint16_t b, int* bad) {
+    const float f = __uint_as_float(((uint32_t)b) << 16);
+    const __half h = __float2half_rn(f);
+    if (__half2float(h) != f && !(f != f)) {
+        *bad = 1;
+    }
+    return __half_as_ushort(h);
+}
+
+__global__ void repack_s_kernel(const uint16_t* __restrict__ s, uint16_t* __restrict__ stl, int n, int ng,
+                                int scale_bf16, int* __restrict__ err) {
+    const size_t total = (size_t)n * (size_t)ng;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        // i indexes the tiled array: [rb][grp][j][hi]
+        const int hi = (int)(i & 1), j = (int)((i >> 1) & 7);
+        const size_t rg = i >> 4;
+        const int grp = (int)(rg % (size_t)ng), rb = (int)(rg / (size_t)ng);
+        uint16_t v = s[(size_t)(rb * TILE_ROWS + j + 8 * hi) * ng + grp];
+        if (scale_bf16) {
+            int bad = 0;
+            v = bf16_to_f16_exact(v, &bad);
+            if (bad && err) {
+                *err = 1;
+            }
+        }
+        stl[i] = v;
+    }
+}
+
+__global__ void unpack_s_kernel(const uint16_t* __restrict__ stl, uint16_t* __restrict__ s, int n, int ng) {
+    const size_t total = (size_t)n * (size_t)ng;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const int hi = (int)(i & 1), j = (int)((i >> 1) & 7);
+        const size_t rg = i >> 4;
+        const int grp = (int)(rg % (size_t)ng), rb = (int)(rg / (size_t)ng);
+        s[(size_t)(rb * TILE_ROWS + j + 8 * hi) * ng + grp] = stl[i];
+    }
+}
+
+// (nibble - 8) * scale in f32 -- exact: 4 significant bits times 11 -- for every element.
+// Follows crates/core/src/matmul/cpu.rs:167-194.  OUT_F16 additionally rounds once to f16 (RNE),
+// which is the value the tensor-core GEMM feeds its MMA.
+template <bool OUT_F16>
+__global__ void dequant_kernel(const uint32_t* __restrict__ qt, const uint16_t* __restrict__ stl,
+                               void* __restrict__ out, int n, int k, int group) {
+    const size_t total = (size_t)n * (size_t)(k / 8);
+    const int nkb = k / TILE_K, ng = k / group;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const WordCoord c = coord_of(i, nkb);
+        const uint32_t w = qt[i];
+        const int rb = c.r0 / TILE_ROWS, g = c.r0 % TILE_ROWS;
+        const int grp = c.kbase / group;
+        const size_t sbase = (((size_t)rb * ng + grp) * 8 + g) * 2;
+        const float s0 = __half2float(__ushort_as_half(stl[sbase]));
+        const float s1 = __half2float(__ushort_as_half(stl[sbase + 1]));
+        const int pos[4] = {0, 4, 2, 6};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float v0 = (float)((int)((w >> (4 * pos[e])) & 0xFu) - 8) * s0;
+            const float v1 = (float)((int)((w >> (4 * (pos[e] + 1))) & 0xFu) - 8) * s1;
+            const size_t o0 = (size_t)c.r0 * k + c.kbase + e;
+            const size_t o1 = (size_t)(c.r0 + 8) * k + c.kbase + e;
+            if (OUT_F16) {
+                ((__half*)out)[o0] = __float2half_rn(v0);
+                ((__half*)out)[o1] = __float2half_rn(v1);
+            } else {
+                ((float*)out)[o0] = v0;
+                ((float*)out)[o1] = v1;
+            }
+        }
+    }
+}
+
+inline int grid_for(size_t total) {
+    size_t b = (total + 255) / 256;
+    if (b > 148 * 32) {
+        b = 148 * 32;
+    }
+    return b < 1 ? 1 : (int)b;
+}
+
+}  // namespace
+
+void launch_repack_q(const uint32_t* q, uint32_t* qt, int n, int k, cudaStream_t st) {
+    repack_q_kernel<<<grid_for((size_t)n * (k / 8)), 256, 0, st>>>(q, qt, n, k);
+}
+void launch_repack_s(const uint16_t* s, uint16_t* stl, int n, int k, int group, int scale_bf16, int* err,
+                     cudaStream_t st) {
+    repack_s_kernel<<<grid_for((size_t)n * (k / group)), 256, 0, st>>>(s, stl, n, k / group, scale_bf16, err);
+}
+void launch_unpack_q(const uint32_t* qt, uint32_t* q, int n, int k, cudaStream_t st) {
+    unpack_q_kernel<<<grid_for((size_t)n * (k / 8)), 256, 0, st>>>(qt, q, n, k);
+}
+void launch_unpack_s(const uint16_t* stl, uint16_t* s, int n, int k, int group, cudaStream_t st) {
+    unpack_s_kernel<<<grid_for((size_t)n * (k / group)), 256, 0, st>>>(stl, s, n, k / group);
+}
+void launch_dequant(const uint32_t* qt, const uint16_t* stl, void* out, int n, int k, int group, int out_f16,
+                    cudaStream_t st) {
+    const int g = grid_for((size_t)n * (k / 8));
+    if (out_f16) {
+        dequant_kernel<true><<<g, 256, 0, st>>>(qt, stl, out, n, k, group);
+    } else {
+        dequant_kernel<false><<<g, 256, 0, st>>>(qt, stl, out, n, k, group);
+    }
+}
+
+}  // namespace w4

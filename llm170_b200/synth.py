@@ -68,3 +68,24 @@ def decode_bytes(n: int, k: int, m: int, group: int = 128) -> int:
 
 def gemm_flops(n: int, k: int, m: int) -> int:
     return 2 * m * n * k
+
+
+def make_linear_cuda(n: int, k: int, group: int, seed: int, device, sigma: float = 0.02):
+    """Same recipe as :func:`make_linear`, generated on the device with torch's seeded generator
+    (used where a host round trip of tens of GB would dominate, e.g. the 64-layer stack).
+    Returns (q int32 [n,k/8], s float16 [n,k/group]) CUDA tensors in the boundary format."""
+    import torch
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    w = torch.randn((n, k // group, group), generator=gen, device=device, dtype=torch.float32) * sigma
+    amax = w.abs().amax(dim=2)
+    amax = torch.where(amax == 0, torch.full_like(amax, 1e-6), amax)
+    s16 = (amax / 7.0).to(torch.float16)
+    sf = s16.to(torch.float32)
+    sf = torch.where(sf == 0, torch.full_like(sf, 2.0 ** -24), sf)
+    nib = (torch.clamp(torch.round(w / sf[:, :, None]), -8, 7).to(torch.int32) + 8).reshape(n, k // 8, 8)
+    del w
+    shifts = (4 * torch.arange(8, device=device, dtype=torch.int64))[None, None, :]
+    q = (nib.to(torch.int64) << shifts).sum(dim=2)
+    q = torch.where(q >= 2 ** 31, q - 2 ** 32, q).to(torch.int32)
+    return q.contiguous(), s16.contiguous()

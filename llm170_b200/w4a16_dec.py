@@ -1,0 +1,203 @@
+"""Host-side mirror of the reference's ``W4a16Dec`` linear call sites, over the C ABI.
+
+Method names, argument meaning and error behaviour follow
+crates/backend-gpu/src/rawcuda/w4a16_dec/{upload.rs,kernels/mod.rs,kernels/decode.rs}: every
+method raises ``W4a16Error`` with the library's message where the reference returns
+``Err(String)``.  Device buffers are ``torch`` CUDA tensors (plumbing only); the work runs in
+``libw4a16_b200.so`` on the caller's current CUDA stream.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+
+OUT_F32, OUT_F16 = 0, 1
+
+
+class W4a16Error(RuntimeError):
+    pass
+
+
+def _cur_stream() -> int:
+    return int(torch.cuda.current_stream().cuda_stream)
+
+
+class W4a16Dec:
+    def __init__(self, device: int = 0):
+        if not torch.cuda.is_available():
+            raise W4a16Error("W4a16Dec needs a CUDA device (no CPU fallback exists)")
+        self._L = _lib.lib()
+        self.device = device
+        torch.cuda.set_device(device)
+        h = C.c_void_p()
+        if self._L.w4a16_dec_new(device, C.byref(h)) != 0:
+            raise W4a16Error(self._L.w4a16_last_error(None).decode())
+        self._h = h
+
+    # -- plumbing ---------------------------------------------------------------------------
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.w4a16_dec_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _ck(self, rc: int):
+        if rc != 0:
+            raise W4a16Error(self._L.w4a16_last_error(self._h).decode())
+
+    def _tensor_ok(self, t: torch.Tensor, dtype, what: str):
+        if not (t.is_cuda and t.is_contiguous() and t.dtype == dtype and t.device.index == self.device):
+            raise W4a16Error(f"{what}: need a contiguous {dtype} CUDA tensor on device {self.device}")
+
+    def set_tuning(self, key: str, value: int):
+        self._ck(self._L.w4a16_set_tuning(self._h, key.encode(), int(value)))
+
+    def launch_count(self) -> int:
+        return int(self._L.w4a16_launch_count(self._h))
+
+    def weights_bytes(self) -> int:
+        return int(self._L.w4a16_weights_bytes(self._h))
+
+    def sync(self):
+        self._ck(self._L.w4a16_sync(self._h))
+
+    # -- weights ----------------------------------------------------------------------------
+    def upload_lin(self, name: str, q: np.ndarray, s: np.ndarray, n: int, k: int):
+        """upload.rs:4-13 -- g128 / f16-scale shorthand."""
+        self.upload_lin_g(name, q, s, n, k, 128, False)
+
+    def upload_lin_g(self, name: str, q, s, n: int, k: int, group: int, scale_bf16: bool = False):
+        """upload.rs:15-65.  q: host bytes of u32 [n,k/8]; s: host bytes of 16-bit scales [n,k/group]."""
+        qb = np.ascontiguousarray(q).view(np.uint8).ravel()
+        sb = np.ascontiguousarray(s).view(np.uint8).ravel()
+        self._ck(self._L.w4a16_upload_lin_g(self._h, name.encode(), qb.ctypes.data, qb.size, sb.ctypes.data,
+                                            sb.size, n, k, group, int(scale_bf16)))
+
+    def upload_lin_g_dev(self, name: str, q: torch.Tensor, s: torch.Tensor, n: int, k: int, group: int,
+                         scale_bf16: bool = False):
+        """Device-source upload: q int32 [n,k/8], s int16/float16 [n,k/group] CUDA tensors."""
+        if q.numel() * q.element_size() != n * (k // 2) or s.numel() * s.element_size() != n * (k // group) * 2:
+            raise W4a16Error(f"upload_lin_g_dev {name}: tensor sizes do not match n={n} k={k} g{group}")
+        if not (q.is_cuda and s.is_cuda and q.is_contiguous() and s.is_contiguous()):
+            raise W4a16Error("upload_lin_g_dev: need contiguous CUDA tensors")
+        self._ck(self._L.w4a16_upload_lin_g_dev(self._h, name.encode(), q.data_ptr(), s.data_ptr(), n, k, group,
+                                                int(scale_bf16)))
+
+    def lin_spec(self, name: str):
+        n, k, g = C.c_int(), C.c_int(), C.c_int()
+        self._ck(self._L.w4a16_lin_spec(self._h, name.encode(), C.byref(n), C.byref(k), C.byref(g)))
+        return n.value, k.value, g.value
+
+    def drop_lin(self, name: str):
+        self._ck(self._L.w4a16_drop_lin(self._h, name.encode()))
+
+    def unpack_lin(self, name: str):
+        """Boundary-format (q int32 [n,k/8], s float16 [n,k/group]) rebuilt from the resident tiles."""
+        n, k, g = self.lin_spec(name)
+        q = torch.empty((n, k // 8), dtype=torch.int32, device=f"cuda:{self.device}")
+        s = torch.empty((n, k // g), dtype=torch.float16, device=f"cuda:{self.device}")
+        self._ck(self._L.w4a16_unpack_lin(self._h, name.encode(), q.data_ptr(), s.data_ptr(), _cur_stream()))
+        return q, s
+
+    def dequant_lin(self, name: str, f16: bool = False) -> torch.Tensor:
+        n, k, _ = self.lin_spec(name)
+        out = torch.empty((n, k), dtype=torch.float16 if f16 else torch.float32, device=f"cuda:{self.device}")
+        self._ck(self._L.w4a16_dequant_lin(self._h, name.encode(), out.data_ptr(), OUT_F16 if f16 else OUT_F32,
+                                           _cur_stream()))
+        return out
+
+    # -- forward ----------------------------------------------------------------------------
+    def _out(self, t: int, n: int, f16: bool, dst):
+        dt = torch.float16 if f16 else torch.float32
+        if dst is None:
+            return torch.empty((t, n), dtype=dt, device=f"cuda:{self.device}")
+        self._tensor_ok(dst, dt, "dst")
+        if dst.numel() != t * n:
+            raise W4a16Error(f"dst has {dst.numel()} elements, need {t}x{n}")
+        return dst
+
+    def lin_forward(self, name: str, x16: torch.Tensor, t: int, dst: torch.Tensor | None = None,
+                    out_f16: bool = False) -> torch.Tensor:
+        """kernels/mod.rs:121-144: dst[t,n] = x16[t,k] @ W^T; GEMV for t<=8, tensor-core GEMM above."""
+        n, k, _ = self.lin_spec(name)
+        self._tensor_ok(x16, torch.float16, "x16")
+        if x16.numel() != t * k:
+            raise W4a16Error(f"lin_forward {name}: x has {x16.numel()} elements, need {t}x{k}")
+        dst = self._out(t, n, out_f16, dst)
+        self._ck(self._L.w4a16_lin_forward(self._h, name.encode(), x16.data_ptr(), dst.data_ptr(), t,
+                                           OUT_F16 if out_f16 else OUT_F32, _cur_stream()))
+        return dst
+
+    def sk_single_dev(self, name: str, x16: torch.Tensor, out: torch.Tensor | None = None, t: int = 1,
+                      out_f16: bool = False) -> torch.Tensor:
+        """kernels/decode.rs:89-127: split-K decode GEMV on one linear."""
+        n, k, _ = self.lin_spec(name)
+        self._tensor_ok(x16, torch.float16, "x16")
+        if x16.numel() != t * k:
+            raise W4a16Error(f"sk_single_dev {name}: x has {x16.numel()} elements, need {t}x{k}")
+        out = self._out(t, n, out_f16, out)
+        self._ck(self._L.w4a16_sk_single_dev(self._h, name.encode(), x16.data_ptr(), out.data_ptr(), t,
+                                             OUT_F16 if out_f16 else OUT_F32, _cur_stream()))
+        return out
+
+    def sk_multi_dev(self, names, x16: torch.Tensor, outs=None, t: int = 1, out_f16: bool = False):
+        """kernels/decode.rs:23-57: q|k|v or gate|up in one launch (same x, same k)."""
+        specs = [self.lin_spec(nm) for nm in names]
+        self._tensor_ok(x16, torch.float16, "x16")
+        if x16.numel() != t * specs[0][1]:
+            raise W4a16Error("sk_multi_dev: x size does not match t*k")
+        if outs is None:
+            outs = [None] * len(names)
+        outs = [self._out(t, sp[0], out_f16, o) for sp, o in zip(specs, outs)]
+        arr_n = (C.c_char_p * len(names))(*[nm.encode() for nm in names])
+        arr_o = (C.c_void_p * len(names))(*[o.data_ptr() for o in outs])
+        self._ck(self._L.w4a16_sk_multi_dev(self._h, arr_n, len(names), x16.data_ptr(), arr_o, t,
+                                            OUT_F16 if out_f16 else OUT_F32, _cur_stream()))
+        return outs
+
+    def lin_forward_host(self, name: str, x16: np.ndarray, t: int, out_f16: bool = False,
+                         out: np.ndarray | None = None) -> np.ndarray:
+        """Host-buffer forward: H2D of x, the linear, D2H of the result, synchronised."""
+        n, k, _ = self.lin_spec(name)
+        xb = np.ascontiguousarray(x16).view(np.uint16).ravel()
+        if xb.size != t * k:
+            raise W4a16Error(f"lin_forward_host {name}: x has {xb.size} elements, need {t}x{k}")
+        if out is None:
+            out = np.empty((t, n), np.float16 if out_f16 else np.float32)
+        self._ck(self._L.w4a16_lin_forward_host(self._h, name.encode(), xb.ctypes.data, out.ctypes.data, t,
+                                                OUT_F16 if out_f16 else OUT_F32))
+        return out
+
+    # -- graphs (ctx/graph.rs:4-85) -----------------------------------------------------------
+    def stream_ptr(self) -> int:
+        return int(self._L.w4a16_stream(self._h))
+
+    def capture_begin(self):
+        self._ck(self._L.w4a16_capture_begin(self._h))
+
+    def capture_end(self) -> int:
+        g = C.c_void_p()
+        self._ck(self._L.w4a16_capture_end(self._h, C.byref(g)))
+        return g.value
+
+    def graph_launch(self, g: int):
+        self._ck(self._L.w4a16_graph_launch(self._h, C.c_void_p(g)))
+
+    def graph_destroy(self, g: int):
+        self._ck(self._L.w4a16_graph_destroy(self._h, C.c_void_p(g)))
+
+    def graph_step_host(self, g: int, x_host: torch.Tensor, x_dev: torch.Tensor, y_dev: torch.Tensor,
+                        y_host: torch.Tensor):
+        """graphs.rs:202 shape: H2D of the step input, graph replay, D2H of the result, sync."""
+        self._ck(self._L.w4a16_graph_step_host(
+            self._h, C.c_void_p(g), x_host.data_ptr(), x_dev.data_ptr(), x_host.numel() * x_host.element_size(),
+            y_dev.data_ptr(), y_host.data_ptr(), y_host.numel() * y_host.element_size()))

@@ -1,0 +1,241 @@
+"""GPU parity of the resident layout, the dequantiser and the decode GEMV against the CPU oracle.
+All calls go through the C ABI (llm170_b200.W4a16Dec / Gptq4 are thin ctypes wrappers)."""
+import numpy as np
+import pytest
+import torch
+
+from llm170_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-3  # max-abs gate on the f32 output against the f32-accumulated lane oracle
+
+
+@pytest.fixture(scope="module")
+def dec():
+    from llm170_b200.w4a16_dec import W4a16Dec
+    d = W4a16Dec(0)
+    yield d
+    d.close()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def x_dev(x_u16):
+    return torch.from_numpy(x_u16.view(np.float16).copy()).cuda()
+
+
+@pytest.mark.parametrize("n,k,group", [(128, 256, 128), (64, 64, 32), (272, 1216, 32), (4096, 4096, 128)])
+def test_repack_roundtrip_and_dequant_bit_exact(dec, orc, n, k, group):
+    q, s = synth.make_linear(n, k, group, seed=n + k)
+    dec.upload_lin_g("t", q, s, n, k, group)
+    assert dec.lin_spec("t") == (n, k, group)
+    q2, s2 = dec.unpack_lin("t")
+    assert np.array_equal(q2.cpu().numpy().view(np.uint32), q)
+    assert np.array_equal(s2.cpu().numpy().view(np.uint16), s)
+    want = orc.dequant_w4a16(q, s, n, k, group)
+    got = dec.dequant_lin("t").cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))           # D1: bit-exact vs lane/cpu.rs
+    got16 = dec.dequant_lin("t", f16=True).cpu().numpy()
+    assert np.array_equal(got16.view(np.uint16), want.astype(np.float16).view(np.uint16))  # D2 = RN_f16(D1)
+
+
+def test_repack_kat_lcg_roundtrip(dec):
+    # same generator as the reference's round-trip test (crates/core/src/marlin.rs:107-122)
+    n, k = 128, 64
+    seed, M64 = 0x123456789ABCDEF0, (1 << 64) - 1
+    q = np.zeros(n * (k // 8), np.uint32)
+    for i in range(q.size):
+        seed = (seed * 6364136223846793005 + 1442695040888963407) & M64
+        q[i] = seed >> 32
+    dec.upload_lin_g("kat", q.reshape(n, k // 8), np.full((n, 2), 0x3C00, np.uint16), n, k, 32)
+    q2, _ = dec.unpack_lin("kat")
+    assert np.array_equal(q2.cpu().numpy().view(np.uint32).ravel(), q)
+
+
+def test_upload_contract_errors(dec):
+    from llm170_b200.w4a16_dec import W4a16Error
+    q, s = synth.make_linear(64, 128, 128, seed=1)
+    with pytest.raises(W4a16Error):      # length mismatch (upload.rs:27-33)
+        dec.upload_lin_g("bad", q[:-1], s, 64, 128, 128)
+    with pytest.raises(W4a16Error):      # unsupported group (gptq4.rs:60-70)
+        dec.upload_lin_g("bad", q, s, 64, 128, 64)
+    with pytest.raises(W4a16Error):      # n not a multiple of the tile
+        dec.upload_lin_g("bad", q[:8], s[:8], 8, 128, 128)
+    with pytest.raises(W4a16Error):
+        dec.lin_spec("bad")
+    with pytest.raises(W4a16Error):
+        dec.sk_single_dev("nope", torch.zeros(128, dtype=torch.float16, device="cuda"))
+
+
+def test_upload_replaces_by_name_and_counts_bytes(dec):
+    base = dec.weights_bytes()
+    q, s = synth.make_linear(64, 128, 128, seed=2)
+    dec.upload_lin_g("rep", q, s, 64, 128, 128)
+    assert dec.weights_bytes() == base + q.nbytes + s.nbytes
+    q2, s2 = synth.make_linear(128, 256, 128, seed=3)
+    dec.upload_lin_g("rep", q2, s2, 128, 256, 128)
+    assert dec.lin_spec("rep") == (128, 256, 128)
+    assert dec.weights_bytes() == base + q2.nbytes + s2.nbytes
+    dec.drop_lin("rep")
+    assert dec.weights_bytes() == base
+
+
+def test_bf16_scales_exact_or_rejected(dec, orc):
+    from llm170_b200.w4a16_dec import W4a16Error
+    n, k = 64, 128
+    q, _ = synth.make_linear(n, k, 32, seed=5)
+    s_bf = np.array([[(127 - ((r + g) % 5)) << 7 for g in range(k // 32)] for r in range(n)], np.uint16)
+    dec.upload_lin_g("bf", q, s_bf, n, k, 32, True)
+    want = orc.dequant_w4a16(q, s_bf, n, k, 32, scale_bf16=True)
+    assert np.array_equal(dec.dequant_lin("bf").cpu().numpy(), want)
+    s_bad = s_bf.copy()
+    s_bad[0, 0] = 0x0080  # 2^-126: not an f16 value
+    with pytest.raises(W4a16Error):
+        dec.upload_lin_g("bf2", q, s_bad, n, k, 32, True)
+
+
+@pytest.mark.parametrize("ksplit", [1, 2, 4])
+def test_decode_selfcheck_kat(dec, ksplit):
+    # crates/backend-gpu/src/rawcuda/w4a16_dec/probe.rs:1291-1426: scale = x = 1 -> y = sum(nib-8), bit-exact,
+    # for split-K 1/2/4 and for a two-segment launch.
+    n, k = 256, 512
+    i = np.arange(n * k // 8, dtype=np.uint64)
+    q = (((i * 0x9E3779B9) & 0xFFFFFFFF) ^ 0x12345678).astype(np.uint32).reshape(n, k // 8)
+    s = np.full((n, k // 128), 0x3C00, np.uint16)
+    nib = ((q[:, :, None] >> (4 * np.arange(8, dtype=np.uint32))) & 0xF).astype(np.int64) - 8
+    want = nib.reshape(n, -1).sum(axis=1).astype(np.float32)
+    dec.upload_lin_g("sc", q, s, n, k, 128)
+    x = torch.ones(k, dtype=torch.float16, device="cuda")
+    dec.set_tuning("gemv_ksplit", ksplit)
+    try:
+        y = dec.sk_single_dev("sc", x).cpu().numpy()[0]
+        assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
+        y1, y2 = dec.sk_multi_dev(["sc", "sc"], x)
+        assert np.array_equal(y1.cpu().numpy()[0], want) and np.array_equal(y2.cpu().numpy()[0], want)
+    finally:
+        dec.set_tuning("gemv_ksplit", 0)
+
+
+@pytest.mark.parametrize("t", [1, 3, 8])
+def test_pow2_kat_exact(dec, orc, t):
+    # crates/server/src/probes/w4a16/gpu/bench.rs:77-121: power-of-two scales and activations make
+    # every partial sum exact, so the GPU result must equal the f64 expectation bit for bit.
+    k, n = 256, 128
+    kk, nn = np.meshgrid(np.arange(k), np.arange(n))
+    nib = ((kk * 7 + nn * 3) % 16).astype(np.uint32)
+    q = np.bitwise_or.reduce(nib.reshape(n, k // 8, 8) << (4 * np.arange(8, dtype=np.uint32)), axis=2).astype(np.uint32)
+    s = np.array([[(15 - ((r + g) % 5)) << 10 for g in range(k // 128)] for r in range(n)], np.uint16)
+    i = np.arange(t * k)
+    x = ((15 - ((i // k + (i % k) // 8) % 4)) << 10).astype(np.uint16).reshape(t, k)
+    expect = (x.view(np.float16).astype(np.float64) @
+              ((nib.astype(np.float64) - 8) * np.repeat(s.view(np.float16).astype(np.float64), 128, axis=1)).T
+              ).astype(np.float32)
+    dec.upload_lin_g("p2", q, s, n, k, 128)
+    y = dec.lin_forward("p2", x_dev(x), t).cpu().numpy()
+    assert np.array_equal(y.view(np.uint32), expect.view(np.uint32))
+
+
+@pytest.mark.parametrize("n,k,group,t", [
+    (4096, 4096, 128, 1), (4096, 4096, 128, 8), (1024, 5120, 128, 2), (1536, 2048, 32, 4),
+    (2048, 768, 32, 1), (2048, 768, 32, 8), (48, 192, 32, 5), (16, 128, 128, 7), (5120, 17408, 128, 1),
+    (5120, 17408, 128, 8),
+])
+def test_gemv_vs_lane_oracle(dec, orc, n, k, group, t):
+    q, s = synth.make_linear(n, k, group, seed=100 + n % 97 + t)
+    x = synth.make_acts(t, k, seed=200 + t)
+    dec.upload_lin_g("g", q, s, n, k, group)
+    y = dec.lin_forward("g", x_dev(x), t)
+    rows = (0, n) if n * k * t <= (1 << 28) else (n // 2 - 256, n // 2 + 256)
+    want = orc.linear_lane(q, s, x, t, n, k, group, rows=rows)
+    got = y.cpu().numpy()[:, rows[0]:rows[1]]
+    err = np.abs(got.astype(np.float64) - want[:, rows[0]:rows[1]]).max()
+    assert err <= TOL, err
+    # f16 output is the f32 result rounded once
+    y16 = dec.lin_forward("g", x_dev(x), t, out_f16=True).cpu().numpy()
+    assert np.array_equal(y16.view(np.uint16), y.cpu().numpy().astype(np.float16).view(np.uint16))
+    dec.drop_lin("g")
+
+
+def test_config1_reference_cpu_case(dec, orc):
+    # BASELINE config 1 (M=16 is served by the GEMM path; here the GEMV covers it as two calls of 8)
+    n = k = 4096
+    q, s = synth.make_linear(n, k, 128, seed=0)
+    x = synth.make_acts(16, k, seed=0)
+    want = orc.linear_lane(q, s, x, 16, n, k, 128)
+    dec.upload_lin_g("c1", q, s, n, k, 128)
+    xd = x_dev(x)
+    got = torch.cat([dec.sk_single_dev("c1", xd[:8].contiguous(), t=8), dec.sk_single_dev("c1", xd[8:].contiguous(), t=8)])
+    assert np.abs(got.cpu().numpy() - want).max() <= TOL
+    dec.drop_lin("c1")
+
+
+def test_multi_segment_matches_single(dec):
+    k = 1024
+    segs = [("q_", 512), ("k_", 128), ("v_", 144)]
+    x = x_dev(synth.make_acts(4, k, seed=9))
+    for i, (nm, n) in enumerate(segs):
+        q, s = synth.make_linear(n, k, 128, seed=40 + i)
+        dec.upload_lin_g(nm, q, s, n, k, 128)
+    outs = dec.sk_multi_dev([nm for nm, _ in segs], x, t=4)
+    for (nm, _), o in zip(segs, outs):
+        assert torch.equal(o, dec.sk_single_dev(nm, x, t=4))
+
+
+def test_split_k_is_deterministic_and_scratch_is_clean(dec):
+    n, k = 512, 4096
+    q, s = synth.make_linear(n, k, 128, seed=77)
+    dec.upload_lin_g("det", q, s, n, k, 128)
+    x = x_dev(synth.make_acts(8, k, seed=78))
+    ref = dec.sk_single_dev("det", x, t=8).clone()
+    for ks in (2, 8, 16):
+        dec.set_tuning("gemv_ksplit", ks)
+        a = dec.sk_single_dev("det", x, t=8).clone()
+        b = dec.sk_single_dev("det", x, t=8).clone()
+        assert torch.equal(a, b)                      # same split -> same bits, tickets were reset
+        assert (a - ref).abs().max().item() < 1e-3
+    dec.set_tuning("gemv_ksplit", 0)
+
+
+def test_graph_capture_replay(dec):
+    n, k = 1024, 2048
+    q, s = synth.make_linear(n, k, 128, seed=31)
+    dec.upload_lin_g("gr", q, s, n, k, 128)
+    x = x_dev(synth.make_acts(1, k, seed=32))
+    eager = dec.sk_single_dev("gr", x).clone()         # also warms scratch
+    out = torch.zeros_like(eager)
+    torch.cuda.synchronize()
+    st = torch.cuda.ExternalStream(dec.stream_ptr())
+    with torch.cuda.stream(st):
+        dec.capture_begin()
+        dec.sk_single_dev("gr", x, out=out)
+        g = dec.capture_end()
+    for _ in range(3):
+        out.zero_()
+        torch.cuda.synchronize()
+        dec.graph_launch(g)
+        dec.sync()
+        assert torch.equal(out, eager)
+    dec.graph_destroy(g)
+
+
+def test_host_buffer_forward_and_gptq4_gate(dec, orc):
+    # crates/server/src/probes/w4a16/gates.rs:108-138: rows<=4 of a linear, x uniform [-1,1) -> f16,
+    # GPU f32 output against dot_row_w4a16_lane_group; the reference accepts <=1e-5 at t=1.
+    from llm170_b200.gptq4 import Gptq4
+    n, k, group = 64, 5120, 128
+    q, s = synth.make_linear(n, k, group, seed=55)
+    rng = np.random.default_rng(5)
+    x = (rng.random((8, k), dtype=np.float32) * 2 - 1).astype(np.float16).view(np.uint16)
+    want = orc.linear_lane(q, s, x, 8, n, k, group)
+    g4 = Gptq4.__new__(Gptq4)
+    g4.dec = dec
+    got8 = g4.gemm(x, 8, q, s, n, k, group)
+    got1 = g4.gemv(x[0], q, s, n, k, group)
+    assert np.abs(got8 - want).max() <= 1e-4
+    assert np.abs(got1[0] - want[0]).max() <= 1e-4
+    dec.upload_lin_g("hb", q, s, n, k, group)
+    y = dec.lin_forward_host("hb", x, 8)
+    assert np.array_equal(y, got8)
