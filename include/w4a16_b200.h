@@ -56,6 +56,11 @@ W4A16_API const char* w4a16_last_error(const w4a16_dec* dec);
 W4A16_API void* w4a16_stream(w4a16_dec* dec);
 /* CudaCtx::sync (crates/backend-gpu/src/rawcuda/ctx/mod.rs:407). */
 W4A16_API int w4a16_sync(w4a16_dec* dec);
+/* Synchronises the device and reports whether a kernel gave up on a bounded wait since the last
+ * check (0 = none). Every device-side wait in this library has an iteration limit and records a
+ * status word instead of hanging; the reference's only guard is its host watchdog
+ * (crates/diag/src/watchdog.rs:46-90). w4a16_sync() includes this check. */
+W4A16_API int w4a16_kernel_status(w4a16_dec* dec);
 /* Kernels launched by forward calls since creation: the launch counter the reference keeps in
  * HOST_LAUNCH_CALLS (crates/backend-gpu/src/rawcuda/ctx/mod.rs:10-11,311-315). */
 W4A16_API unsigned long long w4a16_launch_count(w4a16_dec* dec);

@@ -247,7 +247,16 @@ int w4a16_dec_new(int device, w4a16_dec** out) {
         e = cudaMalloc(&d.err_flag, sizeof(int));
     }
     if (e == cudaSuccess) {
+        e = cudaMalloc(&d.gemm_status, sizeof(int));
+    }
+    if (e == cudaSuccess) {
+        e = cudaMemset(d.gemm_status, 0, sizeof(int));
+    }
+    if (e == cudaSuccess) {
         e = w4::gemv_init_device();
+    }
+    if (e == cudaSuccess) {
+        e = w4::gemm_init_device();
     }
     if (e != cudaSuccess) {
         g_create_error = std::string("w4a16_dec_new: ") + cudaGetErrorString(e);
@@ -283,6 +292,9 @@ void w4a16_dec_free(w4a16_dec* dec) {
     if (d.err_flag) {
         cudaFree(d.err_flag);
     }
+    if (d.gemm_status) {
+        cudaFree(d.gemm_status);
+    }
     if (d.xh) {
         cudaFree(d.xh);
     }
@@ -303,7 +315,25 @@ void* w4a16_stream(w4a16_dec* dec) { return dec ? (void*)dec->d.stream : nullptr
 
 int w4a16_sync(w4a16_dec* dec) {
     cudaError_t e = cudaStreamSynchronize(dec->d.stream);
-    return e == cudaSuccess ? 0 : dec->d.cuda_fail("sync", e);
+    if (e != cudaSuccess) {
+        return dec->d.cuda_fail("sync", e);
+    }
+    return w4a16_kernel_status(dec);
+}
+
+int w4a16_kernel_status(w4a16_dec* dec) {
+    Dec& d = dec->d;
+    int st = 0;
+    cudaError_t e = cudaMemcpy(&st, d.gemm_status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) {
+        return d.cuda_fail("read kernel status", e);
+    }
+    if (st != 0) {
+        cudaMemset(d.gemm_status, 0, sizeof(int));
+        return d.fail("w4a16 gemm: a pipeline wait expired (role %d, k-block %d); results are invalid", st >> 16,
+                      st & 0xFFFF);
+    }
+    return 0;
 }
 
 unsigned long long w4a16_launch_count(w4a16_dec* dec) { return dec->d.launches; }

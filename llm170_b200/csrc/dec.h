@@ -26,6 +26,7 @@ struct Dec {
     unsigned* counters = nullptr;
     size_t counters_cap = 0;
     int* err_flag = nullptr;
+    int* gemm_status = nullptr;  // device word: first expired wait of a tensor-core GEMM (0 = none)
     // device staging for the host-buffer entry points
     void* xh = nullptr;
     size_t xh_cap = 0;

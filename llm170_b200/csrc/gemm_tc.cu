@@ -1,10 +1,462 @@
-// Prefill W4A16 GEMM (tensor cores). Placeholder translation unit until the tcgen05 kernel lands.
+// Prefill W4A16 GEMM on the 5th-generation tensor cores:  y[m][n] = sum_k x[m][k] * f16((q[n][k]-8)*s[n][k/g]).
+//
+// Takes the place of the reference's prefill GEMMs (vendored Marlin instantiations launched from
+// crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/marlin.rs:94-213, and the hand-written
+// crates/backend-gpu/src/rawcuda/assets/moe.cu:1139-1587 / gptq4.cu:984-1147), which are mma.sync kernels.
+// Like them it multiplies the dequantised weight ROUNDED ONCE TO F16 (hmul2 of the exact integer and
+// the f16 scale; the reference's own model of this is crates/server/src/probes/w4a16/gpu/bench.rs:240)
+// and accumulates in f32.
+//
+// One CTA computes a 128 (tokens) x 256 (weight rows) tile:
+//   warp 0      producer: TMA-loads the f16 activation tile (128 x 64, 128B swizzle) and bulk-copies the
+//               raw int4 tiles (16 x 512 B of the T64 layout) of each 64-wide k-block into a 4-stage ring
+//   warps 2-9   expand int4 -> f16 into the K-major 128B-swizzled B operand of the stage (one 16-byte
+//               chunk = 8 consecutive k of one weight row), then signal the MMA warp
+//   warp 1      one lane issues 4 x tcgen05.mma (M128 N256 K16, f16 x f16 -> f32 in TMEM) per k-block and
+//               commits the stage back to the producer
+//   warps 2-5   epilogue: tcgen05.ld the 128 x 256 f32 accumulator, convert, store y
+// Every mbarrier wait is bounded: on expiry the kernel records a status code, all roles fall through to
+// the common exit, TMEM is released, and the host reports an error instead of hanging.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "../../include/w4a16_b200.h"
 #include "dec.h"
 
 namespace w4 {
 
-int Dec::gemm(const Lin*, const void*, void*, int t, int, cudaStream_t) {
-    return fail("w4a16 gemm: t=%d > 8 is not available in this build", t);
+namespace {
+
+constexpr int BM = 128;           // tokens per tile (UMMA M)
+constexpr int BN = 256;           // weight rows per tile (UMMA N)
+constexpr int BK = TILE_K;        // 64 k per stage = one 128-byte swizzle row of f16
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;          // 16 KB
+constexpr int RAW_BYTES = BN * BK / 2;        // 8 KB
+constexpr int B_BYTES = BN * BK * 2;          // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + RAW_BYTES + B_BYTES;
+constexpr int NUM_DQ_WARPS = 8;
+constexpr int NUM_THREADS = (2 + NUM_DQ_WARPS) * 32;
+constexpr int TMEM_COLS = 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int GROUP_M = 8;        // m-tiles per rasterisation group (L2 reuse of the weight tiles)
+
+struct GemmArgs {
+    const uint32_t* qt;
+    const uint32_t* st;  // scale pairs
+    void* out;
+    int m, n, k;
+    int out_f16;
+    int m_tiles, n_tiles;
+    int* status;  // 0 = ok; otherwise code<<16 | detail of the first wait that expired
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait. Returns false if it gave up (2^31 cycles, about a second) or another role already did.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int code) {
+    if (mbar_try(bar, parity)) {
+        return true;
+    }
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    while (!mbar_try(bar, parity)) {
+        if ((++spins & 0x3FF) == 0) {
+            if (*abort_flag) {
+                return false;
+            }
+            if (clock64() - t0 > (1ll << 31)) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+// K-major, 128B-swizzled operand: 8-row groups are 1024 B apart (SBO), LBO unused, descriptor version 1.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accum) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accum)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t hmul2u(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+// packed word -> a[0]=(r0;k,k+1) a[1]=(r1;k,k+1) a[2]=(r0;k+2,k+3) a[3]=(r1;k+2,k+3), each exactly nibble-8
+__device__ __forceinline__ void dequant_word(uint32_t w, uint32_t (&a)[4]) {
+    const uint32_t MAGIC = 0x64006400u, SUB = 0x64086408u, MUL = 0x2c002c00u, ADD = 0xd480d480u;
+    const uint32_t w8 = w >> 8;
+    const uint32_t lo0 = lop3_and_or(w, 0x000f000fu, MAGIC), hi0 = lop3_and_or(w, 0x00f000f0u, MAGIC);
+    const uint32_t lo1 = lop3_and_or(w8, 0x000f000fu, MAGIC), hi1 = lop3_and_or(w8, 0x00f000f0u, MAGIC);
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(a[0]) : "r"(lo0), "r"(SUB));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(a[1]) : "r"(hi0), "r"(MUL), "r"(ADD));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(a[2]) : "r"(lo1), "r"(SUB));
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(a[3]) : "r"(hi1), "r"(MUL), "r"(ADD));
+}
+
+template <int GROUP>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+    unsigned char* base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
+    // stage s: [A 16K][B f16 32K][raw 8K]; A and B bases stay 1024-byte aligned
+    auto a_addr = [&](int s) { return base + (uint32_t)s * STAGE_BYTES; };
+    auto b_addr = [&](int s) { return base + (uint32_t)s * STAGE_BYTES + A_BYTES; };
+    auto raw_addr = [&](int s) { return base + (uint32_t)s * STAGE_BYTES + A_BYTES + B_BYTES; };
+    const uint32_t bars = base + STAGES * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto bready_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto empty_bar = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+    const uint32_t accum_bar = bars + 8u * (3 * STAGES);
+
+    // tile of this CTA (groups of GROUP_M m-tiles walk the n-tiles together)
+    int m_tile, n_tile;
+    {
+        const int tile = blockIdx.x;
+        const int per_group = GROUP_M * a.n_tiles;
+        const int grp = tile / per_group;
+        const int first_m = grp * GROUP_M;
+        const int gsz = min(GROUP_M, a.m_tiles - first_m);
+        const int rem = tile - grp * per_group;
+        m_tile = first_m + rem % gsz;
+        n_tile = rem / gsz;
+    }
+    const int m0 = m_tile * BM, n0 = n_tile * BN;
+    const int nkb = a.k / BK;
+    const int rb0 = n0 / TILE_ROWS;
+    const int nrbv = min(BN, a.n - n0) / TILE_ROWS;  // valid 16-row blocks in this tile
+
+    if (threadIdx.x == 0) {
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(bready_bar(s), NUM_DQ_WARPS);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem_base)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem_base;
+    volatile int* abort_flag = &s_abort;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            for (int it = 0; it < nkb; ++it) {
+                const int s = it % STAGES, r = it / STAGES;
+                if (!mbar_wait(empty_bar(s), (r & 1) ^ 1, abort_flag, a.status, (1 << 16) | it)) {
+                    break;
+                }
+                mbar_expect_tx(full_bar(s), A_BYTES + nrbv * (TILE_WORDS * 4));
+                tma_load_2d(a_addr(s), &tmap_x, it * BK, m0, full_bar(s));
+                for (int j = 0; j < nrbv; ++j) {
+                    bulk_load(raw_addr(s) + j * (TILE_WORDS * 4),
+                              a.qt + ((size_t)(rb0 + j) * nkb + it) * TILE_WORDS, TILE_WORDS * 4, full_bar(s));
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (int it = 0; it < nkb && ok; ++it) {
+                const int s = it % STAGES, r = it / STAGES;
+                ok = mbar_wait(full_bar(s), r & 1, abort_flag, a.status, (2 << 16) | it) &&
+                     mbar_wait(bready_bar(s), r & 1, abort_flag, a.status, (3 << 16) | it);
+                if (!ok) {
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint64_t da = umma_desc(a_addr(s)), db = umma_desc(b_addr(s));
+#pragma unroll
+                for (int j = 0; j < BK / 16; ++j) {
+                    umma_f16(tmem, da + 2 * j, db + 2 * j, IDESC, (it > 0 || j > 0) ? 1u : 0u);
+                }
+                umma_commit(empty_bar(s));
+            }
+            if (ok) {
+                umma_commit(accum_bar);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ dequantise, then epilogue
+        const int dw = warp - 2;
+        // bank-conflict-free assignment of the 32 (g,t) slots of a tile to lanes (reads and writes)
+        const int ph = lane >> 3, jj = lane & 7;
+        const int t = jj & 3, g = 2 * ((t + ph) & 3) + (jj >> 2);
+        const int ng = a.k / GROUP;
+        bool ok = true;
+        for (int it = 0; it < nkb && ok; ++it) {
+            const int s = it % STAGES, r = it / STAGES;
+            uint32_t sc[2][2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int rbi = dw + NUM_DQ_WARPS * j;
+                sc[j][0] = sc[j][1] = 0;
+                if (rbi < nrbv) {
+                    const uint32_t* sp = a.st + ((size_t)(rb0 + rbi) * ng) * 8 + g;
+                    if (GROUP >= BK) {
+                        sc[j][0] = sc[j][1] = __ldg(sp + (size_t)(it * BK / GROUP) * 8);
+                    } else {
+                        sc[j][0] = __ldg(sp + (size_t)(it * 2) * 8);
+                        sc[j][1] = __ldg(sp + (size_t)(it * 2 + 1) * 8);
+                    }
+                }
+            }
+            ok = mbar_wait(full_bar(s), r & 1, abort_flag, a.status, (4 << 16) | it);
+            if (!ok) {
+                break;
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int rbi = dw + NUM_DQ_WARPS * j;
+                if (rbi < nrbv) {
+                    uint4 raw;
+                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                                 : "r"(raw_addr(s) + rbi * (TILE_WORDS * 4) + (4 * g + t) * 16));
+                    const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+                    const uint32_t row_off = b_addr(s) + (uint32_t)(rbi * TILE_ROWS + g) * 128u;
+#pragma unroll
+                    for (int p = 0; p < 2; ++p) {
+                        uint32_t f0[4], f1[4];
+                        dequant_word(rw[2 * p], f0);
+                        dequant_word(rw[2 * p + 1], f1);
+                        const uint32_t s2 = sc[j][p];
+                        const uint32_t s_r0 = __byte_perm(s2, s2, 0x1010);  // (s[r0], s[r0])
+                        const uint32_t s_r1 = __byte_perm(s2, s2, 0x3232);  // (s[r1], s[r1])
+                        const uint32_t chunk = (uint32_t)(((4 * p + t) ^ g) << 4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row_off + chunk),
+                                     "r"(hmul2u(f0[0], s_r0)), "r"(hmul2u(f0[2], s_r0)), "r"(hmul2u(f1[0], s_r0)),
+                                     "r"(hmul2u(f1[2], s_r0))
+                                     : "memory");
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row_off + 8u * 128u + chunk),
+                                     "r"(hmul2u(f0[1], s_r1)), "r"(hmul2u(f0[3], s_r1)), "r"(hmul2u(f1[1], s_r1)),
+                                     "r"(hmul2u(f1[3], s_r1))
+                                     : "memory");
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(bready_bar(s));
+            }
+        }
+        if (warp < 6) {
+            // epilogue: this warp may touch TMEM lanes 32*(warp%4) .. +31
+            if (ok) {
+                ok = mbar_wait(accum_bar, 0, abort_flag, a.status, (5 << 16));
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const int quad = warp & 3;
+                const int row = m0 + quad * 32 + lane;
+                const int ncols = min(BN, a.n - n0);
+                for (int c0 = 0; c0 < ncols; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+                    if (row < a.m) {
+                        if (a.out_f16) {
+                            __half* o = reinterpret_cast<__half*>(a.out) + (size_t)row * a.n + n0 + c0;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                if (c0 + i < ncols) {
+                                    uint4 pk;
+                                    __half2 h;
+                                    h = __floats2half2_rn(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                                    pk.x = *reinterpret_cast<uint32_t*>(&h);
+                                    h = __floats2half2_rn(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                                    pk.y = *reinterpret_cast<uint32_t*>(&h);
+                                    h = __floats2half2_rn(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                                    pk.z = *reinterpret_cast<uint32_t*>(&h);
+                                    h = __floats2half2_rn(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                                    pk.w = *reinterpret_cast<uint32_t*>(&h);
+                                    *reinterpret_cast<uint4*>(o + i) = pk;
+                                }
+                            }
+                        } else {
+                            float* o = reinterpret_cast<float*>(a.out) + (size_t)row * a.n + n0 + c0;
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) {
+                                if (c0 + i < ncols) {
+                                    *reinterpret_cast<uint4*>(o + i) = make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+    (void)base_ptr;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess) {
+            fn = (EncodeTiledFn)p;
+        }
+    }
+    return fn;
+}
+
+}  // namespace
+
+cudaError_t gemm_init_device() {
+    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SMEM_BYTES);
+    if (e != cudaSuccess) {
+        return e;
+    }
+    return cudaFuncSetAttribute(gemm_w4a16_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+}
+
+int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaStream_t st) {
+    if (((uintptr_t)x & 15) != 0 || ((uintptr_t)dst & 15) != 0) {
+        return fail("w4a16 gemm: x and dst must be 16-byte aligned");
+    }
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) {
+        return fail("w4a16 gemm: cuTensorMapEncodeTiled is not available from the driver");
+    }
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)l->k, (cuuint64_t)t};
+    const cuuint64_t strides[1] = {(cuuint64_t)l->k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) {
+        return fail("w4a16 gemm: cuTensorMapEncodeTiled failed (%d)", (int)cr);
+    }
+    GemmArgs a;
+    a.qt = l->qt;
+    a.st = (const uint32_t*)l->st;
+    a.out = dst;
+    a.m = t;
+    a.n = l->n;
+    a.k = l->k;
+    a.out_f16 = out_kind == W4A16_OUT_F16;
+    a.m_tiles = (t + BM - 1) / BM;
+    a.n_tiles = (l->n + BN - 1) / BN;
+    a.status = gemm_status;
+    const int grid = a.m_tiles * a.n_tiles;
+    if (l->group == 128) {
+        gemm_w4a16_tc_kernel<128><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map, a);
+    } else {
+        gemm_w4a16_tc_kernel<32><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map, a);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        return cuda_fail("launch gemm", e);
+    }
+    launches++;
+    return 0;
 }
 
 }  // namespace w4

@@ -55,4 +55,8 @@ cudaError_t launch_gemv(const GemvArgs& a, int grid_x, cudaStream_t st);
 // Raises the dynamic shared-memory limit of the GEMV kernels on the current device.
 cudaError_t gemv_init_device();
 
+// ---- gemm_tc.cu ------------------------------------------------------------------------------
+// Raises the dynamic shared-memory limit of the tensor-core GEMM kernels on the current device.
+cudaError_t gemm_init_device();
+
 }  // namespace w4

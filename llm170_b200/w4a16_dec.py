@@ -23,7 +23,11 @@ class W4a16Error(RuntimeError):
 
 
 def _cur_stream() -> int:
-    return int(torch.cuda.current_stream().cuda_stream)
+    """torch's current stream as a cudaStream_t.  torch's default stream has the handle 0, which the
+    C ABI reads as "use the decoder's own stream"; 1 is cudaStreamLegacy, the explicit name of that
+    same default stream, so work stays ordered with the caller's torch ops."""
+    h = int(torch.cuda.current_stream().cuda_stream)
+    return h if h != 0 else 1
 
 
 class W4a16Dec:
@@ -69,6 +73,10 @@ class W4a16Dec:
 
     def sync(self):
         self._ck(self._L.w4a16_sync(self._h))
+
+    def kernel_status(self):
+        """Raises if a kernel gave up on a bounded wait since the last check."""
+        self._ck(self._L.w4a16_kernel_status(self._h))
 
     # -- weights ----------------------------------------------------------------------------
     def upload_lin(self, name: str, q: np.ndarray, s: np.ndarray, n: int, k: int):

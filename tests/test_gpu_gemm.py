@@ -1,0 +1,85 @@
+"""GPU parity of the tensor-core prefill GEMM (t > 8) through the C ABI.
+
+Three references:  (1) exact-arithmetic known-answer tests of the reference (bit equality);
+(2) the value the kernel is specified to compute -- x times the dequantised weight rounded once
+to f16, accumulated in f32 -- as a plain torch fp32 matmul (tolerance 1e-4 relative to the output
+scale); (3) the f32-accumulated CPU lane oracle with the 2e-3 max-abs gate."""
+import numpy as np
+import pytest
+import torch
+
+from llm170_b200 import synth
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+@pytest.fixture(scope="module")
+def dec():
+    from llm170_b200.w4a16_dec import W4a16Dec
+    torch.backends.cuda.matmul.allow_tf32 = False
+    d = W4a16Dec(0)
+    yield d
+    d.close()
+
+
+def x_dev(x_u16):
+    return torch.from_numpy(x_u16.view(np.float16).copy()).cuda()
+
+
+def pow2_case(t, k, n, group):
+    kk, nn = np.meshgrid(np.arange(k), np.arange(n))
+    nib = ((kk * 7 + nn * 3) % 16).astype(np.uint32)
+    q = np.bitwise_or.reduce(nib.reshape(n, k // 8, 8) << (4 * np.arange(8, dtype=np.uint32)), axis=2).astype(np.uint32)
+    s = np.array([[(15 - ((r + g) % 5)) << 10 for g in range(k // group)] for r in range(n)], np.uint16)
+    i = np.arange(t * k)
+    x = ((15 - ((i // k + (i % k) // 8) % 4)) << 10).astype(np.uint16).reshape(t, k)
+    w = (nib.astype(np.float64) - 8) * np.repeat(s.view(np.float16).astype(np.float64), group, axis=1)
+    return q, s, x, (x.view(np.float16).astype(np.float64) @ w.T).astype(np.float32)
+
+
+@pytest.mark.parametrize("t,k,n,group", [(16, 256, 128, 128), (64, 512, 256, 128), (300, 256, 272, 128),
+                                         (33, 128, 64, 32), (129, 768, 512, 32)])
+def test_pow2_kat_exact(dec, t, k, n, group):
+    # crates/server/src/probes/w4a16/gpu/bench.rs:77-166: power-of-two scales/activations -> exact sums
+    q, s, x, expect = pow2_case(t, k, n, group)
+    dec.upload_lin_g("p2", q, s, n, k, group)
+    y = dec.lin_forward("p2", x_dev(x), t)
+    dec.sync()
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), expect.view(np.uint32))
+
+
+@pytest.mark.parametrize("n,k,group,t", [(256, 128, 128, 9), (512, 1024, 128, 130), (1536, 2048, 32, 257),
+                                         (2048, 768, 32, 64), (4096, 4096, 128, 16), (7168, 5120, 128, 512)])
+def test_gemm_vs_f16_dequant_model_and_lane_oracle(dec, orc, n, k, group, t):
+    q, s = synth.make_linear(n, k, group, seed=300 + t)
+    x = synth.make_acts(t, k, seed=400 + t, scale=1.0 / np.sqrt(k))
+    dec.upload_lin_g("g", q, s, n, k, group)
+    xd = x_dev(x)
+    y = dec.lin_forward("g", xd, t)
+    dec.sync()
+    w16 = dec.dequant_lin("g", f16=True)
+    ref = xd.float() @ w16.float().T                       # plain torch fp32 reference of the specified op
+    scale = ref.abs().max().item()
+    assert (y - ref).abs().max().item() <= 1e-4 * scale + 1e-6
+    rows = (0, min(n, 64))
+    want = orc.linear_lane(q, s, x, t, n, k, group, rows=rows)
+    got = y.cpu().numpy()[:, rows[0]:rows[1]]
+    assert np.abs(got - want[:, rows[0]:rows[1]]).max() <= TOL
+    y16 = dec.lin_forward("g", xd, t, out_f16=True)
+    dec.sync()
+    assert torch.equal(y16, y.to(torch.float16))
+    dec.drop_lin("g")
+
+
+def test_gemm_and_gemv_agree_on_the_same_weights(dec):
+    # both kernels read the one resident copy; they differ only by the f16 rounding of the weight
+    n, k = 1024, 2048
+    q, s = synth.make_linear(n, k, 128, seed=12)
+    dec.upload_lin_g("both", q, s, n, k, 128)
+    x = x_dev(synth.make_acts(16, k, seed=13, scale=1 / np.sqrt(k)))
+    y_gemm = dec.lin_forward("both", x, 16)
+    y_gemv = torch.cat([dec.sk_single_dev("both", x[:8].contiguous(), t=8),
+                        dec.sk_single_dev("both", x[8:].contiguous(), t=8)])
+    dec.sync()
+    assert (y_gemm - y_gemv).abs().max().item() <= 2e-4
