@@ -171,6 +171,9 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape / M sweep extras")
+    ap.add_argument("--case", default=None,
+                    help="run ONE small case instead of the benchmark, for profilers: "
+                         "gemv:<linear>:<m> or gemm:<linear>:<m>, e.g. gemm:gate_up:4096 (prints its device time)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -195,6 +198,31 @@ def main():
     peaks, peak_kind = load_peaks()
 
     dec = W4a16Dec(local_rank)
+    if args.case:
+        kind, nm, m = args.case.split(":")
+        m = int(m)
+        k, n = synth.DENSE_27B[nm]
+        q, s = synth.make_linear_cuda(n, k, 128, seed=7, device=device)
+        dec.upload_lin_g_dev("case", q, s, n, k, 128)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(1)
+        xg = (torch.randn((m, k), generator=gen, device=device) / (k ** 0.5 if kind == "gemm" else 1.0)).to(torch.float16)
+        yg = torch.empty((m, n), device=device, dtype=torch.float16)
+        fn = (lambda: dec.lin_forward("case", xg, m, dst=yg, out_f16=True)) if kind == "gemm" else \
+             (lambda: dec.sk_single_dev("case", xg, out=yg, t=m, out_f16=True))
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        e1.synchronize()
+        dec.kernel_status()
+        print(json.dumps({"case": args.case, "launches": args.steps + 1,
+                          "us_per_launch": e0.elapsed_time(e1) * 1e3 / args.steps}))
+        dec.close()
+        return
     L = args.layers
     shapes = layer_shapes(world)
     t_build = time.time()
@@ -347,6 +375,39 @@ def main():
                     per[nm] = {"us": round(us, 3), "GBps": round(b / us / 1e3, 1),
                                "frac_measured_hbm": round(b / us / 1e3 / peaks["hbm_gbs"], 4)}
                 extras[f"M{m}"] = per
+
+    # ---- extras: prefill GEMM sweep (tensor-core kernel), TFLOP/s per shape, rotating over 8 layers ----
+    if world == 1 and not args.no_extras:
+        pre = {}
+        with torch.cuda.stream(st):
+            for m in (512, 1024, 4096):
+                per = {}
+                for nm in LAYER_ORDER:
+                    k, n, _ = shapes[nm]
+                    xg = (torch.randn((m, k), generator=g, device=device, dtype=torch.float32) / (k ** 0.5)
+                          ).to(torch.float16)
+                    yg = torch.empty((m, n), device=device, dtype=torch.float16)
+                    nl = min(L, 8)
+                    for li in range(nl):
+                        dec.lin_forward(f"l{li}.{nm}", xg, m, dst=yg, out_f16=True)
+                    st.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    reps = 3
+                    e0.record(st)
+                    for _ in range(reps):
+                        for li in range(nl):
+                            dec.lin_forward(f"l{li}.{nm}", xg, m, dst=yg, out_f16=True)
+                    e1.record(st)
+                    e1.synchronize()
+                    us = e0.elapsed_time(e1) * 1e3 / (reps * nl)
+                    tf = synth.gemm_flops(n, k, m) / us / 1e6
+                    per[nm] = {"us": round(us, 2), "TFLOPs": round(tf, 1),
+                               "frac_measured_bf16": round(tf / peaks["bf16_tflops"], 4),
+                               "frac_nominal_2250": round(tf / 2250.0, 4)}
+                    del xg, yg
+                pre[f"M{m}"] = per
+        dec.kernel_status()
+        extras["prefill"] = pre
 
     # ---- CPU baseline (rank 0, N=1): the oracle on a bounded sample ----------------------------------
     cpu_baseline = None
