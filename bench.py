@@ -171,6 +171,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape / M sweep extras")
+    ap.add_argument("--tune", action="append", default=[], help="library knob key=value (repeatable)")
     ap.add_argument("--case", default=None,
                     help="run ONE small case instead of the benchmark, for profilers: "
                          "gemv:<linear>:<m> or gemm:<linear>:<m>, e.g. gemm:gate_up:4096 (prints its device time)")
@@ -198,6 +199,9 @@ def main():
     peaks, peak_kind = load_peaks()
 
     dec = W4a16Dec(local_rank)
+    for kv in args.tune:
+        key, val = kv.split("=")
+        dec.set_tuning(key, int(val))
     if args.case:
         kind, nm, m = args.case.split(":")
         m = int(m)

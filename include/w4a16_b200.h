@@ -65,7 +65,11 @@ W4A16_API int w4a16_kernel_status(w4a16_dec* dec);
  * HOST_LAUNCH_CALLS (crates/backend-gpu/src/rawcuda/ctx/mod.rs:10-11,311-315). */
 W4A16_API unsigned long long w4a16_launch_count(w4a16_dec* dec);
 /* Kernel-selection knobs, the analogue of the reference's LLM170_* environment flags
- * (crates/diag/src/flag.rs:3-27). Keys: "gemv_ctas_per_sm", "gemv_ksplit" (0 = automatic). */
+ * (crates/diag/src/flag.rs:3-27). Keys: "gemv_ctas_per_sm", "gemv_ksplit" (0 = automatic),
+ * "gemv_stages" (2 KB weight chunks in flight per warp, 2..4),
+ * "gemv_subnormal" (1 = default arithmetic, 0 = exact nibble-8 operands), "pdl" (1 = default: kernels are
+ * launched with programmatic stream serialization and prefetch weights while the previous kernel of
+ * the stream drains; 0 = ordinary launches). */
 W4A16_API int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value);
 
 /* ---- weights ----------------------------------------------------------------------------- */

@@ -166,18 +166,26 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
     a.x = (const uint16_t*)x;
     const int grid_x = gemv_plan_ctas(a);
     int ks = tune_gemv_ksplit > 0 ? tune_gemv_ksplit
-                                  : gemv_pick_ksplit(grid_x, a.k, a.group, t, sm_count, tune_gemv_ctas_per_sm);
+                                  : gemv_pick_ksplit(grid_x, a.k, a.group, t, sm_count, tune_gemv_ctas_per_sm,
+                                                     tune_gemv_stages);
     const int unit = a.group > TILE_K ? a.group : TILE_K;
     if (ks > a.k / unit) {
         ks = a.k / unit;
     }
-    while (gemv_smem_bytes(a.k, a.group, t, ks) > 96 * 1024 && ks < a.k / unit) {
+    while (gemv_smem_bytes(a.k, a.group, t, ks, tune_gemv_stages) > 112 * 1024 && ks < a.k / unit) {
         ++ks;
     }
-    if (gemv_smem_bytes(a.k, a.group, t, ks) > 96 * 1024) {
+    if (gemv_smem_bytes(a.k, a.group, t, ks, tune_gemv_stages) > 112 * 1024) {
         return fail("w4a16 gemv: k=%d too large for t=%d", a.k, t);
     }
+    if (((uintptr_t)x & 15) != 0) {
+        return fail("w4a16 gemv: x must be 16-byte aligned");
+    }
     a.ksplit = ks;
+    a.subnormal = tune_gemv_subnormal;
+    a.pdl = tune_pdl;
+    a.ring_stages = tune_gemv_stages;
+    a.status = gemm_status;
     if (int rc = ensure_scratch(gemv_part_floats(grid_x, ks), grid_x, st)) {
         return rc;
     }
@@ -330,7 +338,7 @@ int w4a16_kernel_status(w4a16_dec* dec) {
     }
     if (st != 0) {
         cudaMemset(d.gemm_status, 0, sizeof(int));
-        return d.fail("w4a16 gemm: a pipeline wait expired (role %d, k-block %d); results are invalid", st >> 16,
+        return d.fail("w4a16: a bounded pipeline wait expired (role %d, step %d); results are invalid", st >> 16,
                       st & 0xFFFF);
     }
     return 0;
@@ -345,6 +353,21 @@ int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
             return d.fail("w4a16 tuning: gemv_ctas_per_sm must be 1..32");
         }
         d.tune_gemv_ctas_per_sm = value;
+        return 0;
+    }
+    if (!strcmp(key, "gemv_stages")) {
+        if (value < 2 || value > 4) {
+            return d.fail("w4a16 tuning: gemv_stages must be 2..4");
+        }
+        d.tune_gemv_stages = value;
+        return 0;
+    }
+    if (!strcmp(key, "pdl")) {
+        d.tune_pdl = value != 0;
+        return 0;
+    }
+    if (!strcmp(key, "gemv_subnormal")) {
+        d.tune_gemv_subnormal = value != 0;
         return 0;
     }
     if (!strcmp(key, "gemv_ksplit")) {

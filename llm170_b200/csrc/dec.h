@@ -26,14 +26,17 @@ struct Dec {
     unsigned* counters = nullptr;
     size_t counters_cap = 0;
     int* err_flag = nullptr;
-    int* gemm_status = nullptr;  // device word: first expired wait of a tensor-core GEMM (0 = none)
+    int* gemm_status = nullptr;  // device word: first bounded wait that expired in any kernel (0 = none)
     // device staging for the host-buffer entry points
     void* xh = nullptr;
     size_t xh_cap = 0;
     void* yh = nullptr;
     size_t yh_cap = 0;
     // knobs
-    int tune_gemv_ctas_per_sm = 4;
+    int tune_gemv_stages = 2;
+    int tune_gemv_ctas_per_sm = 5;   // residency cap assumed by the split-K cost model (register-limited)
+    int tune_gemv_subnormal = 1;
+    int tune_pdl = 1;
     int tune_gemv_ksplit = 0;
     // kernels launched by forward calls since creation
     unsigned long long launches = 0;

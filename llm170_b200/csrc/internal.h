@@ -43,13 +43,17 @@ struct GemvArgs {
     const uint16_t* x;  // f16 [m][k]
     float* part;        // [ksplit][grid_x][GEMV_WARPS*16][GEMV_MAX_M] partial sums (ksplit > 1)
     unsigned* counters; // [grid_x], zero on entry, left zero on exit
+    int subnormal;      // 1: feed raw nibbles as f16 subnormals and fix up per group (default); 0: exact nibble-8
+    int ring_stages;    // 2 KB chunks in flight per warp (2..4)
+    int pdl;            // 1: launch with programmatic stream serialization (overlaps the previous kernel's tail)
+    int* status;        // device word that records the first bounded wait that expired
 };
 
 // Total CTAs along x for the segments in `a` (fills seg[].cta0).
 int gemv_plan_ctas(GemvArgs& a);
 // Smallest and preferred split-K for a plan (see gemv.cu).
-int gemv_pick_ksplit(int grid_x, int k, int group, int m, int sm_count, int target_ctas_per_sm);
-size_t gemv_smem_bytes(int k, int group, int m, int ksplit);
+int gemv_pick_ksplit(int grid_x, int k, int group, int m, int sm_count, int max_ctas_per_sm, int stages);
+size_t gemv_smem_bytes(int k, int group, int m, int ksplit, int stages);
 size_t gemv_part_floats(int grid_x, int ksplit);
 cudaError_t launch_gemv(const GemvArgs& a, int grid_x, cudaStream_t st);
 // Raises the dynamic shared-memory limit of the GEMV kernels on the current device.

@@ -97,8 +97,9 @@ def test_bf16_scales_exact_or_rejected(dec, orc):
         dec.upload_lin_g("bf2", q, s_bad, n, k, 32, True)
 
 
+@pytest.mark.parametrize("subn", [1, 0])
 @pytest.mark.parametrize("ksplit", [1, 2, 4])
-def test_decode_selfcheck_kat(dec, ksplit):
+def test_decode_selfcheck_kat(dec, ksplit, subn):
     # crates/backend-gpu/src/rawcuda/w4a16_dec/probe.rs:1291-1426: scale = x = 1 -> y = sum(nib-8), bit-exact,
     # for split-K 1/2/4 and for a two-segment launch.
     n, k = 256, 512
@@ -110,6 +111,7 @@ def test_decode_selfcheck_kat(dec, ksplit):
     dec.upload_lin_g("sc", q, s, n, k, 128)
     x = torch.ones(k, dtype=torch.float16, device="cuda")
     dec.set_tuning("gemv_ksplit", ksplit)
+    dec.set_tuning("gemv_subnormal", subn)
     try:
         y = dec.sk_single_dev("sc", x).cpu().numpy()[0]
         assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
@@ -117,10 +119,12 @@ def test_decode_selfcheck_kat(dec, ksplit):
         assert np.array_equal(y1.cpu().numpy()[0], want) and np.array_equal(y2.cpu().numpy()[0], want)
     finally:
         dec.set_tuning("gemv_ksplit", 0)
+        dec.set_tuning("gemv_subnormal", 1)
 
 
+@pytest.mark.parametrize("subn", [1, 0])
 @pytest.mark.parametrize("t", [1, 3, 8])
-def test_pow2_kat_exact(dec, orc, t):
+def test_pow2_kat_exact(dec, orc, t, subn):
     # crates/server/src/probes/w4a16/gpu/bench.rs:77-121: power-of-two scales and activations make
     # every partial sum exact, so the GPU result must equal the f64 expectation bit for bit.
     k, n = 256, 128
@@ -134,7 +138,11 @@ def test_pow2_kat_exact(dec, orc, t):
               ((nib.astype(np.float64) - 8) * np.repeat(s.view(np.float16).astype(np.float64), 128, axis=1)).T
               ).astype(np.float32)
     dec.upload_lin_g("p2", q, s, n, k, 128)
-    y = dec.lin_forward("p2", x_dev(x), t).cpu().numpy()
+    dec.set_tuning("gemv_subnormal", subn)
+    try:
+        y = dec.lin_forward("p2", x_dev(x), t).cpu().numpy()
+    finally:
+        dec.set_tuning("gemv_subnormal", 1)
     assert np.array_equal(y.view(np.uint32), expect.view(np.uint32))
 
 
@@ -157,6 +165,22 @@ def test_gemv_vs_lane_oracle(dec, orc, n, k, group, t):
     y16 = dec.lin_forward("g", x_dev(x), t, out_f16=True).cpu().numpy()
     assert np.array_equal(y16.view(np.uint16), y.cpu().numpy().astype(np.float16).view(np.uint16))
     dec.drop_lin("g")
+
+
+def test_both_operand_forms_agree(dec, orc):
+    # raw-nibble subnormal operands + per-group fix-up vs exact (nibble-8) operands: same sums up to f32 rounding
+    n, k, t = 1024, 5120, 8
+    q, s = synth.make_linear(n, k, 128, seed=21)
+    x = x_dev(synth.make_acts(t, k, seed=22))
+    dec.upload_lin_g("ab", q, s, n, k, 128)
+    a = dec.sk_single_dev("ab", x, t=t).clone()
+    dec.set_tuning("gemv_subnormal", 0)
+    try:
+        b = dec.sk_single_dev("ab", x, t=t).clone()
+    finally:
+        dec.set_tuning("gemv_subnormal", 1)
+    assert (a - b).abs().max().item() <= 5e-5
+    dec.kernel_status()
 
 
 def test_config1_reference_cpu_case(dec, orc):
