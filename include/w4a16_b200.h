@@ -61,13 +61,18 @@ W4A16_API int w4a16_sync(w4a16_dec* dec);
  * status word instead of hanging; the reference's only guard is its host watchdog
  * (crates/diag/src/watchdog.rs:46-90). w4a16_sync() includes this check. */
 W4A16_API int w4a16_kernel_status(w4a16_dec* dec);
+/* Diagnostic: after set_tuning("debug_timeline", 1), the first CTA of every kernel stamps the SM
+ * cycle counter at its pipeline events into a device buffer; this copies up to max_slots entries out.
+ * Plays the role of the reference's per-launch event profiler
+ * (crates/backend-gpu/src/rawcuda/ctx/prof.rs:56-131) at a finer grain. */
+W4A16_API int w4a16_debug_timeline(w4a16_dec* dec, long long* out, int max_slots);
 /* Kernels launched by forward calls since creation: the launch counter the reference keeps in
  * HOST_LAUNCH_CALLS (crates/backend-gpu/src/rawcuda/ctx/mod.rs:10-11,311-315). */
 W4A16_API unsigned long long w4a16_launch_count(w4a16_dec* dec);
 /* Kernel-selection knobs, the analogue of the reference's LLM170_* environment flags
  * (crates/diag/src/flag.rs:3-27). Keys: "gemv_ctas_per_sm", "gemv_ksplit" (0 = automatic),
- * "gemv_stages" (2 KB weight chunks in flight per warp, 2..4),
- * "gemv_subnormal" (1 = default arithmetic, 0 = exact nibble-8 operands), "pdl" (1 = default: kernels are
+ * "gemv_stages" (16 KB weight stages in flight per CTA, 2..8), "gemv_warps" (consumer warps per CTA, 8 or 16),
+ * "gemv_subnormal" (1 = default arithmetic, 0 = exact nibble-8 operands), "debug_timeline" (0/1, see w4a16_debug_timeline), "pdl" (1 = default: kernels are
  * launched with programmatic stream serialization and prefetch weights while the previous kernel of
  * the stream drains; 0 = ordinary launches). */
 W4A16_API int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value);

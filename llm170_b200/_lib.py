@@ -22,6 +22,7 @@ _SIGS = {
     "w4a16_stream": (_vp, [_vp]),
     "w4a16_sync": (_i, [_vp]),
     "w4a16_kernel_status": (_i, [_vp]),
+    "w4a16_debug_timeline": (_i, [_vp, _vp, _i]),
     "w4a16_launch_count": (C.c_ulonglong, [_vp]),
     "w4a16_set_tuning": (_i, [_vp, C.c_char_p, _i]),
     "w4a16_check_shapes": (_i, [_sz] * 7),

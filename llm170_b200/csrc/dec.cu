@@ -184,7 +184,10 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
     a.ksplit = ks;
     a.subnormal = tune_gemv_subnormal;
     a.pdl = tune_pdl;
+    a.dbg = dbg_buf;
+    a.dbg_seq = (int)(launches % 400);
     a.ring_stages = tune_gemv_stages;
+    a.cons_warps = tune_gemv_warps;
     a.status = gemm_status;
     if (int rc = ensure_scratch(gemv_part_floats(grid_x, ks), grid_x, st)) {
         return rc;
@@ -303,6 +306,9 @@ void w4a16_dec_free(w4a16_dec* dec) {
     if (d.gemm_status) {
         cudaFree(d.gemm_status);
     }
+    if (d.dbg_buf) {
+        cudaFree(d.dbg_buf);
+    }
     if (d.xh) {
         cudaFree(d.xh);
     }
@@ -327,6 +333,19 @@ int w4a16_sync(w4a16_dec* dec) {
         return dec->d.cuda_fail("sync", e);
     }
     return w4a16_kernel_status(dec);
+}
+
+int w4a16_debug_timeline(w4a16_dec* dec, long long* out, int max_slots) {
+    Dec& d = dec->d;
+    if (!d.dbg_buf) {
+        return d.fail("w4a16: timeline is off; set_tuning(\"debug_timeline\", 1) first");
+    }
+    const int n = max_slots < w4::DBG_SLOTS ? max_slots : w4::DBG_SLOTS;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) {
+        e = cudaMemcpy(out, d.dbg_buf, (size_t)n * sizeof(long long), cudaMemcpyDeviceToHost);
+    }
+    return e == cudaSuccess ? 0 : d.cuda_fail("read timeline", e);
 }
 
 int w4a16_kernel_status(w4a16_dec* dec) {
@@ -356,10 +375,31 @@ int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
         return 0;
     }
     if (!strcmp(key, "gemv_stages")) {
-        if (value < 2 || value > 4) {
-            return d.fail("w4a16 tuning: gemv_stages must be 2..4");
+        if (value < 2 || value > 8) {
+            return d.fail("w4a16 tuning: gemv_stages must be 2..8");
         }
         d.tune_gemv_stages = value;
+        return 0;
+    }
+    if (!strcmp(key, "gemv_warps")) {
+        if (value != 8 && value != 16) {
+            return d.fail("w4a16 tuning: gemv_warps must be 8 or 16");
+        }
+        d.tune_gemv_warps = value;
+        return 0;
+    }
+    if (!strcmp(key, "debug_timeline")) {
+        if (value && !d.dbg_buf) {
+            cudaError_t e = cudaMalloc(&d.dbg_buf, w4::DBG_SLOTS * sizeof(long long));
+            if (e != cudaSuccess) {
+                return d.cuda_fail("alloc timeline buffer", e);
+            }
+            cudaMemset(d.dbg_buf, 0, w4::DBG_SLOTS * sizeof(long long));
+        } else if (!value && d.dbg_buf) {
+            cudaDeviceSynchronize();
+            cudaFree(d.dbg_buf);
+            d.dbg_buf = nullptr;
+        }
         return 0;
     }
     if (!strcmp(key, "pdl")) {

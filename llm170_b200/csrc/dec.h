@@ -7,6 +7,8 @@
 
 namespace w4 {
 
+constexpr int DBG_SLOTS = 8192;
+
 struct Lin {
     uint32_t* qt = nullptr;  // T64 tiles (layout.cuh)
     uint16_t* st = nullptr;  // tiled f16 scale pairs
@@ -33,10 +35,12 @@ struct Dec {
     void* yh = nullptr;
     size_t yh_cap = 0;
     // knobs
-    int tune_gemv_stages = 2;
-    int tune_gemv_ctas_per_sm = 5;   // residency cap assumed by the split-K cost model (register-limited)
+    int tune_gemv_stages = 4;
+    int tune_gemv_warps = 16;
+    int tune_gemv_ctas_per_sm = 3;   // residency cap assumed by the split-K cost model (register-limited)
     int tune_gemv_subnormal = 1;
     int tune_pdl = 1;
+    long long* dbg_buf = nullptr;  // device timeline buffer (DBG_SLOTS entries) when the knob is on
     int tune_gemv_ksplit = 0;
     // kernels launched by forward calls since creation
     unsigned long long launches = 0;

@@ -9,8 +9,8 @@
 //
 // One CTA computes a 128 (tokens) x 256 (weight rows) tile:
 //   warp 0      producer: TMA-loads the f16 activation tile (128 x 64, 128B swizzle) and bulk-copies the
-//               raw int4 tiles (16 x 512 B of the T64 layout) of each 64-wide k-block into a 4-stage ring
-//   warps 2-9   expand int4 -> f16 into the K-major 128B-swizzled B operand of the stage (one 16-byte
+//               raw int4 tiles (16 x 512 B of the T64 layout) of each 64-wide k-block into a 6-stage ring
+//   warps 2-17  expand int4 -> f16 into a 2-stage ring of K-major 128B-swizzled B operands (one 16-byte
 //               chunk = 8 consecutive k of one weight row), then signal the MMA warp
 //   warp 1      one lane issues 4 x tcgen05.mma (M128 N256 K16, f16 x f16 -> f32 in TMEM) per k-block and
 //               commits the stage back to the producer
@@ -22,6 +22,7 @@
 
 #include "../../include/w4a16_b200.h"
 #include "dec.h"
+#include "ptx.cuh"
 
 namespace w4 {
 
@@ -30,15 +31,15 @@ namespace {
 constexpr int BM = 128;           // tokens per tile (UMMA M)
 constexpr int BN = 256;           // weight rows per tile (UMMA N)
 constexpr int BK = TILE_K;        // 64 k per stage = one 128-byte swizzle row of f16
-constexpr int STAGES = 4;
+constexpr int NT = 6;              // TMA ring: activation tile + raw int4 tile per stage
+constexpr int NB = 2;              // ring of expanded f16 weight tiles
 constexpr int A_BYTES = BM * BK * 2;          // 16 KB
 constexpr int RAW_BYTES = BN * BK / 2;        // 8 KB
 constexpr int B_BYTES = BN * BK * 2;          // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + RAW_BYTES + B_BYTES;
-constexpr int NUM_DQ_WARPS = 8;
+constexpr int NUM_DQ_WARPS = 16;   // one 16-row block of the tile each
 constexpr int NUM_THREADS = (2 + NUM_DQ_WARPS) * 32;
 constexpr int TMEM_COLS = 256;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int SMEM_BYTES = NT * (A_BYTES + RAW_BYTES) + NB * B_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr int GROUP_M = 8;        // m-tiles per rasterisation group (L2 reuse of the weight tiles)
 
 struct GemmArgs {
@@ -49,65 +50,8 @@ struct GemmArgs {
     int out_f16;
     int m_tiles, n_tiles;
     int* status;  // 0 = ok; otherwise code<<16 | detail of the first wait that expired
+    long long* dbg;  // optional timeline buffer (diagnostic), CTA 0 only
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Bounded wait. Returns false if it gave up (2^31 cycles, about a second) or another role already did.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
-    if (mbar_try(bar, parity)) {
-        return true;
-    }
-    const long long t0 = clock64();
-    unsigned spins = 0;
-    while (!mbar_try(bar, parity)) {
-        if ((++spins & 0x3FF) == 0) {
-            if (*abort_flag) {
-                return false;
-            }
-            if (clock64() - t0 > (1ll << 31)) {
-                *abort_flag = 1;
-                atomicCAS(status, 0, code);
-                return false;
-            }
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
 
 // K-major, 128B-swizzled operand: 8-row groups are 1024 B apart (SBO), LBO unused, descriptor version 1.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
@@ -143,28 +87,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
 __device__ __forceinline__ uint32_t hmul2u(uint32_t a, uint32_t b) {
     uint32_t r;
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
-// packed word -> a[0]=(r0;k,k+1) a[1]=(r1;k,k+1) a[2]=(r0;k+2,k+3) a[3]=(r1;k+2,k+3), each exactly nibble-8
-__device__ __forceinline__ void dequant_word(uint32_t w, uint32_t (&a)[4]) {
-    const uint32_t MAGIC = 0x64006400u, SUB = 0x64086408u, MUL = 0x2c002c00u, ADD = 0xd480d480u;
-    const uint32_t w8 = w >> 8;
-    const uint32_t lo0 = lop3_and_or(w, 0x000f000fu, MAGIC), hi0 = lop3_and_or(w, 0x00f000f0u, MAGIC);
-    const uint32_t lo1 = lop3_and_or(w8, 0x000f000fu, MAGIC), hi1 = lop3_and_or(w8, 0x00f000f0u, MAGIC);
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(a[0]) : "r"(lo0), "r"(SUB));
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(a[1]) : "r"(hi0), "r"(MUL), "r"(ADD));
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(a[2]) : "r"(lo1), "r"(SUB));
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(a[3]) : "r"(hi1), "r"(MUL), "r"(ADD));
-}
-
 template <int GROUP>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
@@ -175,15 +102,16 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
-    // stage s: [A 16K][B f16 32K][raw 8K]; A and B bases stay 1024-byte aligned
-    auto a_addr = [&](int s) { return base + (uint32_t)s * STAGE_BYTES; };
-    auto b_addr = [&](int s) { return base + (uint32_t)s * STAGE_BYTES + A_BYTES; };
-    auto raw_addr = [&](int s) { return base + (uint32_t)s * STAGE_BYTES + A_BYTES + B_BYTES; };
-    const uint32_t bars = base + STAGES * STAGE_BYTES;
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto bready_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    auto empty_bar = [&](int s) { return bars + 8u * (2 * STAGES + s); };
-    const uint32_t accum_bar = bars + 8u * (3 * STAGES);
+    // [A ring NT x 16K][B ring NB x 32K][raw ring NT x 8K][barriers]; A and B bases are 1024-byte aligned
+    auto a_addr = [&](int s) { return base + (uint32_t)s * A_BYTES; };
+    auto b_addr = [&](int s) { return base + (uint32_t)(NT * A_BYTES) + (uint32_t)s * B_BYTES; };
+    auto raw_addr = [&](int s) { return base + (uint32_t)(NT * A_BYTES + NB * B_BYTES) + (uint32_t)s * RAW_BYTES; };
+    const uint32_t bars = base + NT * (A_BYTES + RAW_BYTES) + NB * B_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };               // TMA landed (A + raw)
+    auto empty_bar = [&](int s) { return bars + 8u * (NT + s); };       // MMAs that read A[s] retired
+    auto bready_bar = [&](int s) { return bars + 8u * (2 * NT + s); };  // B[s] expanded
+    auto bfree_bar = [&](int s) { return bars + 8u * (2 * NT + NB + s); };  // MMAs that read B[s] retired
+    const uint32_t accum_bar = bars + 8u * (2 * NT + 2 * NB);
 
     // tile of this CTA (groups of GROUP_M m-tiles walk the n-tiles together)
     int m_tile, n_tile;
@@ -202,12 +130,19 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
     const int rb0 = n0 / TILE_ROWS;
     const int nrbv = min(BN, a.n - n0) / TILE_ROWS;  // valid 16-row blocks in this tile
 
+    const bool stamp = a.dbg != nullptr && blockIdx.x == 0;
+    if (stamp && threadIdx.x == 0) {
+        a.dbg[4000] = clock64();
+    }
     if (threadIdx.x == 0) {
         s_abort = 0;
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < NT; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(bready_bar(s), NUM_DQ_WARPS);
             mbar_init(empty_bar(s), 1);
+        }
+        for (int s = 0; s < NB; ++s) {
+            mbar_init(bready_bar(s), NUM_DQ_WARPS);
+            mbar_init(bfree_bar(s), 1);
         }
         mbar_init(accum_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -228,16 +163,18 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
             for (int it = 0; it < nkb; ++it) {
-                const int s = it % STAGES, r = it / STAGES;
+                const int s = it % NT, r = it / NT;
                 if (!mbar_wait(empty_bar(s), (r & 1) ^ 1, abort_flag, a.status, (1 << 16) | it)) {
                     break;
                 }
+                if (stamp && it < 1000) {
+                    a.dbg[it] = clock64();
+                }
                 mbar_expect_tx(full_bar(s), A_BYTES + nrbv * (TILE_WORDS * 4));
                 tma_load_2d(a_addr(s), &tmap_x, it * BK, m0, full_bar(s));
-                for (int j = 0; j < nrbv; ++j) {
-                    bulk_load(raw_addr(s) + j * (TILE_WORDS * 4),
-                              a.qt + ((size_t)(rb0 + j) * nkb + it) * TILE_WORDS, TILE_WORDS * 4, full_bar(s));
-                }
+                // the tile's row blocks are contiguous at one k-block (k-block-major layout): one copy
+                bulk_load(raw_addr(s), a.qt + ((size_t)it * (a.n / TILE_ROWS) + rb0) * TILE_WORDS,
+                          nrbv * (TILE_WORDS * 4), full_bar(s));
             }
         }
         __syncwarp();
@@ -247,19 +184,23 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
             constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             bool ok = true;
             for (int it = 0; it < nkb && ok; ++it) {
-                const int s = it % STAGES, r = it / STAGES;
+                const int s = it % NT, r = it / NT, sb = it % NB, rb_ = it / NB;
                 ok = mbar_wait(full_bar(s), r & 1, abort_flag, a.status, (2 << 16) | it) &&
-                     mbar_wait(bready_bar(s), r & 1, abort_flag, a.status, (3 << 16) | it);
+                     mbar_wait(bready_bar(sb), rb_ & 1, abort_flag, a.status, (3 << 16) | it);
                 if (!ok) {
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t da = umma_desc(a_addr(s)), db = umma_desc(b_addr(s));
+                if (stamp && it < 1000) {
+                    a.dbg[3000 + it] = clock64();
+                }
+                const uint64_t da = umma_desc(a_addr(s)), db = umma_desc(b_addr(sb));
 #pragma unroll
                 for (int j = 0; j < BK / 16; ++j) {
                     umma_f16(tmem, da + 2 * j, db + 2 * j, IDESC, (it > 0 || j > 0) ? 1u : 0u);
                 }
                 umma_commit(empty_bar(s));
+                umma_commit(bfree_bar(sb));
             }
             if (ok) {
                 umma_commit(accum_bar);
@@ -274,61 +215,64 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
         const int t = jj & 3, g = 2 * ((t + ph) & 3) + (jj >> 2);
         const int ng = a.k / GROUP;
         bool ok = true;
-        for (int it = 0; it < nkb && ok; ++it) {
-            const int s = it % STAGES, r = it / STAGES;
-            uint32_t sc[2][2];
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int rbi = dw + NUM_DQ_WARPS * j;
-                sc[j][0] = sc[j][1] = 0;
-                if (rbi < nrbv) {
-                    const uint32_t* sp = a.st + ((size_t)(rb0 + rbi) * ng) * 8 + g;
-                    if (GROUP >= BK) {
-                        sc[j][0] = sc[j][1] = __ldg(sp + (size_t)(it * BK / GROUP) * 8);
-                    } else {
-                        sc[j][0] = __ldg(sp + (size_t)(it * 2) * 8);
-                        sc[j][1] = __ldg(sp + (size_t)(it * 2 + 1) * 8);
-                    }
+        // scales of k-block `it` for this lane's two row blocks, fetched one k-block ahead
+        auto load_scales = [&](int it, uint32_t (&sc)[2]) {
+            sc[0] = sc[1] = 0;
+            if (dw < nrbv && it < nkb) {
+                const uint32_t* sp = a.st + ((size_t)(rb0 + dw) * ng) * 8 + g;
+                if (GROUP >= BK) {
+                    sc[0] = sc[1] = __ldg(sp + (size_t)(it * BK / GROUP) * 8);
+                } else {
+                    sc[0] = __ldg(sp + (size_t)(it * 2) * 8);
+                    sc[1] = __ldg(sp + (size_t)(it * 2 + 1) * 8);
                 }
             }
-            ok = mbar_wait(full_bar(s), r & 1, abort_flag, a.status, (4 << 16) | it);
+        };
+        uint32_t sc[2], sc_next[2];
+        load_scales(0, sc_next);
+        for (int it = 0; it < nkb && ok; ++it) {
+            const int s = it % NT, r = it / NT, sb = it % NB, rb_ = it / NB;
+            sc[0] = sc_next[0];
+            sc[1] = sc_next[1];
+            load_scales(it + 1, sc_next);
+            ok = mbar_wait(full_bar(s), r & 1, abort_flag, a.status, (4 << 16) | it) &&
+                 mbar_wait(bfree_bar(sb), (rb_ & 1) ^ 1, abort_flag, a.status, (6 << 16) | it);
             if (!ok) {
                 break;
             }
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int rbi = dw + NUM_DQ_WARPS * j;
+            if (stamp && threadIdx.x == 64 && it < 1000) {
+                a.dbg[1000 + it] = clock64();
+            }
+            {
+                const int rbi = dw;
                 if (rbi < nrbv) {
-                    uint4 raw;
-                    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                 : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
-                                 : "r"(raw_addr(s) + rbi * (TILE_WORDS * 4) + (4 * g + t) * 16));
+                    const uint4 raw = *reinterpret_cast<const uint4*>(
+                        base_ptr + (raw_addr(s) - base) + rbi * (TILE_WORDS * 4) + (4 * g + t) * 16);
                     const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-                    const uint32_t row_off = b_addr(s) + (uint32_t)(rbi * TILE_ROWS + g) * 128u;
+                    const uint32_t row_off = b_addr(sb) + (uint32_t)(rbi * TILE_ROWS + g) * 128u;
 #pragma unroll
                     for (int p = 0; p < 2; ++p) {
                         uint32_t f0[4], f1[4];
                         dequant_word(rw[2 * p], f0);
                         dequant_word(rw[2 * p + 1], f1);
-                        const uint32_t s2 = sc[j][p];
+                        const uint32_t s2 = sc[p];
                         const uint32_t s_r0 = __byte_perm(s2, s2, 0x1010);  // (s[r0], s[r0])
                         const uint32_t s_r1 = __byte_perm(s2, s2, 0x3232);  // (s[r1], s[r1])
                         const uint32_t chunk = (uint32_t)(((4 * p + t) ^ g) << 4);
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row_off + chunk),
-                                     "r"(hmul2u(f0[0], s_r0)), "r"(hmul2u(f0[2], s_r0)), "r"(hmul2u(f1[0], s_r0)),
-                                     "r"(hmul2u(f1[2], s_r0))
-                                     : "memory");
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(row_off + 8u * 128u + chunk),
-                                     "r"(hmul2u(f0[1], s_r1)), "r"(hmul2u(f0[3], s_r1)), "r"(hmul2u(f1[1], s_r1)),
-                                     "r"(hmul2u(f1[3], s_r1))
-                                     : "memory");
+                        *reinterpret_cast<uint4*>(base_ptr + (row_off - base) + chunk) =
+                            make_uint4(hmul2u(f0[0], s_r0), hmul2u(f0[2], s_r0), hmul2u(f1[0], s_r0), hmul2u(f1[2], s_r0));
+                        *reinterpret_cast<uint4*>(base_ptr + (row_off - base) + 8u * 128u + chunk) =
+                            make_uint4(hmul2u(f0[1], s_r1), hmul2u(f0[3], s_r1), hmul2u(f1[1], s_r1), hmul2u(f1[3], s_r1));
                     }
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(bready_bar(s));
+                mbar_arrive(bready_bar(sb));
+            }
+            if (stamp && threadIdx.x == 64 && it < 1000) {
+                a.dbg[2000 + it] = clock64();
             }
         }
         if (warp < 6) {
@@ -337,6 +281,9 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                 ok = mbar_wait(accum_bar, 0, abort_flag, a.status, (5 << 16));
             }
             ok = __all_sync(0xffffffffu, ok);
+            if (stamp && threadIdx.x == 64) {
+                a.dbg[4001] = clock64();
+            }
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int quad = warp & 3;
@@ -379,12 +326,14 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
         }
     }
 
+    if (stamp && threadIdx.x == 64) {
+        a.dbg[4002] = clock64();
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
-    (void)base_ptr;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -445,6 +394,7 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.m_tiles = (t + BM - 1) / BM;
     a.n_tiles = (l->n + BN - 1) / BN;
     a.status = gemm_status;
+    a.dbg = dbg_buf;
     const int grid = a.m_tiles * a.n_tiles;
     if (l->group == 128) {
         gemm_w4a16_tc_kernel<128><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map, a);

@@ -8,11 +8,15 @@
 //   * weights never become rounded f16 values: the MMA multiplies the raw nibble (as an exact f16
 //     subnormal, nibble * 2^-24 or 2^-20) by x, and the power of two, the zero point 8 (through a
 //     per-group sum of x) and the f32 group scale are applied to the f32 accumulator once per group;
-//   * each warp streams its row block through a private ring of 2 KB bulk (TMA) copies in shared
-//     memory, so the bytes in flight do not depend on registers or occupancy;
+//   * a CTA owns 256 weight rows and a K range.  One producer lane streams them through a ring of
+//     16 KB stages in shared memory with 8 KB bulk (TMA) copies -- the 16 row blocks of a CTA are
+//     contiguous at each k-block in the T64 layout -- and 8 consumer warps (two row blocks each, sharing
+//     the x fragments) only wait on a "full" mbarrier and arrive on an "empty" one;
 //   * split-K partials are reduced by the last CTA to arrive (atomic ticket, no spin, fixed summation
-//     order): no second launch, reproducible results, and the tickets are left at zero for graph replay.
-// The kernel is HBM-bound: each lane consumes 16-byte pieces of the T64 layout (layout.cuh).
+//     order): no second launch, reproducible results, and the tickets are left at zero for graph replay;
+//   * launched with programmatic stream serialization: the weight stream starts while the previous
+//     kernel of the stream drains; x, scratch and outputs are touched only after griddepcontrol.wait.
+// The kernel is HBM-bound.
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -22,22 +26,22 @@ namespace w4 {
 
 namespace {
 
-constexpr int MAX_RING_STAGES = 4;
-constexpr int CHUNK_KB = 4;                         // k-blocks per bulk copy
-constexpr int CHUNK_BYTES = CHUNK_KB * TILE_WORDS * 4;  // 2 KB
-constexpr int ROWS_PER_CTA = GEMV_WARPS * TILE_ROWS;
+constexpr int CTA_RB = 16;                        // 16 row blocks = 256 rows per CTA
+constexpr int ROWS_PER_CTA = CTA_RB * TILE_ROWS;
+constexpr int CK = 2;                             // k-blocks per ring stage
+constexpr int KB_BYTES = CTA_RB * TILE_WORDS * 4; // 8 KB: one k-block of the CTA's rows
+constexpr int STAGE_BYTES = CK * KB_BYTES;        // 16 KB
+constexpr int MAX_STAGES = 8;
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 // first MMA of a group: accumulates onto zero
 __device__ __forceinline__ void mma16816_z(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%10,%10,%10,%10};"
         : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
@@ -67,15 +71,15 @@ struct SmemPlan {
     int x_stride;   // halves per token row (byte stride = 64 mod 128: conflict-free 128-bit reads)
     int x_rows;     // token rows staged (m, plus one all-zero row when m < 8)
     int off_xsum;   // f32 [groups][8]: -8 * sum of x over the group, per token
-    int off_ring;   // GEMV_WARPS x RING_STAGES x CHUNK_BYTES
-    int off_bars;   // 1 + GEMV_WARPS*stages mbarriers
-    int stages;     // chunks in flight per warp
+    int off_ring;   // stages x STAGE_BYTES, 1024-byte aligned
+    int off_bars;   // xbar, full[stages], empty[stages]
+    int stages;
     int total;
 };
 
 __host__ SmemPlan make_plan(int k, int group, int m, int ksplit, int stages) {
     SmemPlan p;
-    p.stages = stages < 2 ? 2 : (stages > MAX_RING_STAGES ? MAX_RING_STAGES : stages);
+    p.stages = stages < 2 ? 2 : (stages > MAX_STAGES ? MAX_STAGES : stages);
     const int halves = max_split_kblocks(k, group, ksplit) * TILE_K;
     p.x_stride = halves + 32;
     p.x_rows = m < GEMV_MAX_M ? m + 1 : m;
@@ -83,26 +87,27 @@ __host__ SmemPlan make_plan(int k, int group, int m, int ksplit, int stages) {
     off = (off + 127) & ~127;
     p.off_xsum = off;
     off += (halves / group) * GEMV_MAX_M * 4;
-    off = (off + 127) & ~127;
+    off = (off + 1023) & ~1023;
     p.off_ring = off;
-    off += GEMV_WARPS * p.stages * CHUNK_BYTES;
+    off += p.stages * STAGE_BYTES;
     p.off_bars = off;
-    off += (1 + GEMV_WARPS * p.stages) * 8;
+    off += (1 + 2 * p.stages) * 8;
     p.total = off;
     return p;
 }
 
-template <int GROUP, bool SUBN>
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
+// CONS_WARPS consumer warps (8 or 16) own 16/CONS_WARPS row blocks each; warp CONS_WARPS is the producer.
+template <int GROUP, bool SUBN, int CONS_WARPS>
+__global__ void __launch_bounds__((CONS_WARPS + 1) * 32)
 gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
-    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int RB_PER_WARP = CTA_RB / CONS_WARPS;
+    extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ int s_is_last;
     __shared__ int s_abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int split = blockIdx.y;
-    const int nkb = a.k / TILE_K;
     constexpr int KB_PER_GROUP = GROUP >= TILE_K ? GROUP / TILE_K : 1;   // 2 for g128, 1 for g32
     constexpr int GROUPS_PER_KB = GROUP >= TILE_K ? 1 : TILE_K / GROUP;  // 1 for g128, 2 for g32
 
@@ -115,29 +120,45 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         }
     }
     const GemvSeg& sg = a.seg[si];
-    const int rb = ((int)blockIdx.x - sg.cta0) * GEMV_WARPS + warp;
-    const bool warp_active = rb < sg.n / TILE_ROWS;
+    const int nrb_seg = sg.n / TILE_ROWS;
+    const int rb_cta0 = ((int)blockIdx.x - sg.cta0) * CTA_RB;    // first row block of this CTA
+    const int nrbv = min(CTA_RB, nrb_seg - rb_cta0);             // valid row blocks in this CTA
 
     int kb0, kb1;
     split_range(a.k, GROUP, a.ksplit, split, &kb0, &kb1);
     const int nloc = kb1 - kb0;                      // k-blocks of this split
     const int halves = nloc * TILE_K;
     const int ngl = halves / GROUP;                  // scale groups of this split
+    const int nchunks = (nloc + CK - 1) / CK;
+    const int S = p.stages;
 
     const uint32_t sbase = smem_u32(smem);
     const uint32_t xbar = sbase + p.off_bars;
-    const int RING_STAGES = p.stages;
-    const uint32_t ring = sbase + p.off_ring + (uint32_t)warp * (RING_STAGES * CHUNK_BYTES);
-    const uint32_t rbar = xbar + 8u + (uint32_t)warp * (RING_STAGES * 8);
+    auto full_bar = [&](int s) { return xbar + 8u + 8u * s; };
+    auto empty_bar = [&](int s) { return xbar + 8u + 8u * (S + s); };
     volatile int* abort_flag = &s_abort;
+    const bool stamp = a.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
 
     if (threadIdx.x == 0) {
+        if (stamp) {
+            a.dbg[0] = clock64();
+            unsigned long long ns;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+            a.dbg[7000 + a.dbg_seq] = (long long)ns;   // kernel start (first CTA), wall-clock ns
+        }
         s_abort = 0;
         mbar_init(xbar, 1);
-        for (int i = 0; i < GEMV_WARPS * RING_STAGES; ++i) {
-            mbar_init(xbar + 8u + 8u * i, 1);
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), CONS_WARPS);
         }
         mbar_init_fence();
+    }
+    if (SUBN && a.m < GEMV_MAX_M) {
+        float* xsum = reinterpret_cast<float*>(smem + p.off_xsum);
+        for (int i = threadIdx.x; i < ngl * GEMV_MAX_M; i += blockDim.x) {
+            xsum[i] = 0.f;
+        }
     }
     // the all-zero token row read by MMA columns >= m
     if (a.m < GEMV_MAX_M) {
@@ -148,99 +169,133 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     }
     __syncthreads();
 
-    const int nchunks = (nloc + CHUNK_KB - 1) / CHUNK_KB;
-    const unsigned char* wsrc =
-        reinterpret_cast<const unsigned char*>(sg.qt) + ((size_t)(warp_active ? rb : 0) * nkb + kb0) * (TILE_WORDS * 4);
+    // chunk c -> stage c % S: CK bulk copies of the CTA's rows at one k-block each (contiguous in T64)
+    const unsigned char* wsrc = reinterpret_cast<const unsigned char*>(sg.qt) +
+                                ((size_t)kb0 * nrb_seg + rb_cta0) * (TILE_WORDS * 4);
+    const size_t kb_pitch = (size_t)nrb_seg * (TILE_WORDS * 4);
     auto issue_chunk = [&](int c) {
-        const int kbs = min(CHUNK_KB, nloc - c * CHUNK_KB);
-        const uint32_t bar = rbar + 8u * (c % RING_STAGES);
-        mbar_expect_tx(bar, kbs * TILE_WORDS * 4);
-        bulk_load(ring + (c % RING_STAGES) * CHUNK_BYTES, wsrc + (size_t)c * CHUNK_BYTES, kbs * TILE_WORDS * 4, bar);
+        const int kbs = min(CK, nloc - c * CK);
+        const int s = c % S;
+        const uint32_t bytes = (uint32_t)nrbv * (TILE_WORDS * 4);
+        mbar_expect_tx(full_bar(s), kbs * bytes);
+        for (int i = 0; i < kbs; ++i) {
+            bulk_load(sbase + p.off_ring + s * STAGE_BYTES + i * KB_BYTES, wsrc + (size_t)(c * CK + i) * kb_pitch, bytes,
+                      full_bar(s));
+        }
     };
-    if (warp_active && lane == 0) {
-        for (int c = 0; c < RING_STAGES && c < nchunks; ++c) {
+    const bool is_producer = warp == CONS_WARPS;
+    if (is_producer && lane == 0) {
+        for (int c = 0; c < S && c < nchunks; ++c) {
             issue_chunk(c);
         }
     }
     // Programmatic dependent launch: the weight copies above do not depend on the previous kernel in the
     // stream, so they are already in flight while it drains.  Everything below reads x or writes
-    // scratch/outputs and must wait for it.  (Both instructions do nothing in an ordinary launch.)
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // scratch/outputs and must wait for it.  (griddepcontrol does nothing in an ordinary launch.)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) {
         mbar_expect_tx(xbar, a.m * halves * 2);
         for (int tok = 0; tok < a.m; ++tok) {
             bulk_load(sbase + tok * p.x_stride * 2, a.x + (size_t)tok * a.k + (size_t)kb0 * TILE_K, halves * 2, xbar);
         }
-    }
-
-    bool ok = mbar_wait(xbar, 0, abort_flag, a.status, (10 << 16));
-    if (SUBN && ok) {
-        // xsum[grp][tok] = -8 * sum_{k in grp} x[tok][k]   (tokens >= m: 0)
-        float* xsum = reinterpret_cast<float*>(smem + p.off_xsum);
-        for (int pr = warp; pr < ngl * GEMV_MAX_M; pr += GEMV_WARPS) {
-            const int grp = pr >> 3, tok = pr & 7;
-            float v = 0.f;
-            if (tok < a.m) {
-                const __half* xr = reinterpret_cast<const __half*>(smem) + (size_t)tok * p.x_stride + grp * GROUP;
-                if (GROUP == 128) {
-                    const uint2 u = *reinterpret_cast<const uint2*>(xr + lane * 4);
-                    const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
-                    const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
-                    v = (f0.x + f0.y) + (f1.x + f1.y);
-                } else {
-                    v = __half2float(xr[lane]);
-                }
-            }
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-                v += __shfl_xor_sync(0xffffffffu, v, off);
-            }
-            if (lane == 0) {
-                xsum[pr] = -8.f * v;
-            }
+        if (stamp) {
+            a.dbg[1] = clock64();
         }
     }
-    __syncthreads();
 
-    float tot[4] = {0.f, 0.f, 0.f, 0.f};
+    if (is_producer) {
+        // ------------------------------------------------------------------ producer: refill freed stages
+        if (lane == 0) {
+            for (int c = S; c < nchunks; ++c) {
+                if (!mbar_wait(empty_bar(c % S), ((c / S) & 1) ^ 1, abort_flag, a.status, (12 << 16) | c)) {
+                    break;
+                }
+                issue_chunk(c);
+            }
+        }
+        __syncwarp();
+    }
+    bool ok = true;
+    if (!is_producer) {
+        ok = mbar_wait(xbar, 0, abort_flag, a.status, (10 << 16));
+        if (stamp && threadIdx.x == 0) {
+            a.dbg[2] = clock64();
+        }
+        if (SUBN && ok) {
+            // xsum[grp][tok] = -8 * sum_{k in grp} x[tok][k] for tok < m (entries of tokens >= m stay zero):
+            // a few threads per (group, token), partial sums combined with shuffles.
+            float* xsum = reinterpret_cast<float*>(smem + p.off_xsum);
+            constexpr int PIECES = GROUP / 8;              // 16-byte pieces per group
+            constexpr int TPP = PIECES >= 8 ? 8 : PIECES;  // threads per (group, token): 8 (g128) or 4 (g32)
+            constexpr int PER_T = PIECES / TPP;
+            const int sub = threadIdx.x % TPP;
+            for (int pr0 = 0; pr0 < ngl * a.m; pr0 += (CONS_WARPS * 32) / TPP) {
+                const int pr = pr0 + threadIdx.x / TPP;
+                float v = 0.f;
+                int grp = 0, tok = 0;
+                const bool live = pr < ngl * a.m;
+                if (live) {
+                    grp = pr / a.m;
+                    tok = pr - grp * a.m;
+                    const uint4* xr =
+                        reinterpret_cast<const uint4*>(smem + ((size_t)tok * p.x_stride + (size_t)grp * GROUP) * 2);
+#pragma unroll
+                    for (int j = 0; j < PER_T; ++j) {
+                        const uint4 u = xr[sub * PER_T + j];
+                        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+                        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+                        const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&u.z));
+                        const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&u.w));
+                        v += ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+                    }
+                }
+#pragma unroll
+                for (int off = TPP / 2; off > 0; off >>= 1) {
+                    v += __shfl_xor_sync(0xffffffffu, v, off);
+                }
+                if (live && sub == 0) {
+                    xsum[grp * GEMV_MAX_M + tok] = -8.f * v;
+                }
+            }
+        }
+        // consumers only: the producer warp is busy refilling the ring
+        asm volatile("bar.sync 1, %0;" ::"n"(CONS_WARPS * 32) : "memory");
+        if (stamp && threadIdx.x == 0) {
+            a.dbg[3] = clock64();
+        }
+    }
+    // ---------------------------------------------------------------------- consumers: stream and accumulate
+    float tot[RB_PER_WARP][4];
+#pragma unroll
+    for (int r = 0; r < RB_PER_WARP; ++r) {
+        tot[r][0] = tot[r][1] = tot[r][2] = tot[r][3] = 0.f;
+    }
+    const int rbw0 = warp * RB_PER_WARP;  // first row block (within the CTA) of this warp
+    const bool warp_active = !is_producer && rbw0 < nrbv;
+    const int nvalid = warp_active ? min(RB_PER_WARP, nrbv - rbw0) : 0;
     if (warp_active && ok) {
         const int ng = a.k / GROUP;
-        const uint32_t* sp = sg.st + ((size_t)rb * ng + (size_t)kb0 * GROUPS_PER_KB / KB_PER_GROUP) * 8 + g;
+        const size_t grp0 = (size_t)kb0 * GROUPS_PER_KB / KB_PER_GROUP;
+        const uint32_t* sp[RB_PER_WARP];
+#pragma unroll
+        for (int r = 0; r < RB_PER_WARP; ++r) {
+            const int rbg = rb_cta0 + rbw0 + (r < nvalid ? r : 0);
+            sp[r] = sg.st + ((size_t)rbg * ng + grp0) * 8 + g;
+        }
         // B fragment source: token g (the zero row when g >= m), this lane's 8 k of each half k-block
         const int xrow_i = g < a.m ? g : a.m;
-        uint32_t xaddr = sbase + (uint32_t)(xrow_i * p.x_stride + 8 * t) * 2;
-        uint32_t xs_addr = sbase + p.off_xsum + (uint32_t)(2 * t) * 4;
-        const uint32_t waddr = ring + lane * 16;
+        const unsigned char* xp = smem + (size_t)(xrow_i * p.x_stride + 8 * t) * 2;
+        const unsigned char* zp = smem + p.off_xsum + (2 * t) * 4;
+        const unsigned char* wbase = smem + p.off_ring + rbw0 * (TILE_WORDS * 4) + lane * 16;
 
-        float acc[4] = {0.f, 0.f, 0.f, 0.f}, acb[4] = {0.f, 0.f, 0.f, 0.f};  // two independent MMA chains
-        uint32_t sc = __ldg(sp);
-        int gl = 0;  // local group index
+        float acc[RB_PER_WARP][2][4];  // two independent MMA chains per row block
+        uint32_t sc[RB_PER_WARP];
+#pragma unroll
+        for (int r = 0; r < RB_PER_WARP; ++r) {
+            sc[r] = __ldg(sp[r]);
+        }
+        int gl = 0;
 
-        auto finish_group = [&]() {
-            const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sc));
-            ++gl;
-            if (gl < ngl) {
-                sc = __ldg(sp + (size_t)gl * 8);  // prefetch the next group's scales
-            }
-            acc[0] += acb[0];
-            acc[1] += acb[1];
-            acc[2] += acb[2];
-            acc[3] += acb[3];
-            if (SUBN) {
-                const float2 z = lds_f32x2(xs_addr);
-                xs_addr += GEMV_MAX_M * 4;
-                tot[0] = fmaf(fmaf(acc[0], 16777216.f, z.x), sf.x, tot[0]);
-                tot[1] = fmaf(fmaf(acc[1], 16777216.f, z.y), sf.x, tot[1]);
-                tot[2] = fmaf(fmaf(acc[2], 1048576.f, z.x), sf.y, tot[2]);
-                tot[3] = fmaf(fmaf(acc[3], 1048576.f, z.y), sf.y, tot[3]);
-            } else {
-                tot[0] = fmaf(acc[0], sf.x, tot[0]);
-                tot[1] = fmaf(acc[1], sf.x, tot[1]);
-                tot[2] = fmaf(acc[2], sf.y, tot[2]);
-                tot[3] = fmaf(acc[3], sf.y, tot[3]);
-            }
-        };
         auto expand = [&](uint32_t w, uint32_t (&fr)[4]) {
             if (SUBN) {
                 nibbles_as_subnormals(w, fr);
@@ -248,88 +303,144 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                 dequant_word(w, fr);
             }
         };
-        // one k-block: 4 MMAs; `first` = this k-block starts a scale group (g128) -- g32 groups are half k-blocks
-        auto kblock = [&](uint32_t wa, uint32_t xa, bool first, bool last) {
-            const uint4 w = lds128(wa);
-            const uint4 x0 = lds128(xa), x1 = lds128(xa + 64);
-            uint32_t fr[4];
-            expand(w.x, fr);
-            if (first || GROUP < TILE_K) {
-                mma16816_z(acc, fr, x0.x, x0.y);
-            } else {
-                mma16816(acc, fr, x0.x, x0.y);
+        auto finish_group = [&]() {
+            float2 z = make_float2(0.f, 0.f);
+            if (SUBN) {
+                z = *reinterpret_cast<const float2*>(zp);
+                zp += GEMV_MAX_M * 4;
             }
-            expand(w.y, fr);
-            if (first || GROUP < TILE_K) {
-                mma16816_z(acb, fr, x0.z, x0.w);
-            } else {
-                mma16816(acb, fr, x0.z, x0.w);
+            ++gl;
+#pragma unroll
+            for (int r = 0; r < RB_PER_WARP; ++r) {
+                const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sc[r]));
+                if (gl < ngl) {
+                    sc[r] = __ldg(sp[r] + (size_t)gl * 8);  // prefetch the next group's scales
+                }
+                const float c0 = acc[r][0][0] + acc[r][1][0], c1 = acc[r][0][1] + acc[r][1][1];
+                const float c2 = acc[r][0][2] + acc[r][1][2], c3 = acc[r][0][3] + acc[r][1][3];
+                if (SUBN) {
+                    tot[r][0] = fmaf(fmaf(c0, 16777216.f, z.x), sf.x, tot[r][0]);
+                    tot[r][1] = fmaf(fmaf(c1, 16777216.f, z.y), sf.x, tot[r][1]);
+                    tot[r][2] = fmaf(fmaf(c2, 1048576.f, z.x), sf.y, tot[r][2]);
+                    tot[r][3] = fmaf(fmaf(c3, 1048576.f, z.y), sf.y, tot[r][3]);
+                } else {
+                    tot[r][0] = fmaf(c0, sf.x, tot[r][0]);
+                    tot[r][1] = fmaf(c1, sf.x, tot[r][1]);
+                    tot[r][2] = fmaf(c2, sf.y, tot[r][2]);
+                    tot[r][3] = fmaf(c3, sf.y, tot[r][3]);
+                }
             }
+        };
+        // half a k-block (32 k = two MMAs) of both row blocks; `first` starts the chains on zero
+        auto half_kblock = [&](const uint4 (&w)[RB_PER_WARP], int hsel, const uint4& x, bool first) {
+#pragma unroll
+            for (int r = 0; r < RB_PER_WARP; ++r) {
+                uint32_t fr[4];
+                expand(hsel ? w[r].z : w[r].x, fr);
+                if (first) {
+                    mma16816_z(acc[r][0], fr, x.x, x.y);
+                } else {
+                    mma16816(acc[r][0], fr, x.x, x.y);
+                }
+                expand(hsel ? w[r].w : w[r].y, fr);
+                if (first) {
+                    mma16816_z(acc[r][1], fr, x.z, x.w);
+                } else {
+                    mma16816(acc[r][1], fr, x.z, x.w);
+                }
+            }
+        };
+        // one k-block; `first`/`last`: it opens / closes a scale group (g128); g32 groups are half k-blocks
+        auto kblock = [&](const unsigned char* wa, const unsigned char* xa, bool first, bool last) {
+            // ordinary shared-memory loads (ordered only against the barrier waits): the compiler overlaps k-blocks
+            uint4 w[RB_PER_WARP];
+#pragma unroll
+            for (int r = 0; r < RB_PER_WARP; ++r) {
+                w[r] = *reinterpret_cast<const uint4*>(wa + r * (TILE_WORDS * 4));
+            }
+            const uint4 x0 = *reinterpret_cast<const uint4*>(xa);
+            const uint4 x1 = *reinterpret_cast<const uint4*>(xa + 64);
+            half_kblock(w, 0, x0, first || GROUP < TILE_K);
             if (GROUP < TILE_K) {
                 finish_group();
             }
-            expand(w.z, fr);
-            if (GROUP < TILE_K) {
-                mma16816_z(acc, fr, x1.x, x1.y);
-            } else {
-                mma16816(acc, fr, x1.x, x1.y);
-            }
-            expand(w.w, fr);
-            if (GROUP < TILE_K) {
-                mma16816_z(acb, fr, x1.z, x1.w);
-            } else {
-                mma16816(acb, fr, x1.z, x1.w);
-            }
+            half_kblock(w, 1, x1, GROUP < TILE_K);
             if (GROUP < TILE_K || last) {
                 finish_group();
             }
         };
 
         for (int c = 0; c < nchunks; ++c) {
-            const int stg = c % RING_STAGES;
-            ok = mbar_wait(rbar + 8u * stg, (c / RING_STAGES) & 1, abort_flag, a.status, (11 << 16) | c);
+            const int s = c % S;
+            if (stamp && threadIdx.x == 0 && c < 1000) {
+                a.dbg[16 + 2 * c] = clock64();
+            }
+            ok = mbar_wait(full_bar(s), (c / S) & 1, abort_flag, a.status, (11 << 16) | c);
             if (!ok) {
                 break;
             }
-            const uint32_t wa = waddr + stg * CHUNK_BYTES;
-            if (c * CHUNK_KB + CHUNK_KB <= nloc) {
-                // group boundaries fall on even k-blocks: splits are whole groups
-                kblock(wa, xaddr, true, KB_PER_GROUP == 1);
-                kblock(wa + 512, xaddr + 128, KB_PER_GROUP == 1, true);
-                kblock(wa + 1024, xaddr + 256, true, KB_PER_GROUP == 1);
-                kblock(wa + 1536, xaddr + 384, KB_PER_GROUP == 1, true);
-            } else {
-                const int rem = nloc - c * CHUNK_KB;
-                for (int i = 0; i < rem; ++i) {
-                    const bool first = KB_PER_GROUP == 1 || (i & 1) == 0;
-                    const bool last = KB_PER_GROUP == 1 || (i & 1) == 1;
-                    kblock(wa + i * 512, xaddr + i * 128, first, last);
-                }
+            if (stamp && threadIdx.x == 0 && c < 1000) {
+                a.dbg[17 + 2 * c] = clock64();
             }
-            xaddr += CHUNK_KB * 128;
+            const unsigned char* wa = wbase + s * STAGE_BYTES;
+            if (c * CK + CK <= nloc) {
+                // group boundaries fall on even k-blocks: splits are whole groups
+                kblock(wa, xp, true, KB_PER_GROUP == 1);
+                kblock(wa + KB_BYTES, xp + 128, KB_PER_GROUP == 1, true);
+            } else {
+                kblock(wa, xp, true, true);  // odd tail: only reachable with 64-wide units (g32)
+            }
+            xp += CK * 128;
             __syncwarp();
-            if (lane == 0 && c + RING_STAGES < nchunks) {
-                issue_chunk(c + RING_STAGES);
+            if (lane == 0) {
+                mbar_arrive(empty_bar(s));
+            }
+        }
+    } else if (!is_producer && ok) {
+        // a consumer warp without rows still releases every stage
+        for (int c = 0; c < nchunks; ++c) {
+            if (!mbar_wait(full_bar(c % S), (c / S) & 1, abort_flag, a.status, (13 << 16) | c)) {
+                break;
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(empty_bar(c % S));
             }
         }
     }
+    if (stamp && threadIdx.x == 0) {
+        a.dbg[4] = clock64();
+        a.dbg[5] = nchunks;
+    }
+    if (a.dbg != nullptr && threadIdx.x == 0) {
+        unsigned long long ns;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+        atomicMax(reinterpret_cast<unsigned long long*>(a.dbg) + 7400 + a.dbg_seq, ns);  // last CTA's main-loop end
+    }
 
-    // tot[0],tot[1]: row g, tokens 2t, 2t+1 ; tot[2],tot[3]: row g+8, tokens 2t, 2t+1
-    const int row0 = rb * TILE_ROWS + g, row1 = row0 + 8;
+    // the next kernel of the stream may start its weight stream now (it waits for our completion
+    // before touching x, scratch or outputs)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // tot[r][0],[1]: row g, tokens 2t, 2t+1 ; tot[r][2],[3]: row g+8, tokens 2t, 2t+1
     if (a.ksplit == 1) {
-        if (warp_active) {
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const int tok = 2 * t + j;
-                if (tok < a.m) {
-                    if (a.out_f16) {
-                        __half* o = reinterpret_cast<__half*>(sg.out) + (size_t)tok * sg.n;
-                        o[row0] = __float2half_rn(tot[j]);
-                        o[row1] = __float2half_rn(tot[2 + j]);
-                    } else {
-                        float* o = reinterpret_cast<float*>(sg.out) + (size_t)tok * sg.n;
-                        o[row0] = tot[j];
-                        o[row1] = tot[2 + j];
+        for (int r = 0; r < RB_PER_WARP; ++r) {
+            if (r < nvalid) {
+                const int row0 = (rb_cta0 + rbw0 + r) * TILE_ROWS + g, row1 = row0 + 8;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int tok = 2 * t + j;
+                    if (tok < a.m) {
+                        if (a.out_f16) {
+                            __half* o = reinterpret_cast<__half*>(sg.out) + (size_t)tok * sg.n;
+                            o[row0] = __float2half_rn(tot[r][j]);
+                            o[row1] = __float2half_rn(tot[r][2 + j]);
+                        } else {
+                            float* o = reinterpret_cast<float*>(sg.out) + (size_t)tok * sg.n;
+                            o[row0] = tot[r][j];
+                            o[row1] = tot[r][2 + j];
+                        }
                     }
                 }
             }
@@ -337,13 +448,16 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         return;
     }
 
-    // split-K: park partials as part[split][cta][row_in_cta (128)][tok (8)], then the last CTA of
+    // split-K: park partials as part[split][cta][row_in_cta (256)][tok (8)], then the last CTA of
     // this column of the grid sums the splits in index order.
     float* mypart = a.part + ((size_t)split * gridDim.x + blockIdx.x) * (ROWS_PER_CTA * GEMV_MAX_M);
-    {
-        const int lr0 = warp * TILE_ROWS + g, lr1 = lr0 + 8;
-        *reinterpret_cast<float2*>(mypart + lr0 * GEMV_MAX_M + 2 * t) = make_float2(tot[0], tot[1]);
-        *reinterpret_cast<float2*>(mypart + lr1 * GEMV_MAX_M + 2 * t) = make_float2(tot[2], tot[3]);
+#pragma unroll
+    for (int r = 0; r < RB_PER_WARP; ++r) {
+        if (r < nvalid) {
+            const int lr0 = (rbw0 + r) * TILE_ROWS + g, lr1 = lr0 + 8;
+            *reinterpret_cast<float2*>(mypart + lr0 * GEMV_MAX_M + 2 * t) = make_float2(tot[r][0], tot[r][1]);
+            *reinterpret_cast<float2*>(mypart + lr1 * GEMV_MAX_M + 2 * t) = make_float2(tot[r][2], tot[r][3]);
+        }
     }
     __threadfence();
     __syncthreads();
@@ -356,7 +470,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         return;
     }
     __threadfence();
-    const int nrows = min(ROWS_PER_CTA, sg.n - ((int)blockIdx.x - sg.cta0) * ROWS_PER_CTA);
+    const int nrows = nrbv * TILE_ROWS;
     for (int i = threadIdx.x; i < ROWS_PER_CTA * (GEMV_MAX_M / 2); i += blockDim.x) {
         // one thread sums a (row, token pair): consecutive threads read consecutive float2
         const int lr = i / (GEMV_MAX_M / 2), tp = i % (GEMV_MAX_M / 2);
@@ -364,12 +478,13 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
             const float* src = a.part + (size_t)blockIdx.x * (ROWS_PER_CTA * GEMV_MAX_M) + lr * GEMV_MAX_M + 2 * tp;
             const size_t stride = (size_t)gridDim.x * (ROWS_PER_CTA * GEMV_MAX_M);
             float2 sum = make_float2(0.f, 0.f);
+#pragma unroll 8
             for (int s = 0; s < a.ksplit; ++s) {
                 const float2 v = __ldcg(reinterpret_cast<const float2*>(src + s * stride));
                 sum.x += v.x;
                 sum.y += v.y;
             }
-            const int row = ((int)blockIdx.x - sg.cta0) * ROWS_PER_CTA + lr;
+            const int row = rb_cta0 * TILE_ROWS + lr;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int tok = 2 * tp + j;
@@ -399,7 +514,7 @@ int gemv_plan_ctas(GemvArgs& a) {
     for (int i = 0; i < a.nseg; ++i) {
         a.seg[i].cta0 = ctas;
         const int nrb = a.seg[i].n / TILE_ROWS;
-        ctas += (nrb + GEMV_WARPS - 1) / GEMV_WARPS;
+        ctas += (nrb + CTA_RB - 1) / CTA_RB;
     }
     return ctas;
 }
@@ -414,12 +529,12 @@ size_t gemv_part_floats(int grid_x, int ksplit) {
 
 // Split-K chosen by a small cost model instead of a fixed target (the reference sizes its split for a
 // 70-SM part: crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:3-20).  For every candidate the
-// time is  waves x (largest split + fixed per-CTA cost), with all CTAs that fit resident at once sharing
-// an SM's bandwidth; the cheapest wins, ties to fewer splits (fewer partials to reduce).
+// time is  (CTAs on the busiest SM) x (largest split + fixed per-CTA cost), all resident CTAs of an SM
+// sharing its bandwidth; the cheapest wins, ties to fewer splits (fewer partials to reduce).
 int gemv_pick_ksplit(int grid_x, int k, int group, int m, int sm_count, int max_ctas_per_sm, int stages) {
     const int unit = group > TILE_K ? group : TILE_K;
     const int units = k / unit;
-    const double fixed = 3.0 * (128.0 / unit);  // per-CTA prologue + reduce, in units of work
+    const double fixed = 4.0 * (128.0 / unit);  // per-CTA prologue + reduce, in units of work
     int best = 1;
     double best_cost = 1e30;
     for (int ks = 1; ks <= units && ks <= 64; ++ks) {
@@ -435,7 +550,6 @@ int gemv_pick_ksplit(int grid_x, int k, int group, int m, int sm_count, int max_
         const long long ctas = (long long)grid_x * ks;
         const long long slots = (long long)sm_count * ctas_per_sm;
         const long long waves = (ctas + slots - 1) / slots;
-        // CTAs on the busiest SM in the last wave
         const long long last = ctas - (waves - 1) * slots;
         const long long busiest = (last + sm_count - 1) / sm_count;
         const double cost = ((waves - 1) * ctas_per_sm + busiest) * (per_split + fixed);
@@ -452,19 +566,37 @@ cudaError_t gemv_init_device() {
 #define W4_SET(K) \
     e = cudaFuncSetAttribute(K, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_SMEM_LIMIT); \
     if (e != cudaSuccess) return e;
-    W4_SET((gemv_w4a16_kernel<128, true>))
-    W4_SET((gemv_w4a16_kernel<128, false>))
-    W4_SET((gemv_w4a16_kernel<32, true>))
-    W4_SET((gemv_w4a16_kernel<32, false>))
+    W4_SET((gemv_w4a16_kernel<128, true, 8>))
+    W4_SET((gemv_w4a16_kernel<128, false, 8>))
+    W4_SET((gemv_w4a16_kernel<32, true, 8>))
+    W4_SET((gemv_w4a16_kernel<32, false, 8>))
+    W4_SET((gemv_w4a16_kernel<128, true, 16>))
+    W4_SET((gemv_w4a16_kernel<128, false, 16>))
+    W4_SET((gemv_w4a16_kernel<32, true, 16>))
+    W4_SET((gemv_w4a16_kernel<32, false, 16>))
 #undef W4_SET
     return cudaSuccess;
+}
+
+template <int CW>
+static cudaError_t launch_gemv_cw(const GemvArgs& a, const SmemPlan& p, cudaLaunchConfig_t& cfg) {
+    cfg.blockDim = dim3((CW + 1) * 32);
+    if (a.group == 128) {
+        if (a.subnormal) {
+            return cudaLaunchKernelEx(&cfg, gemv_w4a16_kernel<128, true, CW>, a, p);
+        }
+        return cudaLaunchKernelEx(&cfg, gemv_w4a16_kernel<128, false, CW>, a, p);
+    }
+    if (a.subnormal) {
+        return cudaLaunchKernelEx(&cfg, gemv_w4a16_kernel<32, true, CW>, a, p);
+    }
+    return cudaLaunchKernelEx(&cfg, gemv_w4a16_kernel<32, false, CW>, a, p);
 }
 
 cudaError_t launch_gemv(const GemvArgs& a, int grid_x, cudaStream_t st) {
     const SmemPlan p = make_plan(a.k, a.group, a.m, a.ksplit, a.ring_stages);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid_x, a.ksplit);
-    cfg.blockDim = dim3(GEMV_WARPS * 32);
     cfg.dynamicSmemBytes = p.total;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -472,16 +604,7 @@ cudaError_t launch_gemv(const GemvArgs& a, int grid_x, cudaStream_t st) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.pdl ? 1 : 0;
-    if (a.group == 128) {
-        if (a.subnormal) {
-            return cudaLaunchKernelEx(&cfg, gemv_w4a16_kernel<128, true>, a, p);
-        }
-        return cudaLaunchKernelEx(&cfg, gemv_w4a16_kernel<128, false>, a, p);
-    }
-    if (a.subnormal) {
-        return cudaLaunchKernelEx(&cfg, gemv_w4a16_kernel<32, true>, a, p);
-    }
-    return cudaLaunchKernelEx(&cfg, gemv_w4a16_kernel<32, false>, a, p);
+    return a.cons_warps == 16 ? launch_gemv_cw<16>(a, p, cfg) : launch_gemv_cw<8>(a, p, cfg);
 }
 
 }  // namespace w4

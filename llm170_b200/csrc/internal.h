@@ -22,7 +22,6 @@ void launch_dequant(const uint32_t* qt, const uint16_t* stl, void* out, int n, i
 // ---- gemv.cu ---------------------------------------------------------------------------------
 constexpr int GEMV_MAX_SEG = 4;
 constexpr int GEMV_MAX_M = 8;
-constexpr int GEMV_WARPS = 8;  // row blocks per CTA
 
 struct GemvSeg {
     const uint4* qt;
@@ -41,10 +40,13 @@ struct GemvArgs {
     int out_f16;
     int ksplit;
     const uint16_t* x;  // f16 [m][k]
-    float* part;        // [ksplit][grid_x][GEMV_WARPS*16][GEMV_MAX_M] partial sums (ksplit > 1)
+    float* part;        // [ksplit][grid_x][256][GEMV_MAX_M] partial sums (ksplit > 1)
     unsigned* counters; // [grid_x], zero on entry, left zero on exit
     int subnormal;      // 1: feed raw nibbles as f16 subnormals and fix up per group (default); 0: exact nibble-8
+    int cons_warps;     // consumer warps per CTA: 8 (two row blocks each) or 16 (one each)
     int ring_stages;    // 2 KB chunks in flight per warp (2..4)
+    long long* dbg;     // optional timeline buffer (diagnostic), CTA (0,0) only
+    int dbg_seq;        // launch sequence number (slot for the per-launch start/end stamps)
     int pdl;            // 1: launch with programmatic stream serialization (overlaps the previous kernel's tail)
     int* status;        // device word that records the first bounded wait that expired
 };

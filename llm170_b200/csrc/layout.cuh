@@ -6,7 +6,7 @@
 // host (crates/core/src/marlin.rs:2-43, [K/16][N/64] tiles of 128 words).  This library keeps ONE
 // device copy in a different tiling chosen for B200:
 //
-//   qt : u32 [N/16][K/64][32 lanes][4 words]            (512 B per 16-row x 64-k tile)
+//   qt : u32 [K/64][N/16][32 lanes][4 words]            (512 B per 16-row x 64-k tile, k-block major)
 //   st : f16 [N/16][K/group][8][2]                      (pair j = scales of rows j and j+8)
 //
 // Inside a tile, lane = 4*g + t (g = 0..7, t = 0..3) and word w = 2*p + h (p, h in {0,1}) hold
@@ -19,8 +19,10 @@
 // in that order, the four half2 registers a0..a3 of an m16n8k16 A fragment whose 16 rows are the
 // tile's rows -- and, for the GEMM, one lane's 16 bytes expand to four whole 16-byte chunks
 // (8 consecutive k of one row) of a 128B-swizzled K-major shared-memory operand.
-// A warp reads a tile with one 128-bit load per lane, fully coalesced; a row block's tiles are
-// contiguous along K, so each warp streams sequential memory.
+// A warp reads a tile with one 128-bit load per lane, fully coalesced.  Tiles are ordered k-block
+// major: the tiles of neighbouring row blocks at one k-block are contiguous, so a CTA that owns R
+// row blocks fetches R*512 contiguous bytes per k-block with ONE bulk copy (8 KB for the GEMM's 256-row
+// tile and for the GEMV's 256-row CTA), and the CTAs running at any moment sweep a narrow band of memory.
 #pragma once
 #include <cstddef>
 #include <cstdint>
@@ -39,7 +41,7 @@ __host__ __device__ inline bool shape_ok(int n, int k, int group) {
 }
 
 // Index of the packed word that holds element (row, kk), and the nibble position inside it.
-__host__ __device__ inline size_t word_index(int row, int kk, int k_total, int* nib_pos) {
+__host__ __device__ inline size_t word_index(int row, int kk, int n_total, int* nib_pos) {
     const int rb = row / TILE_ROWS, rr = row % TILE_ROWS;
     const int g = rr & 7, hi_row = rr >> 3;
     const int kb = kk / TILE_K, kr = kk % TILE_K;
@@ -47,7 +49,7 @@ __host__ __device__ inline size_t word_index(int row, int kk, int k_total, int* 
     // e: 0 -> pos 0, 1 -> pos 4, 2 -> pos 2, 3 -> pos 6 ; rows r1 shift by one position
     const int base = ((e & 1) << 2) | (e & 2);
     *nib_pos = base + hi_row;
-    const size_t tile = (size_t)rb * (size_t)(k_total / TILE_K) + (size_t)kb;
+    const size_t tile = (size_t)kb * (size_t)(n_total / TILE_ROWS) + (size_t)rb;
     return tile * TILE_WORDS + (size_t)(4 * g + t) * 4 + (size_t)(2 * p + h);
 }
 

@@ -29,12 +29,12 @@ struct WordCoord {
     int r0, kbase;
 };
 
-__device__ __forceinline__ WordCoord coord_of(size_t widx, int nkb) {
+__device__ __forceinline__ WordCoord coord_of(size_t widx, int nrb) {
     const int w = (int)(widx & 3);
     const int lane = (int)((widx >> 2) & 31);
     const size_t tile = widx >> 7;
-    const int kb = (int)(tile % (size_t)nkb);
-    const int rb = (int)(tile / (size_t)nkb);
+    const int rb = (int)(tile % (size_t)nrb);
+    const int kb = (int)(tile / (size_t)nrb);
     const int g = lane >> 2, t = lane & 3, p = w >> 1, h = w & 1;
     WordCoord c;
     c.r0 = rb * TILE_ROWS + g;
@@ -44,10 +44,10 @@ __device__ __forceinline__ WordCoord coord_of(size_t widx, int nkb) {
 
 __global__ void repack_q_kernel(const uint32_t* __restrict__ q, uint32_t* __restrict__ qt, int n, int k) {
     const size_t total = (size_t)n * (size_t)(k / 8);
-    const int nkb = k / TILE_K, k8 = k / 8;
+    const int nrb = n / TILE_ROWS, k8 = k / 8;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
-        const WordCoord c = coord_of(i, nkb);
+        const WordCoord c = coord_of(i, nrb);
         const int sh = 4 * (c.kbase & 7);
         const uint32_t a = (q[(size_t)c.r0 * k8 + (c.kbase >> 3)] >> sh) & 0xFFFFu;
         const uint32_t b = (q[(size_t)(c.r0 + 8) * k8 + (c.kbase >> 3)] >> sh) & 0xFFFFu;
@@ -63,8 +63,8 @@ __global__ void unpack_q_kernel(const uint32_t* __restrict__ qt, uint32_t* __res
          i += (size_t)gridDim.x * blockDim.x) {
         const int row = (int)(i / (size_t)k8), kw = (int)(i % (size_t)k8);
         int pos0, pos1;
-        const size_t w0 = word_index(row, kw * 8, k, &pos0);
-        const size_t w1 = word_index(row, kw * 8 + 4, k, &pos1);
+        const size_t w0 = word_index(row, kw * 8, n, &pos0);
+        const size_t w1 = word_index(row, kw * 8 + 4, n, &pos1);
         const uint32_t lo = gather4(qt[w0] >> (4 * (pos0 & 1)));
         const uint32_t hi = gather4(qt[w1] >> (4 * (pos1 & 1)));
         q[i] = lo | (hi << 16);
@@ -119,10 +119,10 @@ template <bool OUT_F16>
 __global__ void dequant_kernel(const uint32_t* __restrict__ qt, const uint16_t* __restrict__ stl,
                                void* __restrict__ out, int n, int k, int group) {
     const size_t total = (size_t)n * (size_t)(k / 8);
-    const int nkb = k / TILE_K, ng = k / group;
+    const int nrb = n / TILE_ROWS, ng = k / group;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
-        const WordCoord c = coord_of(i, nkb);
+        const WordCoord c = coord_of(i, nrb);
         const uint32_t w = qt[i];
         const int rb = c.r0 / TILE_ROWS, g = c.r0 % TILE_ROWS;
         const int grp = c.kbase / group;

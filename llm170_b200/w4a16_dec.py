@@ -74,6 +74,11 @@ class W4a16Dec:
     def sync(self):
         self._ck(self._L.w4a16_sync(self._h))
 
+    def debug_timeline(self, slots: int = 8192) -> np.ndarray:
+        out = np.zeros(slots, np.int64)
+        self._ck(self._L.w4a16_debug_timeline(self._h, out.ctypes.data, slots))
+        return out
+
     def kernel_status(self):
         """Raises if a kernel gave up on a bounded wait since the last check."""
         self._ck(self._L.w4a16_kernel_status(self._h))

@@ -100,6 +100,6 @@ def test_layout_word_index_is_a_bijection():
             kb, kr = divmod(kk, 64)
             p, t, h, e = kr >> 5, (kr >> 3) & 3, (kr >> 2) & 1, kr & 3
             pos = (((e & 1) << 2) | (e & 2)) + hi
-            w = (rb * (k // 64) + kb) * 128 + (4 * g + t) * 4 + 2 * p + h
+            w = (kb * (n // 16) + rb) * 128 + (4 * g + t) * 4 + 2 * p + h
             seen.add((w, pos))
     assert len(seen) == n * k and max(w for w, _ in seen) == n * k // 8 - 1
