@@ -138,6 +138,37 @@ W4A16_API int w4a16_lin_forward_host(w4a16_dec* dec, const char* name, const voi
 W4A16_API int w4a16_gptq4_gemm(w4a16_dec* dec, const void* x16_host, int t, const void* q_host, const void* s_host,
                      int n, int k, int group, int scale_bf16, float* out_host);
 
+/* ---- MoE ---------------------------------------------------------------------------------- */
+
+/* W4a16Dec::set_moe (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:795-812): expert count, top-k,
+ * expert intermediate size, hidden size and quantisation group of the expert linears. The last two
+ * arguments name the experts resident on THIS decoder, [expert_first, expert_first+expert_count):
+ * all of them on one GPU, 128/G per GPU under expert parallelism (the reference keeps all experts on
+ * one device: crates/backend-gpu/src/rawcuda/w4a16_dec/moe/mod.rs:77-101). */
+W4A16_API int w4a16_set_moe(w4a16_dec* dec, int n_experts, int top_k, int moe_ffn, int hidden, int group,
+                            int expert_first, int expert_count);
+/* upload_experts_resident_streamed + build_marlin_moe_arenas
+ * (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:1021-1082,1116-1235): the local experts of one
+ * layer from HOST memory, in the boundary format, stacked expert-major: w13 = gate rows then up rows
+ * per expert, q u32 [count][2*ffn][hidden/8], s [count][2*ffn][hidden/group]; w2 = down,
+ * q [count][hidden][ffn/8], s [count][hidden][ffn/group]. */
+W4A16_API int w4a16_upload_experts(w4a16_dec* dec, int layer, const void* w13_q, const void* w13_s, const void* w2_q,
+                                   const void* w2_s, int scale_bf16);
+/* Same with the four arrays already in DEVICE memory (the reference has no such variant). */
+W4A16_API int w4a16_upload_experts_dev(w4a16_dec* dec, int layer, const void* w13_q, const void* w13_s,
+                                       const void* w2_q, const void* w2_s, int scale_bf16);
+/* w4a16_moe_topk_t (crates/backend-gpu/src/rawcuda/assets/moe.cu:686-759; host mirror moe_topk,
+ * crates/backend-gpu/src/rawcuda/w4a16_dec/mod.rs:168-185): softmax over f32 logits [t][n_experts],
+ * top-k with lower-index tie-break, weights renormalised over the k picked. idx int32 [t][k], wt f32 [t][k]. */
+W4A16_API int w4a16_moe_topk(w4a16_dec* dec, const float* logits_dev, int* idx_dev, float* wt_dev, int t, void* stream);
+/* W4a16Dec::moe_ffn_dev_t (crates/backend-gpu/src/rawcuda/w4a16_dec/moe/mod.rs:263-447) on the resident
+ * grouped-GEMM path (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/marlin_moe.rs:290-422):
+ * y[t][hidden] = sum over the token's top-k experts of w * down_e( silu(gate_e x) * up_e x ), restricted to
+ * the local experts (under expert parallelism the caller sums y over ranks). router logits f32 [t][n_experts]
+ * come from the caller (a plain GEMM outside this path); x16 f16 [t][hidden]; y f32 or f16. */
+W4A16_API int w4a16_moe_ffn(w4a16_dec* dec, int layer, const float* router_logits_dev, const void* x16_dev, void* y_dev,
+                            int t, int out_kind, void* stream);
+
 /* ---- graph capture ----------------------------------------------------------------------- */
 
 /* CudaCtx::capture_begin / capture_end / graph_instantiate / graph_launch / graph destroy

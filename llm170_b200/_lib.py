@@ -38,6 +38,11 @@ _SIGS = {
     "w4a16_sk_multi_dev": (_i, [_vp, C.POINTER(C.c_char_p), _i, _vp, C.POINTER(_vp), _i, _i, _vp]),
     "w4a16_lin_forward_host": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i]),
     "w4a16_gptq4_gemm": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "w4a16_set_moe": (_i, [_vp] + [_i] * 7),
+    "w4a16_upload_experts": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i]),
+    "w4a16_upload_experts_dev": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _i]),
+    "w4a16_moe_topk": (_i, [_vp, _vp, _vp, _vp, _i, _vp]),
+    "w4a16_moe_ffn": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _vp]),
     "w4a16_capture_begin": (_i, [_vp]),
     "w4a16_capture_end": (_i, [_vp, C.POINTER(_vp)]),
     "w4a16_graph_launch": (_i, [_vp, _vp]),

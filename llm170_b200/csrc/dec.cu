@@ -207,10 +207,6 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
 using w4::Dec;
 using w4::Lin;
 
-struct w4a16_dec {
-    Dec d;
-};
-
 static cudaStream_t pick_stream(w4a16_dec* dec, void* stream) {
     return stream ? (cudaStream_t)stream : dec->d.stream;
 }
@@ -290,6 +286,7 @@ void w4a16_dec_free(w4a16_dec* dec) {
     Dec& d = dec->d;
     cudaSetDevice(d.device);
     cudaDeviceSynchronize();
+    d.free_moe();
     for (auto& kv : d.lins) {
         d.free_lin(kv.second);
     }

@@ -16,6 +16,26 @@ struct Lin {
     size_t bytes = 0;
 };
 
+// MoE configuration (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:795-812) and device scratch.
+struct MoeCfg {
+    bool set = false;
+    int n_experts = 0, top_k = 0, ffn = 0, hidden = 0, group = 32;
+    int e0 = 0, e1 = 0;  // experts [e0, e1) are resident on this decoder (expert parallelism)
+};
+
+struct MoeBufs {
+    int* idx = nullptr;          // [slots] expert of each (token, j) slot
+    float* wt = nullptr;         // [slots] routing weight
+    int *cnt = nullptr, *off = nullptr, *cursor = nullptr;  // [n_experts]
+    int *pos_of_slot = nullptr, *slot_of_pos = nullptr;     // [slots]
+    int *tile_expert = nullptr, *tile_row0 = nullptr, *tile_rows = nullptr;  // [max_tiles]
+    int *n_tiles = nullptr, *n_rows = nullptr;
+    float* row_w = nullptr;      // [slots] routing weight in sorted order
+    void *xs = nullptr, *c13 = nullptr, *act = nullptr, *c2 = nullptr;  // f16 [slots][h | 2f | f | h]
+    size_t cap_tokens = 0;
+    int max_tiles = 0;
+};
+
 struct Dec {
     int device = 0;
     int sm_count = 148;
@@ -56,6 +76,18 @@ struct Dec {
     int gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, int t, int out_kind,
              cudaStream_t st);
     int gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaStream_t st);
+    int gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int n_per_expert, const MoeBufs& b,
+                     int max_tiles, const float* row_w, cudaStream_t st);
+    MoeCfg moe;
+    MoeBufs mb;
+    int ensure_moe(int t, cudaStream_t st);
+    void free_moe();
+    int moe_ffn(int layer, const float* logits, const void* x16, void* y, int t, int out_kind, cudaStream_t st);
 };
 
 }  // namespace w4
+
+// The opaque handle of the C ABI.
+struct w4a16_dec {
+    w4::Dec d;
+};

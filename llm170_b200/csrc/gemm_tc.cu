@@ -49,6 +49,15 @@ struct GemmArgs {
     int m, n, k;
     int out_f16;
     int m_tiles, n_tiles;
+    int nrb_w;       // 16-row blocks of the resident weight matrix (= n/16; experts stacked along n when grouped)
+    // grouped (MoE) mode: m-tiles come from a device table, one expert's weights per tile
+    int grouped;
+    const int* tile_expert;
+    const int* tile_row0;
+    const int* tile_rows;
+    const int* num_tiles;
+    int expert0;          // first expert held by this decoder
+    const float* row_w;   // optional per-row factor applied in the epilogue (routing weight)
     int* status;  // 0 = ok; otherwise code<<16 | detail of the first wait that expired
     long long* dbg;  // optional timeline buffer (diagnostic), CTA 0 only
 };
@@ -114,20 +123,31 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
     const uint32_t accum_bar = bars + 8u * (2 * NT + 2 * NB);
 
     // tile of this CTA (groups of GROUP_M m-tiles walk the n-tiles together)
-    int m_tile, n_tile;
-    {
+    int m0, n0, rb0, rows_valid;
+    if (a.grouped) {
+        // consecutive CTAs walk the m-tiles of one n-tile: neighbours share an expert's weight tile in L2
+        const int mt = blockIdx.x % a.m_tiles, n_tile = blockIdx.x / a.m_tiles;
+        if (mt >= *a.num_tiles) {
+            return;  // the table is sized for the worst case
+        }
+        m0 = a.tile_row0[mt];
+        rows_valid = a.tile_rows[mt];
+        n0 = n_tile * BN;
+        rb0 = ((a.tile_expert[mt] - a.expert0) * a.n + n0) / TILE_ROWS;
+    } else {
+        // groups of GROUP_M m-tiles walk the n-tiles together
         const int tile = blockIdx.x;
         const int per_group = GROUP_M * a.n_tiles;
         const int grp = tile / per_group;
         const int first_m = grp * GROUP_M;
         const int gsz = min(GROUP_M, a.m_tiles - first_m);
         const int rem = tile - grp * per_group;
-        m_tile = first_m + rem % gsz;
-        n_tile = rem / gsz;
+        m0 = (first_m + rem % gsz) * BM;
+        n0 = (rem / gsz) * BN;
+        rb0 = n0 / TILE_ROWS;
+        rows_valid = min(BM, a.m - m0);
     }
-    const int m0 = m_tile * BM, n0 = n_tile * BN;
     const int nkb = a.k / BK;
-    const int rb0 = n0 / TILE_ROWS;
     const int nrbv = min(BN, a.n - n0) / TILE_ROWS;  // valid 16-row blocks in this tile
 
     const bool stamp = a.dbg != nullptr && blockIdx.x == 0;
@@ -173,7 +193,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                 mbar_expect_tx(full_bar(s), A_BYTES + nrbv * (TILE_WORDS * 4));
                 tma_load_2d(a_addr(s), &tmap_x, it * BK, m0, full_bar(s));
                 // the tile's row blocks are contiguous at one k-block (k-block-major layout): one copy
-                bulk_load(raw_addr(s), a.qt + ((size_t)it * (a.n / TILE_ROWS) + rb0) * TILE_WORDS,
+                bulk_load(raw_addr(s), a.qt + ((size_t)it * a.nrb_w + rb0) * TILE_WORDS,
                           nrbv * (TILE_WORDS * 4), full_bar(s));
             }
         }
@@ -287,12 +307,20 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int quad = warp & 3;
-                const int row = m0 + quad * 32 + lane;
+                const int row_l = quad * 32 + lane;
+                const int row = m0 + row_l;
+                const float rw = (a.row_w != nullptr && row_l < rows_valid) ? a.row_w[row] : 1.0f;
                 const int ncols = min(BN, a.n - n0);
                 for (int c0 = 0; c0 < ncols; c0 += 32) {
                     uint32_t v[32];
                     tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
-                    if (row < a.m) {
+                    if (row_l < rows_valid) {
+                        if (a.row_w != nullptr) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                v[i] = __float_as_uint(__uint_as_float(v[i]) * rw);
+                            }
+                        }
                         if (a.out_f16) {
                             __half* o = reinterpret_cast<__half*>(a.out) + (size_t)row * a.n + n0 + c0;
 #pragma unroll
@@ -393,6 +421,11 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.out_f16 = out_kind == W4A16_OUT_F16;
     a.m_tiles = (t + BM - 1) / BM;
     a.n_tiles = (l->n + BN - 1) / BN;
+    a.nrb_w = l->n / TILE_ROWS;
+    a.grouped = 0;
+    a.tile_expert = a.tile_row0 = a.tile_rows = a.num_tiles = nullptr;
+    a.expert0 = 0;
+    a.row_w = nullptr;
     a.status = gemm_status;
     a.dbg = dbg_buf;
     const int grid = a.m_tiles * a.n_tiles;
@@ -404,6 +437,59 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         return cuda_fail("launch gemm", e);
+    }
+    launches++;
+    return 0;
+}
+
+// Grouped GEMM over expert segments: `l` stacks the local experts along n (n_per_expert rows each);
+// xs holds the gathered rows (sorted by expert), the m-tile table lives on the device (moe.cu).
+int Dec::gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int n_per_expert, const MoeBufs& b,
+                      int max_tiles, const float* row_w, cudaStream_t st) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) {
+        return fail("w4a16 gemm: cuTensorMapEncodeTiled is not available from the driver");
+    }
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)l->k, (cuuint64_t)xs_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)l->k * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(xs), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) {
+        return fail("w4a16 gemm: cuTensorMapEncodeTiled failed (%d)", (int)cr);
+    }
+    GemmArgs a;
+    a.qt = l->qt;
+    a.st = (const uint32_t*)l->st;
+    a.out = out;
+    a.m = xs_rows;
+    a.n = n_per_expert;
+    a.k = l->k;
+    a.out_f16 = 1;
+    a.m_tiles = max_tiles;
+    a.n_tiles = (n_per_expert + BN - 1) / BN;
+    a.nrb_w = l->n / TILE_ROWS;
+    a.grouped = 1;
+    a.tile_expert = b.tile_expert;
+    a.tile_row0 = b.tile_row0;
+    a.tile_rows = b.tile_rows;
+    a.num_tiles = b.n_tiles;
+    a.expert0 = moe.e0;
+    a.row_w = row_w;
+    a.status = gemm_status;
+    a.dbg = nullptr;
+    const int grid = a.m_tiles * a.n_tiles;
+    if (l->group == 128) {
+        gemm_w4a16_tc_kernel<128><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map, a);
+    } else {
+        gemm_w4a16_tc_kernel<32><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map, a);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        return cuda_fail("launch grouped gemm", e);
     }
     launches++;
     return 0;

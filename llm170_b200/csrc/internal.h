@@ -65,4 +65,13 @@ cudaError_t gemv_init_device();
 // Raises the dynamic shared-memory limit of the tensor-core GEMM kernels on the current device.
 cudaError_t gemm_init_device();
 
+// ---- moe.cu ----------------------------------------------------------------------------------
+struct MoeBufs;
+void launch_moe_topk(const float* logits, int* idx, float* wt, int t, int n_exp, int k, cudaStream_t st);
+// histogram -> offsets + m-tile table (tiles of `bm` rows) -> placement of the local experts' slots
+void launch_moe_align(const MoeBufs& b, int ns, int n_exp, int e0, int e1, int bm, cudaStream_t st);
+void launch_moe_gather(const void* x, const MoeBufs& b, int ns, int k, int h, cudaStream_t st);
+void launch_moe_act(const MoeBufs& b, int rows_upper, int ffn, cudaStream_t st);
+void launch_moe_combine(const MoeBufs& b, void* out, int t, int h, int k, int out_f16, cudaStream_t st);
+
 }  // namespace w4

@@ -1,0 +1,237 @@
+// MoE routing, dispatch and combine around the grouped W4A16 GEMM.
+//
+// Follows the reference's resident-expert path (crates/backend-gpu/src/rawcuda/w4a16_dec/moe/mod.rs:263-447,
+// crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/marlin_moe.rs:290-422):
+//   router top-k -> group the T*k (token, expert) slots by expert -> grouped GEMM-1 over gate|up ->
+//   SiLU(gate)*up -> grouped GEMM-2 over down, scaled by the routing weight -> sum over k.
+// Kernels here: top-k (crates/backend-gpu/src/rawcuda/assets/moe.cu:686-759), the expert histogram / offsets /
+// placement that replace the single-block counting sort (crates/backend-gpu/src/rawcuda/assets/gptq4.cu:376-413,
+// crates/backend-gpu/src/rawcuda/assets/moe.cu:1599-1633), the row gather, the activation
+// (crates/backend-gpu/src/rawcuda/assets/moe.cu:1649-1660) and the top-k sum (:1662-1674).
+// Slots of one expert are placed with an atomic cursor, so their order inside an expert's segment is
+// not fixed; every output row is computed independently and the final sum runs over k in index order,
+// so results do not depend on that order.
+#include <cuda_fp16.h>
+
+#include "dec.h"
+
+namespace w4 {
+
+namespace {
+
+constexpr int TOPK_WARPS = 8;
+
+// One warp per token. p_e = exp(l_e - max); pick k times the largest remaining p (ties: lower index);
+// weights = p / sum of the picked p. Same selection rule as select_topk
+// (crates/core/src/qwen35/stages/moe.rs:8-31), which divides by the full softmax sum first; that factor cancels.
+__global__ void moe_topk_kernel(const float* __restrict__ lg, int* __restrict__ idx, float* __restrict__ wt, int t,
+                                int n, int k) {
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ti = blockIdx.x * TOPK_WARPS + w;
+    if (ti >= t) {
+        return;
+    }
+    const float* l = lg + (size_t)ti * n;
+    float mx = -INFINITY;
+    for (int i = lane; i < n; i += 32) {
+        mx = fmaxf(mx, l[i]);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    float pv[32];
+    int cnt = 0;
+    for (int i = lane; i < n; i += 32) {
+        pv[cnt++] = expf(l[i] - mx);
+    }
+    unsigned used = 0u;
+    float wsum = 0.f;
+    float mine = 0.f;  // lane r keeps the r-th picked weight
+    for (int r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int j = 0; j < cnt; ++j) {
+            const int e = lane + 32 * j;
+            if (!(used & (1u << j)) && (pv[j] > bv || (pv[j] == bv && e < bi))) {
+                bv = pv[j];
+                bi = e;
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+        if ((bi & 31) == lane) {
+            used |= 1u << (bi >> 5);
+        }
+        if (lane == 0) {
+            idx[(size_t)ti * k + r] = bi;
+        }
+        if (lane == (r & 31)) {
+            mine = bv;
+        }
+        wsum += bv;
+    }
+    if (lane < k) {
+        wt[(size_t)ti * k + lane] = mine / wsum;
+    }
+}
+
+__global__ void moe_count_kernel(const int* __restrict__ idx, int* __restrict__ cnt, int ns, int e0, int e1) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ns; i += gridDim.x * blockDim.x) {
+        const int e = idx[i];
+        if (e >= e0 && e < e1) {
+            atomicAdd(cnt + e, 1);
+        }
+    }
+}
+
+// One block: exclusive offsets of the local experts' segments and the m-tile table of the grouped GEMM:
+// tile i -> (expert, first sorted row, valid rows).  Also clears the placement cursors.
+__global__ void moe_offsets_kernel(const int* __restrict__ cnt, int* __restrict__ off, int* __restrict__ cursor,
+                                   int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                   int* __restrict__ tile_rows, int* __restrict__ n_tiles, int* __restrict__ n_rows,
+                                   int n_exp, int e0, int e1, int bm) {
+    if (threadIdx.x == 0) {
+        int pos = 0, nt = 0;
+        for (int e = e0; e < e1; ++e) {
+            const int c = cnt[e];
+            off[e] = pos;
+            for (int r = 0; r < c; r += bm) {
+                tile_expert[nt] = e;
+                tile_row0[nt] = pos + r;
+                tile_rows[nt] = min(bm, c - r);
+                ++nt;
+            }
+            pos += c;
+        }
+        *n_tiles = nt;
+        *n_rows = pos;
+    }
+    for (int e = threadIdx.x; e < n_exp; e += blockDim.x) {
+        cursor[e] = 0;
+    }
+}
+
+__global__ void moe_place_kernel(const int* __restrict__ idx, const int* __restrict__ off, int* __restrict__ cursor,
+                                 int* __restrict__ pos_of_slot, int* __restrict__ slot_of_pos, int ns, int e0, int e1) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ns; i += gridDim.x * blockDim.x) {
+        const int e = idx[i];
+        int pos = -1;
+        if (e >= e0 && e < e1) {
+            pos = off[e] + atomicAdd(cursor + e, 1);
+            slot_of_pos[pos] = i;
+        }
+        pos_of_slot[i] = pos;  // -1: the expert lives on another rank
+    }
+}
+
+// xs[pos][:] = x[slot / k][:]  (f16 rows of h), 16 bytes per thread
+__global__ void moe_gather_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs, const int* __restrict__ pos_of_slot,
+                                  int ns, int k, int h8) {
+    const size_t total = (size_t)ns * h8;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int slot = (int)(i / h8), c = (int)(i % h8);
+        const int pos = pos_of_slot[slot];
+        if (pos >= 0) {
+            xs[(size_t)pos * h8 + c] = x[(size_t)(slot / k) * h8 + c];
+        }
+    }
+}
+
+// act[pos][c] = f16( silu(gate) * up ),  c13 = [rows][2*ffn] with gate in the first half
+__global__ void moe_act_silu_kernel(const __half* __restrict__ c13, __half* __restrict__ act, const int* __restrict__ n_rows,
+                                    int ffn) {
+    const size_t total = (size_t)(*n_rows) * ffn;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / ffn, c = i % ffn;
+        const float g = __half2float(c13[r * 2 * ffn + c]);
+        const float u = __half2float(c13[r * 2 * ffn + ffn + c]);
+        act[i] = __float2half_rn((g / (1.0f + expf(-g))) * u);
+    }
+}
+
+// out[t][c] = sum_j c2[pos(t*k+j)][c]  (routing weights were applied in GEMM-2's epilogue); slots whose
+// expert is not local contribute nothing
+template <bool OUT_F16>
+__global__ void moe_combine_kernel(const __half* __restrict__ c2, void* __restrict__ out, const int* __restrict__ pos_of_slot,
+                                   int t, int h, int k) {
+    const size_t total = (size_t)t * h;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int r = (int)(i / h), c = (int)(i % h);
+        float acc = 0.f;
+        for (int j = 0; j < k; ++j) {
+            const int pos = pos_of_slot[r * k + j];
+            if (pos >= 0) {
+                acc += __half2float(c2[(size_t)pos * h + c]);
+            }
+        }
+        if (OUT_F16) {
+            ((__half*)out)[i] = __float2half_rn(acc);
+        } else {
+            ((float*)out)[i] = acc;
+        }
+    }
+}
+
+// sorted routing weight of each row (GEMM-2 multiplies by it)
+__global__ void moe_row_weight_kernel(const float* __restrict__ wt, const int* __restrict__ slot_of_pos,
+                                      const int* __restrict__ pos_of_slot, float* __restrict__ row_w, int ns) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ns; i += gridDim.x * blockDim.x) {
+        const int pos = pos_of_slot[i];
+        if (pos >= 0) {
+            row_w[pos] = wt[i];
+        }
+    }
+    (void)slot_of_pos;
+}
+
+inline int blocks_for(size_t total, int threads) {
+    size_t b = (total + threads - 1) / threads;
+    if (b > 148 * 16) {
+        b = 148 * 16;
+    }
+    return b < 1 ? 1 : (int)b;
+}
+
+}  // namespace
+
+void launch_moe_topk(const float* logits, int* idx, float* wt, int t, int n_exp, int k, cudaStream_t st) {
+    moe_topk_kernel<<<(t + TOPK_WARPS - 1) / TOPK_WARPS, TOPK_WARPS * 32, 0, st>>>(logits, idx, wt, t, n_exp, k);
+}
+
+void launch_moe_align(const MoeBufs& b, int ns, int n_exp, int e0, int e1, int bm, cudaStream_t st) {
+    cudaMemsetAsync(b.cnt, 0, (size_t)n_exp * sizeof(int), st);
+    moe_count_kernel<<<blocks_for(ns, 256), 256, 0, st>>>(b.idx, b.cnt, ns, e0, e1);
+    moe_offsets_kernel<<<1, 256, 0, st>>>(b.cnt, b.off, b.cursor, b.tile_expert, b.tile_row0, b.tile_rows, b.n_tiles,
+                                          b.n_rows, n_exp, e0, e1, bm);
+    moe_place_kernel<<<blocks_for(ns, 256), 256, 0, st>>>(b.idx, b.off, b.cursor, b.pos_of_slot, b.slot_of_pos, ns, e0, e1);
+    moe_row_weight_kernel<<<blocks_for(ns, 256), 256, 0, st>>>(b.wt, b.slot_of_pos, b.pos_of_slot, b.row_w, ns);
+}
+
+void launch_moe_gather(const void* x, const MoeBufs& b, int ns, int k, int h, cudaStream_t st) {
+    moe_gather_kernel<<<blocks_for((size_t)ns * (h / 8), 256), 256, 0, st>>>((const uint4*)x, (uint4*)b.xs, b.pos_of_slot,
+                                                                           ns, k, h / 8);
+}
+
+void launch_moe_act(const MoeBufs& b, int rows_upper, int ffn, cudaStream_t st) {
+    moe_act_silu_kernel<<<blocks_for((size_t)rows_upper * ffn, 256), 256, 0, st>>>((const __half*)b.c13, (__half*)b.act,
+                                                                                 b.n_rows, ffn);
+}
+
+void launch_moe_combine(const MoeBufs& b, void* out, int t, int h, int k, int out_f16, cudaStream_t st) {
+    const int g = blocks_for((size_t)t * h, 256);
+    if (out_f16) {
+        moe_combine_kernel<true><<<g, 256, 0, st>>>((const __half*)b.c2, out, b.pos_of_slot, t, h, k);
+    } else {
+        moe_combine_kernel<false><<<g, 256, 0, st>>>((const __half*)b.c2, out, b.pos_of_slot, t, h, k);
+    }
+}
+
+}  // namespace w4

@@ -1,0 +1,197 @@
+// Host side of the MoE path: configuration, expert residency, scratch, and the FFN call.
+// Mirrors W4a16Dec::set_moe / upload_experts_resident_streamed / build_marlin_moe_arenas
+// (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:795-812,1021-1235) and moe_ffn_dev_t
+// (crates/backend-gpu/src/rawcuda/w4a16_dec/moe/mod.rs:263-447).
+#include <cstdio>
+#include <string>
+
+#include "../../include/w4a16_b200.h"
+#include "dec.h"
+
+namespace w4 {
+
+namespace {
+constexpr int MOE_BM = 128;  // rows per m-tile of the grouped GEMM
+
+std::string w13_name(int layer) { return "\x01moe." + std::to_string(layer) + ".w13"; }
+std::string w2_name(int layer) { return "\x01moe." + std::to_string(layer) + ".w2"; }
+
+template <class T>
+cudaError_t dalloc(T** p, size_t count) {
+    return cudaMalloc((void**)p, count * sizeof(T));
+}
+}  // namespace
+
+void Dec::free_moe() {
+    void* ptrs[] = {mb.idx, mb.wt, mb.cnt, mb.off, mb.cursor, mb.pos_of_slot, mb.slot_of_pos, mb.tile_expert, mb.tile_row0,
+                    mb.tile_rows, mb.n_tiles, mb.n_rows, mb.row_w, mb.xs, mb.c13, mb.act, mb.c2};
+    for (void* p : ptrs) {
+        if (p) {
+            cudaFree(p);
+        }
+    }
+    mb = MoeBufs{};
+}
+
+// Grow-only scratch for t tokens; never grows while `st` is capturing.
+int Dec::ensure_moe(int t, cudaStream_t st) {
+    if ((size_t)t <= mb.cap_tokens) {
+        return 0;
+    }
+    if (capturing(st)) {
+        return fail("w4a16 moe: scratch too small during graph capture; run the call once before capturing");
+    }
+    cudaDeviceSynchronize();
+    free_moe();
+    const size_t slots = (size_t)t * moe.top_k;
+    const int max_tiles = (int)((slots + MOE_BM - 1) / MOE_BM) + (moe.e1 - moe.e0);
+    cudaError_t e = cudaSuccess;
+    auto ok = [&](cudaError_t r) {
+        if (e == cudaSuccess) {
+            e = r;
+        }
+    };
+    ok(dalloc(&mb.idx, slots));
+    ok(dalloc(&mb.wt, slots));
+    ok(dalloc(&mb.cnt, (size_t)moe.n_experts));
+    ok(dalloc(&mb.off, (size_t)moe.n_experts));
+    ok(dalloc(&mb.cursor, (size_t)moe.n_experts));
+    ok(dalloc(&mb.pos_of_slot, slots));
+    ok(dalloc(&mb.slot_of_pos, slots));
+    ok(dalloc(&mb.tile_expert, (size_t)max_tiles));
+    ok(dalloc(&mb.tile_row0, (size_t)max_tiles));
+    ok(dalloc(&mb.tile_rows, (size_t)max_tiles));
+    ok(dalloc(&mb.n_tiles, 1));
+    ok(dalloc(&mb.n_rows, 1));
+    ok(dalloc(&mb.row_w, slots));
+    ok(cudaMalloc(&mb.xs, slots * moe.hidden * 2));
+    ok(cudaMalloc(&mb.c13, slots * 2 * moe.ffn * 2));
+    ok(cudaMalloc(&mb.act, slots * moe.ffn * 2));
+    ok(cudaMalloc(&mb.c2, slots * moe.hidden * 2));
+    if (e != cudaSuccess) {
+        free_moe();
+        return cuda_fail("alloc moe scratch", e);
+    }
+    mb.cap_tokens = (size_t)t;
+    mb.max_tiles = max_tiles;
+    return 0;
+}
+
+int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t, int out_kind, cudaStream_t st) {
+    if (!moe.set) {
+        return fail("w4a16 moe_ffn: set_moe was not called");
+    }
+    if (t < 1) {
+        return fail("w4a16 moe_ffn: t=%d", t);
+    }
+    auto i13 = lins.find(w13_name(layer)), i2 = lins.find(w2_name(layer));
+    if (i13 == lins.end() || i2 == lins.end()) {
+        return fail("w4a16 moe_ffn: experts of layer %d are not resident", layer);
+    }
+    if (int rc = ensure_moe(t, st)) {
+        return rc;
+    }
+    const int ns = t * moe.top_k;
+    const int max_tiles = (ns + MOE_BM - 1) / MOE_BM + (moe.e1 - moe.e0);
+    launch_moe_topk(logits, mb.idx, mb.wt, t, moe.n_experts, moe.top_k, st);
+    launch_moe_align(mb, ns, moe.n_experts, moe.e0, moe.e1, MOE_BM, st);
+    launch_moe_gather(x16, mb, ns, moe.top_k, moe.hidden, st);
+    launches += 6;
+    if (int rc = gemm_grouped(&i13->second, mb.xs, ns, mb.c13, 2 * moe.ffn, mb, max_tiles, nullptr, st)) {
+        return rc;
+    }
+    launch_moe_act(mb, ns, moe.ffn, st);
+    if (int rc = gemm_grouped(&i2->second, mb.act, ns, mb.c2, moe.hidden, mb, max_tiles, mb.row_w, st)) {
+        return rc;
+    }
+    launch_moe_combine(mb, y, t, moe.hidden, moe.top_k, out_kind == W4A16_OUT_F16, st);
+    launches += 2;
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : cuda_fail("moe_ffn launch", e);
+}
+
+}  // namespace w4
+
+using w4::Dec;
+
+static cudaStream_t moe_stream(w4a16_dec* dec, void* stream) { return stream ? (cudaStream_t)stream : dec->d.stream; }
+
+extern "C" {
+
+int w4a16_set_moe(w4a16_dec* dec, int n_experts, int top_k, int moe_ffn, int hidden, int group, int expert_first,
+                  int expert_count) {
+    Dec& d = dec->d;
+    if (n_experts < 1 || n_experts > 1024 || top_k < 1 || top_k > 32 || top_k > n_experts) {
+        return d.fail("w4a16 set_moe: n_experts=%d top_k=%d unsupported (experts <= 1024, top_k <= 32)", n_experts, top_k);
+    }
+    if ((group != 32 && group != 128) || moe_ffn % 64 != 0 || hidden % 64 != 0 || moe_ffn % group != 0 ||
+        hidden % group != 0) {
+        return d.fail("w4a16 set_moe: ffn=%d hidden=%d group=%d violate the tile contract", moe_ffn, hidden, group);
+    }
+    if (expert_first < 0 || expert_count < 1 || expert_first + expert_count > n_experts) {
+        return d.fail("w4a16 set_moe: local expert range [%d,+%d) outside 0..%d", expert_first, expert_count, n_experts);
+    }
+    cudaSetDevice(d.device);
+    cudaDeviceSynchronize();
+    d.free_moe();
+    d.moe.set = true;
+    d.moe.n_experts = n_experts;
+    d.moe.top_k = top_k;
+    d.moe.ffn = moe_ffn;
+    d.moe.hidden = hidden;
+    d.moe.group = group;
+    d.moe.e0 = expert_first;
+    d.moe.e1 = expert_first + expert_count;
+    return 0;
+}
+
+static int upload_experts_impl(w4a16_dec* dec, int layer, const void* w13_q, const void* w13_s, const void* w2_q,
+                               const void* w2_s, int scale_bf16, bool on_device) {
+    Dec& d = dec->d;
+    if (!d.moe.set) {
+        return d.fail("w4a16 upload_experts: set_moe was not called");
+    }
+    const int ne = d.moe.e1 - d.moe.e0, f = d.moe.ffn, h = d.moe.hidden, g = d.moe.group;
+    const int n13 = ne * 2 * f, n2 = ne * h;
+    const std::string a = w4::w13_name(layer), b = w4::w2_name(layer);
+    if (on_device) {
+        if (int rc = w4a16_upload_lin_g_dev(dec, a.c_str(), w13_q, w13_s, n13, h, g, scale_bf16)) {
+            return rc;
+        }
+        return w4a16_upload_lin_g_dev(dec, b.c_str(), w2_q, w2_s, n2, f, g, scale_bf16);
+    }
+    if (int rc = w4a16_upload_lin_g(dec, a.c_str(), w13_q, (size_t)n13 * (h / 2), w13_s, (size_t)n13 * (h / g) * 2, n13,
+                                    h, g, scale_bf16)) {
+        return rc;
+    }
+    return w4a16_upload_lin_g(dec, b.c_str(), w2_q, (size_t)n2 * (f / 2), w2_s, (size_t)n2 * (f / g) * 2, n2, f, g,
+                              scale_bf16);
+}
+
+int w4a16_upload_experts(w4a16_dec* dec, int layer, const void* w13_q, const void* w13_s, const void* w2_q,
+                         const void* w2_s, int scale_bf16) {
+    return upload_experts_impl(dec, layer, w13_q, w13_s, w2_q, w2_s, scale_bf16, false);
+}
+
+int w4a16_upload_experts_dev(w4a16_dec* dec, int layer, const void* w13_q, const void* w13_s, const void* w2_q,
+                             const void* w2_s, int scale_bf16) {
+    return upload_experts_impl(dec, layer, w13_q, w13_s, w2_q, w2_s, scale_bf16, true);
+}
+
+int w4a16_moe_topk(w4a16_dec* dec, const float* logits_dev, int* idx_dev, float* wt_dev, int t, void* stream) {
+    Dec& d = dec->d;
+    if (!d.moe.set) {
+        return d.fail("w4a16 moe_topk: set_moe was not called");
+    }
+    w4::launch_moe_topk(logits_dev, idx_dev, wt_dev, t, d.moe.n_experts, d.moe.top_k, moe_stream(dec, stream));
+    d.launches++;
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : d.cuda_fail("moe_topk", e);
+}
+
+int w4a16_moe_ffn(w4a16_dec* dec, int layer, const float* router_logits_dev, const void* x16_dev, void* y_dev, int t,
+                  int out_kind, void* stream) {
+    return dec->d.moe_ffn(layer, router_logits_dev, x16_dev, y_dev, t, out_kind, moe_stream(dec, stream));
+}
+
+}  // extern "C"

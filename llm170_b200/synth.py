@@ -89,3 +89,12 @@ def make_linear_cuda(n: int, k: int, group: int, seed: int, device, sigma: float
     q = (nib.to(torch.int64) << shifts).sum(dim=2)
     q = torch.where(q >= 2 ** 31, q - 2 ** 32, q).to(torch.int32)
     return q.contiguous(), s16.contiguous()
+
+
+def make_experts(n_exp: int, ffn: int, hidden: int, group: int, seed: int, sigma: float = 0.02):
+    """Expert linears of one MoE layer, expert-major: w13 = gate rows then up rows [n_exp, 2*ffn, hidden],
+    w2 = down [n_exp, hidden, ffn].  Returns (w13_q, w13_s, w2_q, w2_s) in the boundary format."""
+    q13, s13 = make_linear(n_exp * 2 * ffn, hidden, group, seed, sigma)
+    q2, s2 = make_linear(n_exp * hidden, ffn, group, seed + 1, sigma)
+    return (q13.reshape(n_exp, 2 * ffn, hidden // 8), s13.reshape(n_exp, 2 * ffn, hidden // group),
+            q2.reshape(n_exp, hidden, ffn // 8), s2.reshape(n_exp, hidden, ffn // group))

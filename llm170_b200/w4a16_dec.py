@@ -214,3 +214,47 @@ class W4a16Dec:
         self._ck(self._L.w4a16_graph_step_host(
             self._h, C.c_void_p(g), x_host.data_ptr(), x_dev.data_ptr(), x_host.numel() * x_host.element_size(),
             y_dev.data_ptr(), y_host.data_ptr(), y_host.numel() * y_host.element_size()))
+
+    # -- MoE (upload.rs:795-812,1021-1235; moe/mod.rs:263-447) --------------------------------------
+    def set_moe(self, n_experts: int, top_k: int, moe_ffn: int, hidden: int, group: int = 32,
+                expert_first: int = 0, expert_count: int | None = None):
+        cnt = n_experts - expert_first if expert_count is None else expert_count
+        self._ck(self._L.w4a16_set_moe(self._h, n_experts, top_k, moe_ffn, hidden, group, expert_first, cnt))
+        self._moe = (n_experts, top_k, moe_ffn, hidden, group, expert_first, cnt)
+
+    def upload_experts(self, layer: int, w13_q, w13_s, w2_q, w2_s, scale_bf16: bool = False):
+        """Local experts of one layer from host arrays (expert-major, gate rows then up rows in w13)."""
+        if isinstance(w13_q, torch.Tensor):
+            self._ck(self._L.w4a16_upload_experts_dev(self._h, layer, w13_q.data_ptr(), w13_s.data_ptr(),
+                                                      w2_q.data_ptr(), w2_s.data_ptr(), int(scale_bf16)))
+            return
+        ne, k, f, h, g, _, cnt = self._moe
+        arrs = [np.ascontiguousarray(a) for a in (w13_q, w13_s, w2_q, w2_s)]
+        want = [cnt * 2 * f * h // 2, cnt * 2 * f * (h // g) * 2, cnt * h * f // 2, cnt * h * (f // g) * 2]
+        for a, w in zip(arrs, want):
+            if a.nbytes != w:
+                raise W4a16Error(f"upload_experts: array of {a.nbytes} bytes, expected {w}")
+        self._ck(self._L.w4a16_upload_experts(self._h, layer, *[a.ctypes.data for a in arrs], int(scale_bf16)))
+
+    def moe_topk(self, logits: torch.Tensor):
+        """moe.cu:686-759 / mod.rs:168-185: (idx int32 [t,k], wt float32 [t,k])."""
+        ne, k = self._moe[0], self._moe[1]
+        self._tensor_ok(logits, torch.float32, "logits")
+        t = logits.numel() // ne
+        idx = torch.empty((t, k), dtype=torch.int32, device=logits.device)
+        wt = torch.empty((t, k), dtype=torch.float32, device=logits.device)
+        self._ck(self._L.w4a16_moe_topk(self._h, logits.data_ptr(), idx.data_ptr(), wt.data_ptr(), t, _cur_stream()))
+        return idx, wt
+
+    def moe_ffn_dev_t(self, il: int, logits: torch.Tensor, x16: torch.Tensor, t: int,
+                      out: torch.Tensor | None = None, out_f16: bool = False) -> torch.Tensor:
+        """moe/mod.rs:263: y[t,h] over the local experts (sum y over ranks under expert parallelism)."""
+        ne, k, f, h, g, _, _ = self._moe
+        self._tensor_ok(logits, torch.float32, "logits")
+        self._tensor_ok(x16, torch.float16, "x16")
+        if logits.numel() != t * ne or x16.numel() != t * h:
+            raise W4a16Error("moe_ffn_dev_t: logits/x sizes do not match t")
+        out = self._out(t, h, out_f16, out)
+        self._ck(self._L.w4a16_moe_ffn(self._h, il, logits.data_ptr(), x16.data_ptr(), out.data_ptr(), t,
+                                       OUT_F16 if out_f16 else OUT_F32, _cur_stream()))
+        return out

@@ -192,3 +192,37 @@ def linear_lane(q_u32, s_u16, x_u16, m: int, n: int, k: int, group: int,
     if rc != 0:
         raise ValueError("linear_lane: shape contract")
     return out
+
+
+def moe_ffn(x_u16, logits, w13_q, w13_s, w2_q, w2_s, top_k: int, group: int, experts=None) -> np.ndarray:
+    """CPU restatement of the resident MoE FFN: routing by select_topk
+    (crates/core/src/qwen35/stages/moe.rs:8-31); per expert the two linears are lane dots; the rounding
+    points follow the reference's GPU path (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/marlin_moe.rs:290-422):
+    c13 -> f16, silu(g)*u -> f16 (crates/backend-gpu/src/rawcuda/assets/moe.cu:1649-1660), w*c2 -> f16, then the
+    f32 sum over k in rank order (crates/backend-gpu/src/rawcuda/assets/moe.cu:1662-1674).
+    `experts=(e0,e1)` keeps only that range (one rank's share under expert parallelism)."""
+    x = _c(x_u16, np.uint16)
+    t, h = x.shape
+    n_exp, f2, _ = w13_q.shape
+    f = f2 // 2
+    lg = _c(logits, np.float32).reshape(t, n_exp)
+    sel = [select_topk(lg[i], top_k) for i in range(t)]
+    e0, e1 = (0, n_exp) if experts is None else experts
+    contrib = np.zeros((t, top_k, h), np.float32)
+    for e in range(e0, e1):
+        rows = [(i, r, w) for i in range(t) for r, (ee, w) in enumerate(sel[i]) if ee == e]
+        if not rows:
+            continue
+        xs = np.ascontiguousarray(x[[i for i, _, _ in rows]])
+        c13 = linear_lane(w13_q[e], w13_s[e], xs, len(rows), 2 * f, h, group).astype(np.float16).astype(np.float32)
+        g, u = c13[:, :f], c13[:, f:]
+        act = ((g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))) * u).astype(np.float16)
+        c2 = linear_lane(w2_q[e], w2_s[e], act.view(np.uint16), len(rows), h, f, group)
+        wv = np.array([w for _, _, w in rows], np.float32)[:, None]
+        c2 = (c2 * wv).astype(np.float16).astype(np.float32)
+        for j, (i, r, _) in enumerate(rows):
+            contrib[i, r] = c2[j]
+    out = np.zeros((t, h), np.float32)
+    for r in range(top_k):
+        out = out + contrib[:, r]
+    return out
