@@ -127,6 +127,17 @@ W4A16_API int w4a16_sk_single_dev(w4a16_dec* dec, const char* name, const void* 
  * four linears that share x and k (q|k|v, gate|up) in ONE launch; outs[i] is [t][n_i]. */
 W4A16_API int w4a16_sk_multi_dev(w4a16_dec* dec, const char* const* names, int n_seg, const void* x16_dev,
                        void* const* outs_dev, int t, int out_kind, void* stream);
+/* The decode GEMV of w4a16_sk_single_dev for hosts that must not allocate device memory (an engine that
+ * owns the whole memory budget and forbids library allocations after start-up, or a decode loop in
+ * which a cudaMalloc -- a device-wide synchronisation -- may never occur). It has no counterpart in the
+ * reference. The split-K scratch lives in an 8 MiB + 16 KiB array inside the library's device image
+ * (held by every GPU that loads the library, until exit), so this call allocates nothing. A shape whose
+ * launch needs more than 8 MiB of partial sums (8 KB per K split and 256-row block) or more than 4096
+ * row blocks is rejected with an error. All calls share the array: calls that overlap on the GPU race;
+ * calls on one stream are safe. The first call on a device resolves the array's address
+ * (cudaGetSymbolAddress) and must be made outside stream capture, with that device current. */
+W4A16_API int w4a16_sk_single_static(w4a16_dec* dec, const char* name, const void* x16_dev, void* out_dev, int t,
+                                     int out_kind, void* stream);
 /* Host-buffer form of lin_forward: copies x from HOST (pinned or pageable) memory, runs the
  * linear, copies dst back and synchronises. The end-to-end call a host engine makes per step
  * (the reference's host round trip: Gptq4::gemm, crates/backend-gpu/src/rawcuda/gptq4.rs:99-189,

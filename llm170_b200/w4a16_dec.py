@@ -162,6 +162,21 @@ class W4a16Dec:
                                              OUT_F16 if out_f16 else OUT_F32, _cur_stream()))
         return out
 
+    def sk_single_static(self, name: str, x16: torch.Tensor, out: torch.Tensor | None = None, t: int = 1,
+                         out_f16: bool = False) -> torch.Tensor:
+        """Same GEMV as :meth:`sk_single_dev`, for hosts that may not allocate device memory: the split-K
+        scratch is a fixed 8 MiB array inside the library, shared by all calls (calls that overlap on the
+        GPU race on it).  Shapes that need more are rejected.  Pass ``out``: this wrapper allocates the
+        output tensor only when it is omitted.  Make the first call on a device outside stream capture."""
+        n, k, _ = self.lin_spec(name)
+        self._tensor_ok(x16, torch.float16, "x16")
+        if x16.numel() != t * k:
+            raise W4a16Error(f"sk_single_static {name}: x has {x16.numel()} elements, need {t}x{k}")
+        out = self._out(t, n, out_f16, out)
+        self._ck(self._L.w4a16_sk_single_static(self._h, name.encode(), x16.data_ptr(), out.data_ptr(), t,
+                                                OUT_F16 if out_f16 else OUT_F32, _cur_stream()))
+        return out
+
     def sk_multi_dev(self, names, x16: torch.Tensor, outs=None, t: int = 1, out_f16: bool = False):
         """kernels/decode.rs:23-57: q|k|v or gate|up in one launch (same x, same k)."""
         specs = [self.lin_spec(nm) for nm in names]

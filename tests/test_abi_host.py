@@ -41,6 +41,7 @@ def test_every_entry_point_cites_the_reference():
     for m in re.finditer(r"/\*(?:[^*]|\*(?!/))*\*/\s*(?:W4A16_API[^;]*;\s*)+", text):
         chunk = m.group(0)
         found += chunk.count("W4A16_API")
+        chunk = re.sub(r"\s*\n\s*\*\s*", " ", chunk)   # undo comment line wrapping
         assert re.search(r"crates/[\w/\-.]+:\d+", chunk) or "no counterpart in the reference" in chunk \
             or "reference has no such variant" in chunk, chunk[:200]
     assert found == len(_lib.declared_symbols())
