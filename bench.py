@@ -254,12 +254,17 @@ def main():
 
     st = torch.cuda.ExternalStream(dec.stream_ptr(), device=device)
 
+    if world > 1:
+        dec.tp_setup(rank, world, max_rows=max(shapes[nm][1] for nm in LAYER_ORDER if shapes[nm][2] == "row"))
+
     def enqueue_step(m: int):
         for li in range(L):
             for nm in LAYER_ORDER:
-                dec.sk_single_dev(f"l{li}.{nm}", xb[nm][:m], out=yb[nm][:m], t=m, out_f16=True)
                 if world > 1 and shapes[nm][2] == "row":
-                    dist.all_reduce(yb[nm][:m])
+                    # row-parallel: the GEMV kernel itself sums the partial outputs over the ranks (peer loads)
+                    dec.sk_single_allreduce(f"l{li}.{nm}", xb[nm][:m], out=yb[nm][:m], t=m, out_f16=True)
+                else:
+                    dec.sk_single_dev(f"l{li}.{nm}", xb[nm][:m], out=yb[nm][:m], t=m, out_f16=True)
 
     graphs = {}
 
@@ -268,7 +273,7 @@ def main():
             enqueue_step(m)                       # warm scratch before capture
             st.synchronize()
             if world > 1:
-                return None
+                dist.barrier()                    # every rank replays the same sequence of exchanges
             c0 = dec.launch_count()
             dec.capture_begin()
             enqueue_step(m)
@@ -325,8 +330,12 @@ def main():
         for _ in range(args.steps):
             dec.graph_step_host(gx, x_host, xdev, ydev, y_host)
         e2e_s = (time.perf_counter() - t0) / args.steps
+        if world > 1:
+            te = torch.tensor([e2e_s], device=device)
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+            e2e_s = float(te.item())
         e2e = {"value": bytes_step / e2e_s / 1e9, "unit": "GB/s", "ms_per_step": e2e_s * 1e3,
-               "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2}
+               "h2d_bytes_per_step": x_host.numel() * 2 * world, "d2h_bytes_per_step": y_host.numel() * 2 * world}
     else:
         # multi-GPU: same step issued eagerly between a pinned H2D and a D2H
         with torch.cuda.stream(st):
@@ -450,7 +459,7 @@ def main():
                                    "gate_up 5120x34816, down 17408x5120), int4 sym g128, f16 scales",
                        "layers": L, "parallelism": f"tp{world}" if world > 1 else "single",
                        "l2": f"inputs larger than L2 ({bytes_step / 1e9:.2f} GB of weights per step)",
-                       "launch": "cuda graph replay" if graphs[1] else "eager + NCCL all-reduce",
+                       "launch": "cuda graph replay" + (", all-reduce fused into the row-parallel GEMV (peer loads)" if world > 1 else ""),
                        "build_s": round(t_build, 1)},
             "roofline": {"bound": "hbm", "kernel": "gemv_w4a16_kernel<128>", "achieved": ach,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
@@ -462,10 +471,13 @@ def main():
             "cpu_baseline": cpu_baseline, "extras": extras,
         }
         print(json.dumps(line), flush=True)
+    sys.stdout.flush()
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    dec.close()
+    # leave without running destructors: tensors allocated on the decoder's stream outlive it otherwise
+    os._exit(0)
 
 
 if __name__ == "__main__":

@@ -149,6 +149,25 @@ W4A16_API int w4a16_lin_forward_host(w4a16_dec* dec, const char* name, const voi
 W4A16_API int w4a16_gptq4_gemm(w4a16_dec* dec, const void* x16_host, int t, const void* q_host, const void* s_host,
                      int n, int k, int group, int scale_bf16, float* out_host);
 
+/* ---- row-parallel tensor parallelism (no counterpart in the reference, which has no collective:
+ *      crates/server/src/main.rs:245-247) ------------------------------------------------------ */
+
+/* Allocates this rank's exchange block (flags + two parity buffers of max_rows x 8 f32 partial sums) and
+ * returns its 64-byte CUDA IPC handle. rank/world describe the tensor-parallel group on one node
+ * (world 2..8, one process per GPU). The reference has no such variant. */
+W4A16_API int w4a16_tp_create(w4a16_dec* dec, int rank, int world, int max_rows, void* handle_out64);
+/* Maps the peers' exchange blocks: `handles` holds world x 64 bytes, the handles of all ranks in rank
+ * order (exchanged by the host, e.g. over its process group). The reference has no such variant. */
+W4A16_API int w4a16_tp_connect(w4a16_dec* dec, const void* handles_world_x64);
+/* Row-parallel decode GEMV with the all-reduce fused into the kernel: each rank holds a K slice of the
+ * linear (whole scale groups), x16 is that slice of the activations, and out receives the SUM over ranks
+ * of the partial products -- the kernel that reduces the split-K partials also publishes the local sums,
+ * waits (bounded) for the peers' flags and adds their rows with peer loads over NVLink. Every rank must
+ * make the same sequence of these calls. Replaces sk_single_dev + an NCCL all-reduce for o_proj / down
+ * (the reference runs them on one GPU: crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:89-127). */
+W4A16_API int w4a16_sk_single_allreduce(w4a16_dec* dec, const char* name, const void* x16_dev, void* out_dev, int t,
+                                        int out_kind, void* stream);
+
 /* ---- MoE ---------------------------------------------------------------------------------- */
 
 /* W4a16Dec::set_moe (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:795-812): expert count, top-k,

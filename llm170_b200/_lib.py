@@ -36,6 +36,9 @@ _SIGS = {
     "w4a16_lin_forward": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
     "w4a16_sk_single_dev": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
     "w4a16_sk_single_static": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
+    "w4a16_tp_create": (_i, [_vp, _i, _i, _i, _vp]),
+    "w4a16_tp_connect": (_i, [_vp, _vp]),
+    "w4a16_sk_single_allreduce": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
     "w4a16_sk_multi_dev": (_i, [_vp, C.POINTER(C.c_char_p), _i, _vp, C.POINTER(_vp), _i, _i, _vp]),
     "w4a16_lin_forward_host": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i]),
     "w4a16_gptq4_gemm": (_i, [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),

@@ -141,7 +141,7 @@ int Dec::upload_common(const char* name, const void* q_dev, const void* s_dev, i
 }
 
 int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, int t, int out_kind,
-              cudaStream_t st) {
+              cudaStream_t st, bool allreduce) {
     if (t < 1 || t > GEMV_MAX_M) {
         return fail("w4a16 gemv: t=%d outside 1..%d", t, GEMV_MAX_M);
     }
@@ -189,6 +189,17 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
     a.ring_stages = tune_gemv_stages;
     a.cons_warps = tune_gemv_warps;
     a.status = gemm_status;
+    a.tp = TpComm{};
+    if (allreduce) {
+        if (tp.world < 2 || tp_peer[(tp.rank + 1) % tp.world] == nullptr) {
+            return fail("w4a16 allreduce gemv: call w4a16_tp_create and w4a16_tp_connect first");
+        }
+        if (nseg != 1 || ls[0]->n > tp_max_rows || grid_x > TP_MAX_CTAS) {
+            return fail("w4a16 allreduce gemv: n=%d exceeds the exchange buffer (%d rows)", ls[0]->n, tp_max_rows);
+        }
+        a.tp = tp;
+        a.pdl = 0;  // the exchange buffers are reused by the next launch: no early start
+    }
     if (int rc = ensure_scratch(gemv_part_floats(grid_x, ks), grid_x, st)) {
         return rc;
     }
@@ -305,6 +316,14 @@ void w4a16_dec_free(w4a16_dec* dec) {
     }
     if (d.dbg_buf) {
         cudaFree(d.dbg_buf);
+    }
+    for (int p = 0; p < w4::TP_MAX_WORLD; ++p) {
+        if (d.tp_peer[p] && d.tp_peer[p] != d.tp_block) {
+            cudaIpcCloseMemHandle(d.tp_peer[p]);
+        }
+    }
+    if (d.tp_block) {
+        cudaFree(d.tp_block);
     }
     if (d.xh) {
         cudaFree(d.xh);
@@ -566,6 +585,80 @@ int w4a16_sk_single_dev(w4a16_dec* dec, const char* name, const void* x16_dev, v
     const Lin* ls[1] = {l};
     void* outs[1] = {out_dev};
     return d.gemv(ls, 1, x16_dev, outs, t, out_kind, pick_stream(dec, stream));
+}
+
+// ---- row-parallel tensor parallelism ----------------------------------------------------------------
+// exchange block layout: [flags world*TP_MAX_CTAS u32][seq u32][done u32][pad -> 4096 B][2 x max_rows x 8 f32]
+static const size_t TP_HEADER = 4096;
+
+int w4a16_tp_create(w4a16_dec* dec, int rank, int world, int max_rows, void* handle_out64) {
+    Dec& d = dec->d;
+    if (world < 2 || world > w4::TP_MAX_WORLD || rank < 0 || rank >= world || max_rows < 16 ||
+        max_rows > w4::TP_MAX_CTAS * 256) {
+        return d.fail("w4a16 tp_create: rank=%d world=%d max_rows=%d unsupported (world 2..%d, rows <= %d)", rank, world,
+                      max_rows, w4::TP_MAX_WORLD, w4::TP_MAX_CTAS * 256);
+    }
+    cudaSetDevice(d.device);
+    cudaDeviceSynchronize();
+    if (d.tp_block) {
+        return d.fail("w4a16 tp_create: already created");
+    }
+    const size_t area = (size_t)max_rows * w4::GEMV_MAX_M;
+    const size_t bytes = TP_HEADER + 2 * area * sizeof(float);
+    cudaError_t e = cudaMalloc(&d.tp_block, bytes);
+    if (e == cudaSuccess) e = cudaMemset(d.tp_block, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, d.tp_block);
+    if (e != cudaSuccess) {
+        return d.cuda_fail("tp_create", e);
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    memcpy(handle_out64, &h, 64);
+    d.tp = w4::TpComm{};
+    d.tp.rank = rank;
+    d.tp.world = world;
+    d.tp.area_floats = (int)area;
+    d.tp_max_rows = max_rows;
+    d.tp_peer[rank] = d.tp_block;
+    return 0;
+}
+
+int w4a16_tp_connect(w4a16_dec* dec, const void* handles_world_x64) {
+    Dec& d = dec->d;
+    if (!d.tp_block) {
+        return d.fail("w4a16 tp_connect: call w4a16_tp_create first");
+    }
+    cudaSetDevice(d.device);
+    for (int p = 0; p < d.tp.world; ++p) {
+        if (p != d.tp.rank && d.tp_peer[p] == nullptr) {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, (const char*)handles_world_x64 + 64 * p, 64);
+            cudaError_t e = cudaIpcOpenMemHandle(&d.tp_peer[p], h, cudaIpcMemLazyEnablePeerAccess);
+            if (e != cudaSuccess) {
+                return d.cuda_fail("tp_connect: cudaIpcOpenMemHandle", e);
+            }
+        }
+    }
+    for (int p = 0; p < d.tp.world; ++p) {
+        d.tp.flags[p] = (unsigned*)d.tp_peer[p];
+        d.tp.buf[p] = (float*)((char*)d.tp_peer[p] + TP_HEADER);
+    }
+    unsigned* local = (unsigned*)d.tp_block;
+    d.tp.seq = local + w4::TP_MAX_WORLD * w4::TP_MAX_CTAS;
+    d.tp.done = d.tp.seq + 1;
+    return 0;
+}
+
+int w4a16_sk_single_allreduce(w4a16_dec* dec, const char* name, const void* x16_dev, void* out_dev, int t,
+                              int out_kind, void* stream) {
+    Dec& d = dec->d;
+    Lin* l = find_lin(d, name);
+    if (!l) {
+        return 1;
+    }
+    const Lin* ls[1] = {l};
+    void* outs[1] = {out_dev};
+    return d.gemv(ls, 1, x16_dev, outs, t, out_kind, pick_stream(dec, stream), true);
 }
 
 int w4a16_sk_multi_dev(w4a16_dec* dec, const char* const* names, int n_seg, const void* x16_dev,

@@ -47,6 +47,20 @@ __device__ __forceinline__ void mma16816_z(float (&c)[4], const uint32_t (&a)[4]
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
 }
 
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
 // K range of split `s` in units of max(group, 64) input channels; ragged splits allowed.
 __device__ __host__ __forceinline__ void split_range(int k, int group, int ksplit, int s, int* kb0, int* kb1) {
     const int unit_kb = group > TILE_K ? group / TILE_K : 1;
@@ -96,6 +110,64 @@ __host__ SmemPlan make_plan(int k, int group, int m, int ksplit, int stages) {
     return p;
 }
 
+// Fused all-reduce of a row-parallel GEMV: the CTA that holds the local sums of rows [row0, row0+nrows) has
+// just written them (f32) to this rank's parity buffer.  It tells every peer (one flag per rank and row
+// block, written with release.sys into the PEER's flag array), waits -- bounded -- until every peer's flag for
+// this row block has reached this launch's number, then adds the peers' partial rows in rank order with
+// plain peer loads over NVLink and writes the final output.  No multicast, no second kernel, no NCCL call.
+// Parity buffers: a peer can be at most one launch ahead, and then writes the other buffer.
+__device__ __forceinline__ void tp_exchange(const GemvArgs& a, const GemvSeg& sg, int rb_cta0, int nrows, unsigned seq,
+                                            volatile int* abort_flag) {
+    const TpComm& tp = a.tp;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        for (int p = 0; p < tp.world; ++p) {
+            if (p != tp.rank) {
+                st_release_sys(tp.flags[p] + tp.rank * TP_MAX_CTAS + blockIdx.x, seq);
+            }
+        }
+    }
+    if ((int)threadIdx.x < tp.world && (int)threadIdx.x != tp.rank) {
+        const unsigned* f = tp.flags[tp.rank] + threadIdx.x * TP_MAX_CTAS + blockIdx.x;
+        const long long t0 = clock64();
+        while ((int)(ld_acquire_sys(f) - seq) < 0) {
+            if (*abort_flag || clock64() - t0 > (1ll << 31)) {
+                *abort_flag = 1;
+                atomicCAS(a.status, 0, (20 << 16) | (int)threadIdx.x);   // peer never arrived
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (!*abort_flag) {
+        const size_t par = (size_t)(seq & 1u) * tp.area_floats;
+        const int row0 = rb_cta0 * TILE_ROWS;
+        for (int i = threadIdx.x; i < nrows * a.m; i += blockDim.x) {
+            const int lr = i % nrows, tok = i / nrows;
+            const size_t off = par + (size_t)(row0 + lr) * GEMV_MAX_M + tok;
+            float v = 0.f;
+            for (int p = 0; p < tp.world; ++p) {
+                v += ld_relaxed_sys_f32(tp.buf[p] + off);
+            }
+            if (a.out_f16) {
+                reinterpret_cast<__half*>(sg.out)[(size_t)tok * sg.n + row0 + lr] = __float2half_rn(v);
+            } else {
+                reinterpret_cast<float*>(sg.out)[(size_t)tok * sg.n + row0 + lr] = v;
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // the last row block of this launch to finish advances the launch number
+        if (atomicAdd(tp.done, 1u) == gridDim.x - 1) {
+            *tp.done = 0;
+            *tp.seq = seq;
+            __threadfence();
+        }
+    }
+}
+
 // CONS_WARPS consumer warps (8 or 16) own 16/CONS_WARPS row blocks each; warp CONS_WARPS is the producer.
 template <int GROUP, bool SUBN, int CONS_WARPS>
 __global__ void __launch_bounds__((CONS_WARPS + 1) * 32)
@@ -139,7 +211,10 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     volatile int* abort_flag = &s_abort;
     const bool stamp = a.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
 
+    __shared__ unsigned s_seq;
+    const bool tp_on = a.tp.world > 1;
     if (threadIdx.x == 0) {
+        s_seq = tp_on ? *a.tp.seq + 1u : 0u;   // this launch's exchange number (advanced by the last CTA to finish)
         if (stamp) {
             a.dbg[0] = clock64();
             unsigned long long ns;
@@ -432,7 +507,11 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                 for (int j = 0; j < 2; ++j) {
                     const int tok = 2 * t + j;
                     if (tok < a.m) {
-                        if (a.out_f16) {
+                        if (tp_on) {
+                            float* o = a.tp.buf[a.tp.rank] + (size_t)(s_seq & 1u) * a.tp.area_floats;
+                            o[(size_t)row0 * GEMV_MAX_M + tok] = tot[r][j];
+                            o[(size_t)row1 * GEMV_MAX_M + tok] = tot[r][2 + j];
+                        } else if (a.out_f16) {
                             __half* o = reinterpret_cast<__half*>(sg.out) + (size_t)tok * sg.n;
                             o[row0] = __float2half_rn(tot[r][j]);
                             o[row1] = __float2half_rn(tot[r][2 + j]);
@@ -444,6 +523,9 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                     }
                 }
             }
+        }
+        if (tp_on) {
+            tp_exchange(a, sg, rb_cta0, nrbv * TILE_ROWS, s_seq, abort_flag);
         }
         return;
     }
@@ -490,7 +572,9 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                 const int tok = 2 * tp + j;
                 if (tok < a.m) {
                     const float v = j ? sum.y : sum.x;
-                    if (a.out_f16) {
+                    if (tp_on) {
+                        a.tp.buf[a.tp.rank][(size_t)(s_seq & 1u) * a.tp.area_floats + (size_t)row * GEMV_MAX_M + tok] = v;
+                    } else if (a.out_f16) {
                         reinterpret_cast<__half*>(sg.out)[(size_t)tok * sg.n + row] = __float2half_rn(v);
                     } else {
                         reinterpret_cast<float*>(sg.out)[(size_t)tok * sg.n + row] = v;
@@ -501,6 +585,9 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     }
     if (threadIdx.x == 0) {
         a.counters[blockIdx.x] = 0;  // ready for the next launch (graph replay needs no memset)
+    }
+    if (tp_on) {
+        tp_exchange(a, sg, rb_cta0, nrows, s_seq, abort_flag);
     }
 }
 

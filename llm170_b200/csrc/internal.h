@@ -23,6 +23,19 @@ void launch_dequant(const uint32_t* qt, const uint16_t* stl, void* out, int n, i
 constexpr int GEMV_MAX_SEG = 4;
 constexpr int GEMV_MAX_M = 8;
 
+// Row-parallel tensor parallelism: peers' partial-sum buffers and flag arrays, mapped into this device's
+// address space (CUDA IPC).  world <= 1 disables the fused all-reduce.
+constexpr int TP_MAX_WORLD = 8;
+constexpr int TP_MAX_CTAS = 64;   // 256-row blocks per row-parallel linear (n <= 16384)
+struct TpComm {
+    int rank, world;
+    int area_floats;                  // floats per parity buffer (max_rows * 8)
+    float* buf[TP_MAX_WORLD];         // rank p's partial sums: [2 parities][max_rows][8 tokens] f32
+    unsigned* flags[TP_MAX_WORLD];    // rank p's flags: [world][TP_MAX_CTAS]; writer q sets flags[p][q][cta]
+    unsigned* seq;                    // local: number of fused launches completed
+    unsigned* done;                   // local: CTAs that finished the current launch's exchange
+};
+
 struct GemvSeg {
     const uint4* qt;
     const uint32_t* st;  // scale pairs, one u32 = (row j, row j+8)
@@ -48,6 +61,7 @@ struct GemvArgs {
     long long* dbg;     // optional timeline buffer (diagnostic), CTA (0,0) only
     int dbg_seq;        // launch sequence number (slot for the per-launch start/end stamps)
     int pdl;            // 1: launch with programmatic stream serialization (overlaps the previous kernel's tail)
+    TpComm tp;          // fused all-reduce over peers (row-parallel); tp.world <= 1: off
     int* status;        // device word that records the first bounded wait that expired
 };
 

@@ -177,6 +177,30 @@ class W4a16Dec:
                                                 OUT_F16 if out_f16 else OUT_F32, _cur_stream()))
         return out
 
+    # -- row-parallel tensor parallelism ---------------------------------------------------------
+    def tp_setup(self, rank: int, world: int, max_rows: int, group=None):
+        """Creates this rank's exchange block and maps the peers' (handles travel over torch.distributed)."""
+        import torch.distributed as dist
+        mine = C.create_string_buffer(64)
+        self._ck(self._L.w4a16_tp_create(self._h, rank, world, max_rows, mine))
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(mine.raw), group=group)
+        blob = C.create_string_buffer(b"".join(handles), 64 * world)
+        self._ck(self._L.w4a16_tp_connect(self._h, blob))
+        dist.barrier(group=group)
+
+    def sk_single_allreduce(self, name: str, x16: torch.Tensor, out: torch.Tensor | None = None, t: int = 1,
+                            out_f16: bool = False) -> torch.Tensor:
+        """Row-parallel GEMV whose kernel also sums the partial outputs over the ranks (peer loads)."""
+        n, k, _ = self.lin_spec(name)
+        self._tensor_ok(x16, torch.float16, "x16")
+        if x16.numel() != t * k:
+            raise W4a16Error(f"sk_single_allreduce {name}: x has {x16.numel()} elements, need {t}x{k}")
+        out = self._out(t, n, out_f16, out)
+        self._ck(self._L.w4a16_sk_single_allreduce(self._h, name.encode(), x16.data_ptr(), out.data_ptr(), t,
+                                                   OUT_F16 if out_f16 else OUT_F32, _cur_stream()))
+        return out
+
     def sk_multi_dev(self, names, x16: torch.Tensor, outs=None, t: int = 1, out_f16: bool = False):
         """kernels/decode.rs:23-57: q|k|v or gate|up in one launch (same x, same k)."""
         specs = [self.lin_spec(nm) for nm in names]
