@@ -70,8 +70,9 @@ W4A16_API int w4a16_debug_timeline(w4a16_dec* dec, long long* out, int max_slots
  * HOST_LAUNCH_CALLS (crates/backend-gpu/src/rawcuda/ctx/mod.rs:10-11,311-315). */
 W4A16_API unsigned long long w4a16_launch_count(w4a16_dec* dec);
 /* Kernel-selection knobs, the analogue of the reference's LLM170_* environment flags
- * (crates/diag/src/flag.rs:3-27). Keys: "gemv_ctas_per_sm", "gemv_ksplit" (0 = automatic),
- * "gemv_stages" (16 KB weight stages in flight per CTA, 2..8), "gemv_warps" (consumer warps per CTA, 8 or 16),
+ * (crates/diag/src/flag.rs:3-27). Keys: "gemv_ksplit" (0 = automatic),
+ * "gemv_stages" (16 KB weight stages in flight per CTA, 2..8), "gemv_warps" (consumer warps per CTA, 8 or 16), "gemv_cluster" (1 = default: 2..8 K splits of a row
+ * block run as a thread-block cluster and reduce through distributed shared memory),
  * "gemv_subnormal" (1 = default arithmetic, 0 = exact nibble-8 operands), "debug_timeline" (0/1, see w4a16_debug_timeline), "pdl" (1 = default: kernels are
  * launched with programmatic stream serialization and prefetch weights while the previous kernel of
  * the stream drains; 0 = ordinary launches). */

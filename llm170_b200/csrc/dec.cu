@@ -166,8 +166,8 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
     a.x = (const uint16_t*)x;
     const int grid_x = gemv_plan_ctas(a);
     int ks = tune_gemv_ksplit > 0 ? tune_gemv_ksplit
-                                  : gemv_pick_ksplit(grid_x, a.k, a.group, t, sm_count, tune_gemv_ctas_per_sm,
-                                                     tune_gemv_stages);
+                                  : gemv_pick_ksplit(grid_x, a.k, a.group, t, sm_count,
+                                                     (tune_gemv_cluster && !allreduce) ? 8 : 16, tune_gemv_stages);
     const int unit = a.group > TILE_K ? a.group : TILE_K;
     if (ks > a.k / unit) {
         ks = a.k / unit;
@@ -189,6 +189,7 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
     a.ring_stages = tune_gemv_stages;
     a.cons_warps = tune_gemv_warps;
     a.status = gemm_status;
+    a.cluster = (tune_gemv_cluster && ks >= 2 && ks <= 8 && !allreduce) ? 1 : 0;
     a.tp = TpComm{};
     if (allreduce) {
         if (tp.world < 2 || tp_peer[(tp.rank + 1) % tp.world] == nullptr) {
@@ -383,18 +384,15 @@ unsigned long long w4a16_launch_count(w4a16_dec* dec) { return dec->d.launches; 
 
 int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
     Dec& d = dec->d;
-    if (!strcmp(key, "gemv_ctas_per_sm")) {
-        if (value < 1 || value > 32) {
-            return d.fail("w4a16 tuning: gemv_ctas_per_sm must be 1..32");
-        }
-        d.tune_gemv_ctas_per_sm = value;
-        return 0;
-    }
     if (!strcmp(key, "gemv_stages")) {
         if (value < 2 || value > 8) {
             return d.fail("w4a16 tuning: gemv_stages must be 2..8");
         }
         d.tune_gemv_stages = value;
+        return 0;
+    }
+    if (!strcmp(key, "gemv_cluster")) {
+        d.tune_gemv_cluster = value != 0;
         return 0;
     }
     if (!strcmp(key, "gemv_warps")) {

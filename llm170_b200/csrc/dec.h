@@ -56,8 +56,8 @@ struct Dec {
     size_t yh_cap = 0;
     // knobs
     int tune_gemv_stages = 4;
-    int tune_gemv_warps = 16;
-    int tune_gemv_ctas_per_sm = 3;   // residency cap assumed by the split-K cost model (register-limited)
+    int tune_gemv_warps = 8;
+    int tune_gemv_cluster = 1;   // K splits of a row block as a thread-block cluster (DSMEM reduce) when 2 <= ksplit <= 8
     int tune_gemv_subnormal = 1;
     int tune_pdl = 1;
     long long* dbg_buf = nullptr;  // device timeline buffer (DBG_SLOTS entries) when the knob is on

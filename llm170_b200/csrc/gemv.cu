@@ -61,6 +61,18 @@ __device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
     return v;
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, unsigned cta_rank) {
+    uint32_t ra;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(cta_rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+    return v;
+}
+
 // K range of split `s` in units of max(group, 64) input channels; ragged splits allowed.
 __device__ __host__ __forceinline__ void split_range(int k, int group, int ksplit, int s, int* kb0, int* kb1) {
     const int unit_kb = group > TILE_K ? group / TILE_K : 1;
@@ -530,6 +542,42 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         return;
     }
 
+    if (a.cluster) {
+        // split-K inside a thread-block cluster: the ksplit CTAs of this row block park their partial sums in
+        // their own shared memory and every CTA sums a slice of the rows over all splits, in split order,
+        // through distributed shared memory -- no global round trip, no ticket.
+        __syncthreads();  // the weight ring is idle now; its first stage becomes the partial buffer
+        float* pbuf = reinterpret_cast<float*>(smem + p.off_ring);  // [256 rows][8 tokens]
+#pragma unroll
+        for (int r = 0; r < RB_PER_WARP; ++r) {
+            if (r < nvalid) {
+                const int lr0 = (rbw0 + r) * TILE_ROWS + g, lr1 = lr0 + 8;
+                *reinterpret_cast<float2*>(pbuf + lr0 * GEMV_MAX_M + 2 * t) = make_float2(tot[r][0], tot[r][1]);
+                *reinterpret_cast<float2*>(pbuf + lr1 * GEMV_MAX_M + 2 * t) = make_float2(tot[r][2], tot[r][3]);
+            }
+        }
+        cluster_sync_all();
+        const int nrows_c = nrbv * TILE_ROWS;
+        const int per = (nrows_c + a.ksplit - 1) / a.ksplit;
+        const int lr_begin = split * per, lr_end = min(nrows_c, lr_begin + per);
+        const uint32_t pbase = sbase + p.off_ring;
+        for (int i = threadIdx.x; i < (lr_end - lr_begin) * a.m; i += blockDim.x) {
+            const int lr = lr_begin + i / a.m, tok = i % a.m;
+            float sum = 0.f;
+            for (int s = 0; s < a.ksplit; ++s) {
+                sum += ld_dsmem_f32(pbase + (uint32_t)(lr * GEMV_MAX_M + tok) * 4u, (unsigned)s);
+            }
+            const int row = rb_cta0 * TILE_ROWS + lr;
+            if (a.out_f16) {
+                reinterpret_cast<__half*>(sg.out)[(size_t)tok * sg.n + row] = __float2half_rn(sum);
+            } else {
+                reinterpret_cast<float*>(sg.out)[(size_t)tok * sg.n + row] = sum;
+            }
+        }
+        cluster_sync_all();  // peers may still be reading this CTA's buffer
+        return;
+    }
+
     // split-K: park partials as part[split][cta][row_in_cta (256)][tok (8)], then the last CTA of
     // this column of the grid sums the splits in index order.
     float* mypart = a.part + ((size_t)split * gridDim.x + blockIdx.x) * (ROWS_PER_CTA * GEMV_MAX_M);
@@ -592,7 +640,6 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
 }
 
 constexpr int GEMV_SMEM_LIMIT = 112 * 1024;
-constexpr int SM_SMEM_BYTES = 233472;  // 228 KB per SM, 1 KB reserved per resident CTA
 
 }  // namespace
 
@@ -614,38 +661,28 @@ size_t gemv_part_floats(int grid_x, int ksplit) {
     return ksplit > 1 ? (size_t)ksplit * grid_x * (ROWS_PER_CTA * GEMV_MAX_M) : 0;
 }
 
-// Split-K chosen by a small cost model instead of a fixed target (the reference sizes its split for a
-// 70-SM part: crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:3-20).  For every candidate the
-// time is  (CTAs on the busiest SM) x (largest split + fixed per-CTA cost), all resident CTAs of an SM
-// sharing its bandwidth; the cheapest wins, ties to fewer splits (fewer partials to reduce).
-int gemv_pick_ksplit(int grid_x, int k, int group, int m, int sm_count, int max_ctas_per_sm, int stages) {
+// Split-K policy (the reference sizes its split for a 70-SM part:
+// crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:3-20).  Measured on B200, one 256-row CTA cannot
+// keep an SM's share of HBM busy but two to three resident CTAs can, and every extra split adds fixed cost,
+// so the split aims at about 2.2 CTAs per SM, keeps at least two scale groups per split, stays within
+// `max_split` (8 when the splits reduce inside a thread-block cluster) and within the shared-memory budget.
+int gemv_pick_ksplit(int grid_x, int k, int group, int m, int sm_count, int max_split, int stages) {
     const int unit = group > TILE_K ? group : TILE_K;
     const int units = k / unit;
-    const double fixed = 4.0 * (128.0 / unit);  // per-CTA prologue + reduce, in units of work
-    int best = 1;
-    double best_cost = 1e30;
-    for (int ks = 1; ks <= units && ks <= 64; ++ks) {
-        const size_t smem = gemv_smem_bytes(k, group, m, ks, stages);
-        if (smem > (size_t)GEMV_SMEM_LIMIT) {
-            continue;
-        }
-        int ctas_per_sm = (int)(SM_SMEM_BYTES / (smem + 1024));
-        if (ctas_per_sm > max_ctas_per_sm) {
-            ctas_per_sm = max_ctas_per_sm;
-        }
-        const int per_split = (units + ks - 1) / ks;
-        const long long ctas = (long long)grid_x * ks;
-        const long long slots = (long long)sm_count * ctas_per_sm;
-        const long long waves = (ctas + slots - 1) / slots;
-        const long long last = ctas - (waves - 1) * slots;
-        const long long busiest = (last + sm_count - 1) / sm_count;
-        const double cost = ((waves - 1) * ctas_per_sm + busiest) * (per_split + fixed);
-        if (cost < best_cost * 0.999) {
-            best_cost = cost;
-            best = ks;
-        }
+    int ks = (int)((2.2 * sm_count) / grid_x + 0.5);
+    if (ks > max_split) {
+        ks = max_split;
     }
-    return best;
+    if (ks > units / 2) {
+        ks = units / 2;
+    }
+    if (ks < 1) {
+        ks = 1;
+    }
+    while (ks < units && gemv_smem_bytes(k, group, m, ks, stages) > (size_t)GEMV_SMEM_LIMIT) {
+        ++ks;
+    }
+    return ks;
 }
 
 cudaError_t gemv_init_device() {
@@ -686,11 +723,22 @@ cudaError_t launch_gemv(const GemvArgs& a, int grid_x, cudaStream_t st) {
     cfg.gridDim = dim3(grid_x, a.ksplit);
     cfg.dynamicSmemBytes = p.total;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (a.pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (a.cluster) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = 1;
+        attr[na].val.clusterDim.y = a.ksplit;  // grid.y == ksplit: one cluster per row block
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = a.pdl ? 1 : 0;
+    cfg.numAttrs = na;
     return a.cons_warps == 16 ? launch_gemv_cw<16>(a, p, cfg) : launch_gemv_cw<8>(a, p, cfg);
 }
 

@@ -88,7 +88,7 @@ extern "C" int w4a16_sk_single_static(w4a16_dec* dec, const char* name, const vo
     const int grid_x = gemv_plan_ctas(a);
     int ks = d.tune_gemv_ksplit > 0
                  ? d.tune_gemv_ksplit
-                 : gemv_pick_ksplit(grid_x, a.k, a.group, t, d.sm_count, d.tune_gemv_ctas_per_sm, d.tune_gemv_stages);
+                 : gemv_pick_ksplit(grid_x, a.k, a.group, t, d.sm_count, d.tune_gemv_cluster ? 8 : 16, d.tune_gemv_stages);
     const int unit = a.group > TILE_K ? a.group : TILE_K;
     if (ks > a.k / unit) {
         ks = a.k / unit;
@@ -110,6 +110,8 @@ extern "C" int w4a16_sk_single_static(w4a16_dec* dec, const char* name, const vo
     a.pdl = 0;  // ordinary launch: the shared array must not be touched while an earlier kernel still runs
     a.ring_stages = d.tune_gemv_stages;
     a.cons_warps = d.tune_gemv_warps;
+    a.cluster = 0;  // this entry point exists for its global scratch; keep the ticketed reduce
+    a.tp = TpComm{};
     a.status = d.gemm_status;
     a.dbg = nullptr;
     a.dbg_seq = 0;

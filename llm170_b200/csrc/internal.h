@@ -56,6 +56,7 @@ struct GemvArgs {
     float* part;        // [ksplit][grid_x][256][GEMV_MAX_M] partial sums (ksplit > 1)
     unsigned* counters; // [grid_x], zero on entry, left zero on exit
     int subnormal;      // 1: feed raw nibbles as f16 subnormals and fix up per group (default); 0: exact nibble-8
+    int cluster;        // 1: the K splits of a row block form a thread-block cluster and reduce through DSMEM
     int cons_warps;     // consumer warps per CTA: 8 (two row blocks each) or 16 (one each)
     int ring_stages;    // 2 KB chunks in flight per warp (2..4)
     long long* dbg;     // optional timeline buffer (diagnostic), CTA (0,0) only
@@ -68,7 +69,7 @@ struct GemvArgs {
 // Total CTAs along x for the segments in `a` (fills seg[].cta0).
 int gemv_plan_ctas(GemvArgs& a);
 // Smallest and preferred split-K for a plan (see gemv.cu).
-int gemv_pick_ksplit(int grid_x, int k, int group, int m, int sm_count, int max_ctas_per_sm, int stages);
+int gemv_pick_ksplit(int grid_x, int k, int group, int m, int sm_count, int max_split, int stages);
 size_t gemv_smem_bytes(int k, int group, int m, int ksplit, int stages);
 size_t gemv_part_floats(int grid_x, int ksplit);
 cudaError_t launch_gemv(const GemvArgs& a, int grid_x, cudaStream_t st);
