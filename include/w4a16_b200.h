@@ -75,7 +75,7 @@ W4A16_API unsigned long long w4a16_launch_count(w4a16_dec* dec);
  * block run as a thread-block cluster and reduce through distributed shared memory),
  * "gemv_subnormal" (1 = default arithmetic, 0 = exact nibble-8 operands), "debug_timeline" (0/1, see w4a16_debug_timeline), "pdl" (1 = default: kernels are
  * launched with programmatic stream serialization and prefetch weights while the previous kernel of
- * the stream drains; 0 = ordinary launches). */
+ * the stream drains; 2 = the next kernel may start as soon as this one is resident; 0 = ordinary launches). */
 W4A16_API int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value);
 
 /* ---- weights ----------------------------------------------------------------------------- */

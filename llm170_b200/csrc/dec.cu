@@ -417,7 +417,10 @@ int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
         return 0;
     }
     if (!strcmp(key, "pdl")) {
-        d.tune_pdl = value != 0;
+        if (value < 0 || value > 2) {
+            return d.fail("w4a16 tuning: pdl must be 0, 1 or 2");
+        }
+        d.tune_pdl = value;
         return 0;
     }
     if (!strcmp(key, "gemv_subnormal")) {

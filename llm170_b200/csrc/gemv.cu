@@ -279,6 +279,11 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     // Programmatic dependent launch: the weight copies above do not depend on the previous kernel in the
     // stream, so they are already in flight while it drains.  Everything below reads x or writes
     // scratch/outputs and must wait for it.  (griddepcontrol does nothing in an ordinary launch.)
+    if (a.pdl == 2) {
+        // early trigger: the next kernel's CTAs take whatever SM slots this grid leaves free and prefetch
+        // their first weight stages while this kernel computes (they still wait for it before using x)
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) {
         mbar_expect_tx(xbar, a.m * halves * 2);
@@ -507,7 +512,9 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
 
     // the next kernel of the stream may start its weight stream now (it waits for our completion
     // before touching x, scratch or outputs)
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (a.pdl != 2) {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
 
     // tot[r][0],[1]: row g, tokens 2t, 2t+1 ; tot[r][2],[3]: row g+8, tokens 2t, 2t+1
     if (a.ksplit == 1) {
