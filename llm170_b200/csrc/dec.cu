@@ -391,6 +391,13 @@ int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
         d.tune_gemv_stages = value;
         return 0;
     }
+    if (!strcmp(key, "gemm_mt")) {
+        if (value < 0 || value > 2) {
+            return d.fail("w4a16 tuning: gemm_mt must be 0, 1 or 2");
+        }
+        d.tune_gemm_mt = value;
+        return 0;
+    }
     if (!strcmp(key, "gemv_cluster")) {
         d.tune_gemv_cluster = value != 0;
         return 0;

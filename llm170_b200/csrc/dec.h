@@ -60,6 +60,7 @@ struct Dec {
     int tune_gemv_cluster = 1;   // K splits of a row block as a thread-block cluster (DSMEM reduce) when 2 <= ksplit <= 8
     int tune_gemv_subnormal = 1;
     int tune_pdl = 1;
+    int tune_gemm_mt = 0;        // 128-token blocks per GEMM tile: 0 = automatic, 1 or 2
     long long* dbg_buf = nullptr;  // device timeline buffer (DBG_SLOTS entries) when the knob is on
     int tune_gemv_ksplit = 0;
     // kernels launched by forward calls since creation

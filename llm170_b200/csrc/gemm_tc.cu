@@ -31,15 +31,20 @@ namespace {
 constexpr int BM = 128;           // tokens per tile (UMMA M)
 constexpr int BN = 256;           // weight rows per tile (UMMA N)
 constexpr int BK = TILE_K;        // 64 k per stage = one 128-byte swizzle row of f16
-constexpr int NT = 6;              // TMA ring: activation tile + raw int4 tile per stage
 constexpr int NB = 2;              // ring of expanded f16 weight tiles
-constexpr int A_BYTES = BM * BK * 2;          // 16 KB
+constexpr int A_BYTES = BM * BK * 2;          // 16 KB per 128-token block
 constexpr int RAW_BYTES = BN * BK / 2;        // 8 KB
 constexpr int B_BYTES = BN * BK * 2;          // 32 KB
 constexpr int NUM_DQ_WARPS = 16;   // one 16-row block of the tile each
 constexpr int NUM_THREADS = (2 + NUM_DQ_WARPS) * 32;
-constexpr int TMEM_COLS = 256;
-constexpr int SMEM_BYTES = NT * (A_BYTES + RAW_BYTES) + NB * B_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+// MT = 128-token blocks per CTA tile (1 or 2).  With MT = 2 one expanded weight stage feeds two MMAs groups
+// (two TMEM accumulators), halving the expand work and the shared-memory traffic per flop.
+template <int MT> struct Cfg {
+    static constexpr int NT = MT == 1 ? 6 : 4;   // TMA ring: activation blocks + raw int4 tile per stage
+    static constexpr int A_STAGE = MT * A_BYTES;
+    static constexpr int TMEM_COLS = 256 * MT;
+    static constexpr int SMEM = NT * (A_STAGE + RAW_BYTES) + NB * B_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
 constexpr int GROUP_M = 8;        // m-tiles per rasterisation group (L2 reuse of the weight tiles)
 
 struct GemmArgs {
@@ -101,9 +106,13 @@ __device__ __forceinline__ uint32_t hmul2u(uint32_t a, uint32_t b) {
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
-template <int GROUP>
+template <int GROUP, int MT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
+    constexpr int NT = Cfg<MT>::NT;
+    constexpr int A_STAGE = Cfg<MT>::A_STAGE;
+    constexpr int TMEM_COLS = Cfg<MT>::TMEM_COLS;
+    constexpr int BMT = BM * MT;
     extern __shared__ unsigned char smem_dyn[];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
@@ -111,11 +120,11 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
     unsigned char* base_ptr = smem_dyn + (base - smem_u32(smem_dyn));
-    // [A ring NT x 16K][B ring NB x 32K][raw ring NT x 8K][barriers]; A and B bases are 1024-byte aligned
-    auto a_addr = [&](int s) { return base + (uint32_t)s * A_BYTES; };
-    auto b_addr = [&](int s) { return base + (uint32_t)(NT * A_BYTES) + (uint32_t)s * B_BYTES; };
-    auto raw_addr = [&](int s) { return base + (uint32_t)(NT * A_BYTES + NB * B_BYTES) + (uint32_t)s * RAW_BYTES; };
-    const uint32_t bars = base + NT * (A_BYTES + RAW_BYTES) + NB * B_BYTES;
+    // [A ring NT x MT*16K][B ring NB x 32K][raw ring NT x 8K][barriers]; A and B bases are 1024-byte aligned
+    auto a_addr = [&](int s) { return base + (uint32_t)s * A_STAGE; };
+    auto b_addr = [&](int s) { return base + (uint32_t)(NT * A_STAGE) + (uint32_t)s * B_BYTES; };
+    auto raw_addr = [&](int s) { return base + (uint32_t)(NT * A_STAGE + NB * B_BYTES) + (uint32_t)s * RAW_BYTES; };
+    const uint32_t bars = base + NT * (A_STAGE + RAW_BYTES) + NB * B_BYTES;
     auto full_bar = [&](int s) { return bars + 8u * s; };               // TMA landed (A + raw)
     auto empty_bar = [&](int s) { return bars + 8u * (NT + s); };       // MMAs that read A[s] retired
     auto bready_bar = [&](int s) { return bars + 8u * (2 * NT + s); };  // B[s] expanded
@@ -142,10 +151,10 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
         const int first_m = grp * GROUP_M;
         const int gsz = min(GROUP_M, a.m_tiles - first_m);
         const int rem = tile - grp * per_group;
-        m0 = (first_m + rem % gsz) * BM;
+        m0 = (first_m + rem % gsz) * BMT;
         n0 = (rem / gsz) * BN;
         rb0 = n0 / TILE_ROWS;
-        rows_valid = min(BM, a.m - m0);
+        rows_valid = min(BMT, a.m - m0);
     }
     const int nkb = a.k / BK;
     const int nrbv = min(BN, a.n - n0) / TILE_ROWS;  // valid 16-row blocks in this tile
@@ -190,8 +199,11 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                 if (stamp && it < 1000) {
                     a.dbg[it] = clock64();
                 }
-                mbar_expect_tx(full_bar(s), A_BYTES + nrbv * (TILE_WORDS * 4));
-                tma_load_2d(a_addr(s), &tmap_x, it * BK, m0, full_bar(s));
+                mbar_expect_tx(full_bar(s), A_STAGE + nrbv * (TILE_WORDS * 4));
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    tma_load_2d(a_addr(s) + mt * A_BYTES, &tmap_x, it * BK, m0 + mt * BM, full_bar(s));
+                }
                 // the tile's row blocks are contiguous at one k-block (k-block-major layout): one copy
                 bulk_load(raw_addr(s), a.qt + ((size_t)it * a.nrb_w + rb0) * TILE_WORDS,
                           nrbv * (TILE_WORDS * 4), full_bar(s));
@@ -214,10 +226,14 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                 if (stamp && it < 1000) {
                     a.dbg[3000 + it] = clock64();
                 }
-                const uint64_t da = umma_desc(a_addr(s)), db = umma_desc(b_addr(sb));
+                const uint64_t db = umma_desc(b_addr(sb));
 #pragma unroll
-                for (int j = 0; j < BK / 16; ++j) {
-                    umma_f16(tmem, da + 2 * j, db + 2 * j, IDESC, (it > 0 || j > 0) ? 1u : 0u);
+                for (int mt = 0; mt < MT; ++mt) {
+                    const uint64_t da = umma_desc(a_addr(s) + mt * A_BYTES);
+#pragma unroll
+                    for (int j = 0; j < BK / 16; ++j) {
+                        umma_f16(tmem + mt * 256, da + 2 * j, db + 2 * j, IDESC, (it > 0 || j > 0) ? 1u : 0u);
+                    }
                 }
                 umma_commit(empty_bar(s));
                 umma_commit(bfree_bar(sb));
@@ -307,13 +323,17 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
             if (ok) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int quad = warp & 3;
-                const int row_l = quad * 32 + lane;
-                const int row = m0 + row_l;
-                const float rw = (a.row_w != nullptr && row_l < rows_valid) ? a.row_w[row] : 1.0f;
                 const int ncols = min(BN, a.n - n0);
-                for (int c0 = 0; c0 < ncols; c0 += 32) {
+                for (int mc = 0; mc < MT * (BN / 32); ++mc) {
+                    const int mt = mc / (BN / 32), c0 = (mc % (BN / 32)) * 32;
+                    if (c0 >= ncols) {
+                        continue;
+                    }
+                    const int row_l = mt * BM + quad * 32 + lane;
+                    const int row = m0 + row_l;
+                    const float rw = (a.row_w != nullptr && row_l < rows_valid) ? a.row_w[row] : 1.0f;
                     uint32_t v[32];
-                    tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+                    tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * 256 + c0), v);
                     if (row_l < rows_valid) {
                         if (a.row_w != nullptr) {
 #pragma unroll
@@ -384,12 +404,16 @@ EncodeTiledFn encode_fn() {
 }  // namespace
 
 cudaError_t gemm_init_device() {
-    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SMEM_BYTES);
-    if (e != cudaSuccess) {
-        return e;
-    }
-    return cudaFuncSetAttribute(gemm_w4a16_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e;
+#define W4_SET(G, MTV) \
+    e = cudaFuncSetAttribute(gemm_w4a16_tc_kernel<G, MTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MTV>::SMEM); \
+    if (e != cudaSuccess) return e;
+    W4_SET(128, 1)
+    W4_SET(128, 2)
+    W4_SET(32, 1)
+    W4_SET(32, 2)
+#undef W4_SET
+    return cudaSuccess;
 }
 
 int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaStream_t st) {
@@ -419,8 +443,12 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.n = l->n;
     a.k = l->k;
     a.out_f16 = out_kind == W4A16_OUT_F16;
-    a.m_tiles = (t + BM - 1) / BM;
     a.n_tiles = (l->n + BN - 1) / BN;
+    // two 128-token blocks per CTA when that still leaves at least two waves of CTAs
+    const int mt = (tune_gemm_mt == 1 || tune_gemm_mt == 2)
+                       ? tune_gemm_mt
+                       : ((((t + 2 * BM - 1) / (2 * BM)) * a.n_tiles >= 2 * sm_count) ? 2 : 1);
+    a.m_tiles = (t + BM * mt - 1) / (BM * mt);
     a.nrb_w = l->n / TILE_ROWS;
     a.grouped = 0;
     a.tile_expert = a.tile_row0 = a.tile_rows = a.num_tiles = nullptr;
@@ -430,9 +458,17 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.dbg = dbg_buf;
     const int grid = a.m_tiles * a.n_tiles;
     if (l->group == 128) {
-        gemm_w4a16_tc_kernel<128><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map, a);
+        if (mt == 2) {
+            gemm_w4a16_tc_kernel<128, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, a);
+        } else {
+            gemm_w4a16_tc_kernel<128, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
+        }
     } else {
-        gemm_w4a16_tc_kernel<32><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map, a);
+        if (mt == 2) {
+            gemm_w4a16_tc_kernel<32, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, a);
+        } else {
+            gemm_w4a16_tc_kernel<32, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
+        }
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -483,9 +519,9 @@ int Dec::gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int 
     a.dbg = nullptr;
     const int grid = a.m_tiles * a.n_tiles;
     if (l->group == 128) {
-        gemm_w4a16_tc_kernel<128><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map, a);
+        gemm_w4a16_tc_kernel<128, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
     } else {
-        gemm_w4a16_tc_kernel<32><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(map, a);
+        gemm_w4a16_tc_kernel<32, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

@@ -72,6 +72,34 @@ def test_gemm_vs_f16_dequant_model_and_lane_oracle(dec, orc, n, k, group, t):
     dec.drop_lin("g")
 
 
+@pytest.mark.parametrize("t,k,n,group", [(300, 256, 272, 128), (257, 768, 512, 32), (64, 512, 256, 128)])
+def test_two_block_tiles_pow2_exact(dec, t, k, n, group):
+    # the 256-token tile variant (two TMEM accumulators per CTA), forced, incl. ragged last tiles
+    q, s, x, expect = pow2_case(t, k, n, group)
+    dec.upload_lin_g("p2b", q, s, n, k, group)
+    dec.set_tuning("gemm_mt", 2)
+    try:
+        y = dec.lin_forward("p2b", x_dev(x), t)
+        dec.sync()
+    finally:
+        dec.set_tuning("gemm_mt", 0)
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), expect.view(np.uint32))
+
+
+def test_tile_variants_agree_bitwise(dec):
+    n, k, t = 1024, 2048, 700
+    q, s = synth.make_linear(n, k, 128, seed=61)
+    dec.upload_lin_g("mtv", q, s, n, k, 128)
+    x = x_dev(synth.make_acts(t, k, seed=62, scale=1 / np.sqrt(k)))
+    outs = []
+    for mt in (1, 2):
+        dec.set_tuning("gemm_mt", mt)
+        outs.append(dec.lin_forward("mtv", x, t).clone())
+    dec.set_tuning("gemm_mt", 0)
+    dec.sync()
+    assert torch.equal(outs[0], outs[1])      # same k order per output element -> same bits
+
+
 def test_gemm_and_gemv_agree_on_the_same_weights(dec):
     # both kernels read the one resident copy; they differ only by the f16 rounding of the weight
     n, k = 1024, 2048
