@@ -444,10 +444,10 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.k = l->k;
     a.out_f16 = out_kind == W4A16_OUT_F16;
     a.n_tiles = (l->n + BN - 1) / BN;
-    // two 128-token blocks per CTA when that still leaves at least two waves of CTAs
+    // two 128-token blocks per CTA unless that leaves fewer CTAs than half the SMs (measured crossover)
     const int mt = (tune_gemm_mt == 1 || tune_gemm_mt == 2)
                        ? tune_gemm_mt
-                       : ((((t + 2 * BM - 1) / (2 * BM)) * a.n_tiles >= 2 * sm_count) ? 2 : 1);
+                       : ((((t + 2 * BM - 1) / (2 * BM)) * a.n_tiles * 2 >= sm_count) ? 2 : 1);
     a.m_tiles = (t + BM * mt - 1) / (BM * mt);
     a.nrb_w = l->n / TILE_ROWS;
     a.grouped = 0;
