@@ -14,7 +14,8 @@
 //               chunk = 8 consecutive k of one weight row), then signal the MMA warp
 //   warp 1      one lane issues 4 x tcgen05.mma (M128 N256 K16, f16 x f16 -> f32 in TMEM) per k-block and
 //               commits the stage back to the producer
-//   warps 2-5   epilogue: tcgen05.ld the 128 x 256 f32 accumulator, convert, store y
+//   warps 2-17  epilogue: tcgen05.ld the f32 accumulators (each warp its TMEM lane quadrant, every fourth
+//               32-column chunk), convert, store y
 // Every mbarrier wait is bounded: on expiry the kernel records a status code, all roles fall through to
 // the common exit, TMEM is released, and the host reports an error instead of hanging.
 #include <cuda.h>
@@ -31,7 +32,6 @@ namespace {
 constexpr int BM = 128;           // tokens per tile (UMMA M)
 constexpr int BN = 256;           // weight rows per tile (UMMA N)
 constexpr int BK = TILE_K;        // 64 k per stage = one 128-byte swizzle row of f16
-constexpr int NB = 2;              // ring of expanded f16 weight tiles
 constexpr int A_BYTES = BM * BK * 2;          // 16 KB per 128-token block
 constexpr int RAW_BYTES = BN * BK / 2;        // 8 KB
 constexpr int B_BYTES = BN * BK * 2;          // 32 KB
@@ -41,6 +41,7 @@ constexpr int NUM_THREADS = (2 + NUM_DQ_WARPS) * 32;
 // (two TMEM accumulators), halving the expand work and the shared-memory traffic per flop.
 template <int MT> struct Cfg {
     static constexpr int NT = MT == 1 ? 6 : 4;   // TMA ring: activation blocks + raw int4 tile per stage
+    static constexpr int NB = 2;                 // ring of expanded f16 weight tiles (3 with a shallower TMA ring measured slower)
     static constexpr int A_STAGE = MT * A_BYTES;
     static constexpr int TMEM_COLS = 256 * MT;
     static constexpr int SMEM = NT * (A_STAGE + RAW_BYTES) + NB * B_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -110,6 +111,7 @@ template <int GROUP, int MT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
     constexpr int NT = Cfg<MT>::NT;
+    constexpr int NB = Cfg<MT>::NB;
     constexpr int A_STAGE = Cfg<MT>::A_STAGE;
     constexpr int TMEM_COLS = Cfg<MT>::TMEM_COLS;
     constexpr int BMT = BM * MT;
@@ -311,8 +313,9 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                 a.dbg[2000 + it] = clock64();
             }
         }
-        if (warp < 6) {
-            // epilogue: this warp may touch TMEM lanes 32*(warp%4) .. +31
+        {
+            // epilogue by all 16 warps: a warp may touch TMEM lanes 32*(warp%4) .. +31; the four warps of a
+            // lane quadrant take every fourth 32-column chunk
             if (ok) {
                 ok = mbar_wait(accum_bar, 0, abort_flag, a.status, (5 << 16));
             }
@@ -326,7 +329,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                 const int ncols = min(BN, a.n - n0);
                 for (int mc = 0; mc < MT * (BN / 32); ++mc) {
                     const int mt = mc / (BN / 32), c0 = (mc % (BN / 32)) * 32;
-                    if (c0 >= ncols) {
+                    if (c0 >= ncols || (mc & 3) != (dw >> 2)) {
                         continue;
                     }
                     const int row_l = mt * BM + quad * 32 + lane;
