@@ -461,10 +461,11 @@ def main():
                        "l2": f"inputs larger than L2 ({bytes_step / 1e9:.2f} GB of weights per step)",
                        "launch": "cuda graph replay" + (", all-reduce fused into the row-parallel GEMV (peer loads)" if world > 1 else ""),
                        "build_s": round(t_build, 1)},
-            "roofline": {"bound": "hbm", "kernel": "gemv_w4a16_kernel<128>", "achieved": ach,
+            "roofline": {"bound": "hbm", "kernel": "gemv_w4a16_kernel<128,true,8>", "achieved": ach,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                          "peak_kind": peak_kind, "frac_of_nominal_8TBps": ach / 8000.0,
-                         "traffic": None, "launches_per_step": launches_per_step,
+                         "traffic": 43.37e6 if world == 1 else None,   # dram read+write per launch, ncu (profiles/gemv_decode_stack_launch_list.md)
+                         "launches_per_step": launches_per_step,
                          "avg_launch_us": ms_per_step * 1e3 / launches_per_step,
                          "algorithmic_bytes_per_launch": bytes_step / launches_per_step},
             "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
