@@ -380,7 +380,9 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         const unsigned char* zp = smem + p.off_xsum + (2 * t) * 4;
         const unsigned char* wbase = smem + p.off_ring + rbw0 * (TILE_WORDS * 4) + lane * 16;
 
-        float acc[RB_PER_WARP][2][4];  // two independent MMA chains per row block
+        // independent MMA chains per row block: a warp with two row blocks already has two
+        constexpr int CH = RB_PER_WARP >= 2 ? 1 : 2;
+        float acc[RB_PER_WARP][CH][4];
         uint32_t sc[RB_PER_WARP];
 #pragma unroll
         for (int r = 0; r < RB_PER_WARP; ++r) {
@@ -408,8 +410,10 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                 if (gl < ngl) {
                     sc[r] = __ldg(sp[r] + (size_t)gl * 8);  // prefetch the next group's scales
                 }
-                const float c0 = acc[r][0][0] + acc[r][1][0], c1 = acc[r][0][1] + acc[r][1][1];
-                const float c2 = acc[r][0][2] + acc[r][1][2], c3 = acc[r][0][3] + acc[r][1][3];
+                const float c0 = CH == 2 ? acc[r][0][0] + acc[r][CH - 1][0] : acc[r][0][0];
+                const float c1 = CH == 2 ? acc[r][0][1] + acc[r][CH - 1][1] : acc[r][0][1];
+                const float c2 = CH == 2 ? acc[r][0][2] + acc[r][CH - 1][2] : acc[r][0][2];
+                const float c3 = CH == 2 ? acc[r][0][3] + acc[r][CH - 1][3] : acc[r][0][3];
                 if (SUBN) {
                     tot[r][0] = fmaf(fmaf(c0, 16777216.f, z.x), sf.x, tot[r][0]);
                     tot[r][1] = fmaf(fmaf(c1, 16777216.f, z.y), sf.x, tot[r][1]);
@@ -435,10 +439,10 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                     mma16816(acc[r][0], fr, x.x, x.y);
                 }
                 expand(hsel ? w[r].w : w[r].y, fr);
-                if (first) {
-                    mma16816_z(acc[r][1], fr, x.z, x.w);
+                if (first && CH == 2) {
+                    mma16816_z(acc[r][CH - 1], fr, x.z, x.w);
                 } else {
-                    mma16816(acc[r][1], fr, x.z, x.w);
+                    mma16816(acc[r][CH - 1], fr, x.z, x.w);
                 }
             }
         };
@@ -475,12 +479,14 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                 a.dbg[17 + 2 * c] = clock64();
             }
             const unsigned char* wa = wbase + s * STAGE_BYTES;
-            if (c * CK + CK <= nloc) {
-                // group boundaries fall on even k-blocks: splits are whole groups
-                kblock(wa, xp, true, KB_PER_GROUP == 1);
-                kblock(wa + KB_BYTES, xp + 128, KB_PER_GROUP == 1, true);
-            } else {
-                kblock(wa, xp, true, true);  // odd tail: only reachable with 64-wide units (g32)
+            // group boundaries fall on even k-blocks: splits are whole groups
+            const int kbs = min(CK, nloc - c * CK);
+#pragma unroll
+            for (int kbi = 0; kbi < CK; ++kbi) {
+                if (kbi < kbs) {
+                    kblock(wa + kbi * KB_BYTES, xp + kbi * 128, kbi % KB_PER_GROUP == 0,
+                           kbi % KB_PER_GROUP == KB_PER_GROUP - 1);
+                }
             }
             xp += CK * 128;
             __syncwarp();
