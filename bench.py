@@ -174,7 +174,7 @@ def main():
     ap.add_argument("--tune", action="append", default=[], help="library knob key=value (repeatable)")
     ap.add_argument("--case", default=None,
                     help="run ONE small case instead of the benchmark, for profilers: "
-                         "gemv:<linear>:<m> or gemm:<linear>:<m>, e.g. gemm:gate_up:4096 (prints its device time)")
+                         "gemv:<linear>:<m>, gemm:<linear>:<m> or moe:<tokens>, e.g. gemm:gate_up:4096 (prints its device time)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -202,6 +202,30 @@ def main():
     for kv in args.tune:
         key, val = kv.split("=")
         dec.set_tuning(key, int(val))
+    if args.case and args.case.startswith("moe:"):
+        T = int(args.case.split(":")[1])
+        mo = synth.MOE_35B
+        ne, h, f, kk, grp = mo["n_experts"], mo["hidden"], mo["moe_ffn"], mo["top_k"], mo["group"]
+        dec.set_moe(ne, kk, f, h, grp)
+        q13, s13 = synth.make_linear_cuda(ne * 2 * f, h, grp, seed=900, device=device)
+        q2, s2 = synth.make_linear_cuda(ne * h, f, grp, seed=950, device=device)
+        dec.upload_experts(0, q13, s13, q2, s2)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(3)
+        lg = torch.randn((T, ne), generator=gen, device=device, dtype=torch.float32)
+        xm = torch.randn((T, h), generator=gen, device=device, dtype=torch.float32).to(torch.float16)
+        ym = torch.empty((T, h), device=device, dtype=torch.float32)
+        dec.moe_ffn_dev_t(0, lg, xm, T, out=ym)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            dec.moe_ffn_dev_t(0, lg, xm, T, out=ym)
+        e1.record()
+        e1.synchronize()
+        dec.kernel_status()
+        print(json.dumps({"case": args.case, "us_per_call": e0.elapsed_time(e1) * 1e3 / args.steps}))
+        os._exit(0)
     if args.case:
         kind, nm, m = args.case.split(":")
         m = int(m)
@@ -421,6 +445,44 @@ def main():
                 pre[f"M{m}"] = per
         dec.kernel_status()
         extras["prefill"] = pre
+
+    # ---- extras: MoE layer (35B-A3B class: 128 experts, hidden 2048, ffn 768, top-8, g32), T in {1, 64, 4096} ----
+    if world == 1 and not args.no_extras:
+        mo = synth.MOE_35B
+        ne, h, f, kk, grp = mo["n_experts"], mo["hidden"], mo["moe_ffn"], mo["top_k"], mo["group"]
+        dec.set_moe(ne, kk, f, h, grp)
+        nlay = 4   # rotate over 4 layers of experts (4 x 340 MB > L2)
+        for li in range(nlay):
+            q13, s13 = synth.make_linear_cuda(ne * 2 * f, h, grp, seed=900 + li, device=device)
+            q2, s2 = synth.make_linear_cuda(ne * h, f, grp, seed=950 + li, device=device)
+            dec.upload_experts(li, q13, s13, q2, s2)
+            del q13, s13, q2, s2
+        moe_res = {}
+        with torch.cuda.stream(st):
+            for T in (1, 64, 4096):
+                lg = torch.randn((T, ne), generator=g, device=device, dtype=torch.float32)
+                xm = torch.randn((T, h), generator=g, device=device, dtype=torch.float32).to(torch.float16)
+                ym = torch.empty((T, h), device=device, dtype=torch.float32)
+                for li in range(nlay):
+                    dec.moe_ffn_dev_t(li, lg, xm, T, out=ym)
+                st.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 5
+                e0.record(st)
+                for _ in range(reps):
+                    for li in range(nlay):
+                        dec.moe_ffn_dev_t(li, lg, xm, T, out=ym)
+                e1.record(st)
+                e1.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / (reps * nlay)
+                idx, _ = dec.moe_topk(lg)
+                hit = int(torch.unique(idx).numel())
+                wbytes = hit * (2 * f * h // 2 + 2 * f * (h // grp) * 2 + h * f // 2 + h * (f // grp) * 2)
+                flops = 2 * T * kk * (h * 2 * f + f * h)
+                moe_res[f"T{T}"] = {"us": round(us, 1), "experts_hit": hit,
+                                    "weight_GBps": round(wbytes / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 2)}
+        dec.kernel_status()
+        extras["moe_35b_a3b_layer"] = moe_res
 
     # ---- CPU baseline (rank 0, N=1): the oracle on a bounded sample ----------------------------------
     cpu_baseline = None

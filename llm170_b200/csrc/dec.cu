@@ -190,6 +190,9 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
     a.cons_warps = tune_gemv_warps;
     a.status = gemm_status;
     a.cluster = (tune_gemv_cluster && ks >= 2 && ks <= 8 && !allreduce) ? 1 : 0;
+    a.grouped = 0;
+    a.row_w = nullptr;
+    a.nrb_w = 0;
     a.tp = TpComm{};
     if (allreduce) {
         if (tp.world < 2 || tp_peer[(tp.rank + 1) % tp.world] == nullptr) {
@@ -209,6 +212,65 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
     cudaError_t e = launch_gemv(a, grid_x, st);
     if (e != cudaSuccess) {
         return cuda_fail("launch gemv", e);
+    }
+    launches++;
+    return 0;
+}
+
+// Decode-time MoE: every <=8-row segment of an expert (device table from moe.cu) is one GEMV over that
+// expert's rows of the stacked matrix `l`; xs / out hold the sorted rows.  Takes the place of the reference's
+// w4a16_gemv_experts_* kernels (crates/backend-gpu/src/rawcuda/assets/gptq4.cu:317-374,
+// crates/backend-gpu/src/rawcuda/w4a16_dec/moe/moe_gemv.rs:92-114).
+int Dec::gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert, const MoeBufs& b, int max_tiles,
+                      int est_tiles, const float* row_w, cudaStream_t st) {
+    GemvArgs a{};
+    a.nseg = 1;
+    a.k = l->k;
+    a.group = l->group;
+    a.seg[0].qt = (const uint4*)l->qt;
+    a.seg[0].st = (const uint32_t*)l->st;
+    a.seg[0].out = out;
+    a.seg[0].n = n_per_expert;
+    a.m = GEMV_MAX_M;            // sizes the staging area; each segment brings its own row count
+    a.out_f16 = 1;
+    a.x = (const uint16_t*)xs;
+    const int cps = gemv_plan_ctas(a);  // CTAs per segment (256 rows each)
+    const int grid_x = cps * max_tiles;
+    int ks = tune_gemv_ksplit > 0 ? tune_gemv_ksplit
+                                  : gemv_pick_ksplit(cps * est_tiles, a.k, a.group, GEMV_MAX_M, sm_count, 8, tune_gemv_stages);
+    if (ks > 8) {
+        ks = 8;  // the splits of a segment always reduce inside a cluster (no global scratch per segment)
+    }
+    const int unit = a.group > TILE_K ? a.group : TILE_K;
+    if (ks > a.k / unit) {
+        ks = a.k / unit;
+    }
+    if (gemv_smem_bytes(a.k, a.group, GEMV_MAX_M, ks, tune_gemv_stages) > 112 * 1024) {
+        return fail("w4a16 grouped gemv: k=%d too large", a.k);
+    }
+    a.ksplit = ks;
+    a.subnormal = tune_gemv_subnormal;
+    a.pdl = 0;
+    a.ring_stages = tune_gemv_stages;
+    a.cons_warps = tune_gemv_warps;
+    a.cluster = ks >= 2 ? 1 : 0;
+    a.status = gemm_status;
+    a.dbg = nullptr;
+    a.grouped = 1;
+    a.ctas_per_seg = cps;
+    a.expert0 = moe.e0;
+    a.tile_expert = b.tile_expert;
+    a.tile_row0 = b.tile_row0;
+    a.tile_rows = b.tile_rows;
+    a.num_tiles = b.n_tiles;
+    a.row_w = row_w;
+    a.nrb_w = l->n / TILE_ROWS;
+    a.tp = TpComm{};
+    a.part = part;
+    a.counters = counters;
+    cudaError_t e = launch_gemv(a, grid_x, st);
+    if (e != cudaSuccess) {
+        return cuda_fail("launch grouped gemv", e);
     }
     launches++;
     return 0;

@@ -78,12 +78,14 @@ struct Dec {
              cudaStream_t st, bool allreduce = false);
     int gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaStream_t st);
     int gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int n_per_expert, const MoeBufs& b,
-                     int max_tiles, const float* row_w, cudaStream_t st);
+                     int max_tiles, int mt, const float* row_w, cudaStream_t st);
     // row-parallel tensor parallelism (fused all-reduce in the GEMV): local exchange block + peer mappings
     TpComm tp{};
     void* tp_block = nullptr;
     void* tp_peer[TP_MAX_WORLD] = {};
     int tp_max_rows = 0;
+    int gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert, const MoeBufs& b, int max_tiles,
+                     int est_tiles, const float* row_w, cudaStream_t st);
     MoeCfg moe;
     MoeBufs mb;
     int ensure_moe(int t, cudaStream_t st);

@@ -484,7 +484,7 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
 // Grouped GEMM over expert segments: `l` stacks the local experts along n (n_per_expert rows each);
 // xs holds the gathered rows (sorted by expert), the m-tile table lives on the device (moe.cu).
 int Dec::gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int n_per_expert, const MoeBufs& b,
-                      int max_tiles, const float* row_w, cudaStream_t st) {
+                      int max_tiles, int mt, const float* row_w, cudaStream_t st) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) {
         return fail("w4a16 gemm: cuTensorMapEncodeTiled is not available from the driver");
@@ -522,9 +522,17 @@ int Dec::gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int 
     a.dbg = nullptr;
     const int grid = a.m_tiles * a.n_tiles;
     if (l->group == 128) {
-        gemm_w4a16_tc_kernel<128, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
+        if (mt == 2) {
+            gemm_w4a16_tc_kernel<128, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, a);
+        } else {
+            gemm_w4a16_tc_kernel<128, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
+        }
     } else {
-        gemm_w4a16_tc_kernel<32, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
+        if (mt == 2) {
+            gemm_w4a16_tc_kernel<32, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, a);
+        } else {
+            gemm_w4a16_tc_kernel<32, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
+        }
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

@@ -203,9 +203,27 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
             si = i;
         }
     }
-    const GemvSeg& sg = a.seg[si];
+    GemvSeg sg = a.seg[si];
+    int m_loc = a.m;                                       // tokens of this CTA (grouped mode: rows of its tile)
+    const uint16_t* x_loc = a.x;
+    int rb_cta0 = ((int)blockIdx.x - sg.cta0) * CTA_RB;    // first row block of this CTA within its output
+    int rb_w0 = rb_cta0;                                   // ... and within the resident weight matrix
+    int row_base = 0;                                      // sorted row of token 0 (grouped mode)
+    if (a.grouped) {
+        const int ti = (int)blockIdx.x / a.ctas_per_seg;
+        if (ti >= *a.num_tiles) {
+            return;  // the grid is sized for the worst case; whole clusters leave together
+        }
+        row_base = a.tile_row0[ti];
+        m_loc = a.tile_rows[ti];
+        x_loc = x_loc + (size_t)row_base * a.k;
+        rb_cta0 = ((int)blockIdx.x % a.ctas_per_seg) * CTA_RB;
+        rb_w0 = (a.tile_expert[ti] - a.expert0) * (sg.n / TILE_ROWS) + rb_cta0;
+        sg.out = a.out_f16 ? (void*)(reinterpret_cast<__half*>(sg.out) + (size_t)row_base * sg.n)
+                           : (void*)(reinterpret_cast<float*>(sg.out) + (size_t)row_base * sg.n);
+    }
     const int nrb_seg = sg.n / TILE_ROWS;
-    const int rb_cta0 = ((int)blockIdx.x - sg.cta0) * CTA_RB;    // first row block of this CTA
+    const int nrb_pitch = a.nrb_w > 0 ? a.nrb_w : nrb_seg;
     const int nrbv = min(CTA_RB, nrb_seg - rb_cta0);             // valid row blocks in this CTA
 
     int kb0, kb1;
@@ -241,15 +259,15 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         }
         mbar_init_fence();
     }
-    if (SUBN && a.m < GEMV_MAX_M) {
+    if (SUBN && m_loc < GEMV_MAX_M) {
         float* xsum = reinterpret_cast<float*>(smem + p.off_xsum);
         for (int i = threadIdx.x; i < ngl * GEMV_MAX_M; i += blockDim.x) {
             xsum[i] = 0.f;
         }
     }
     // the all-zero token row read by MMA columns >= m
-    if (a.m < GEMV_MAX_M) {
-        uint4* z = reinterpret_cast<uint4*>(smem + (size_t)a.m * p.x_stride * 2);
+    if (m_loc < GEMV_MAX_M) {
+        uint4* z = reinterpret_cast<uint4*>(smem + (size_t)m_loc * p.x_stride * 2);
         for (int i = threadIdx.x; i < p.x_stride / 8; i += blockDim.x) {
             z[i] = make_uint4(0, 0, 0, 0);
         }
@@ -258,8 +276,8 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
 
     // chunk c -> stage c % S: CK bulk copies of the CTA's rows at one k-block each (contiguous in T64)
     const unsigned char* wsrc = reinterpret_cast<const unsigned char*>(sg.qt) +
-                                ((size_t)kb0 * nrb_seg + rb_cta0) * (TILE_WORDS * 4);
-    const size_t kb_pitch = (size_t)nrb_seg * (TILE_WORDS * 4);
+                                ((size_t)kb0 * nrb_pitch + rb_w0) * (TILE_WORDS * 4);
+    const size_t kb_pitch = (size_t)nrb_pitch * (TILE_WORDS * 4);
     auto issue_chunk = [&](int c) {
         const int kbs = min(CK, nloc - c * CK);
         const int s = c % S;
@@ -286,9 +304,9 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) {
-        mbar_expect_tx(xbar, a.m * halves * 2);
-        for (int tok = 0; tok < a.m; ++tok) {
-            bulk_load(sbase + tok * p.x_stride * 2, a.x + (size_t)tok * a.k + (size_t)kb0 * TILE_K, halves * 2, xbar);
+        mbar_expect_tx(xbar, m_loc * halves * 2);
+        for (int tok = 0; tok < m_loc; ++tok) {
+            bulk_load(sbase + tok * p.x_stride * 2, x_loc + (size_t)tok * a.k + (size_t)kb0 * TILE_K, halves * 2, xbar);
         }
         if (stamp) {
             a.dbg[1] = clock64();
@@ -321,14 +339,14 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
             constexpr int TPP = PIECES >= 8 ? 8 : PIECES;  // threads per (group, token): 8 (g128) or 4 (g32)
             constexpr int PER_T = PIECES / TPP;
             const int sub = threadIdx.x % TPP;
-            for (int pr0 = 0; pr0 < ngl * a.m; pr0 += (CONS_WARPS * 32) / TPP) {
+            for (int pr0 = 0; pr0 < ngl * m_loc; pr0 += (CONS_WARPS * 32) / TPP) {
                 const int pr = pr0 + threadIdx.x / TPP;
                 float v = 0.f;
                 int grp = 0, tok = 0;
-                const bool live = pr < ngl * a.m;
+                const bool live = pr < ngl * m_loc;
                 if (live) {
-                    grp = pr / a.m;
-                    tok = pr - grp * a.m;
+                    grp = pr / m_loc;
+                    tok = pr - grp * m_loc;
                     const uint4* xr =
                         reinterpret_cast<const uint4*>(smem + ((size_t)tok * p.x_stride + (size_t)grp * GROUP) * 2);
 #pragma unroll
@@ -371,11 +389,11 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         const uint32_t* sp[RB_PER_WARP];
 #pragma unroll
         for (int r = 0; r < RB_PER_WARP; ++r) {
-            const int rbg = rb_cta0 + rbw0 + (r < nvalid ? r : 0);
+            const int rbg = rb_w0 + rbw0 + (r < nvalid ? r : 0);
             sp[r] = sg.st + ((size_t)rbg * ng + grp0) * 8 + g;
         }
         // B fragment source: token g (the zero row when g >= m), this lane's 8 k of each half k-block
-        const int xrow_i = g < a.m ? g : a.m;
+        const int xrow_i = g < m_loc ? g : m_loc;
         const unsigned char* xp = smem + (size_t)(xrow_i * p.x_stride + 8 * t) * 2;
         const unsigned char* zp = smem + p.off_xsum + (2 * t) * 4;
         const unsigned char* wbase = smem + p.off_ring + rbw0 * (TILE_WORDS * 4) + lane * 16;
@@ -531,7 +549,12 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
 #pragma unroll
                 for (int j = 0; j < 2; ++j) {
                     const int tok = 2 * t + j;
-                    if (tok < a.m) {
+                    if (tok < m_loc) {
+                        if (a.row_w != nullptr) {
+                            const float rw = a.row_w[row_base + tok];
+                            tot[r][j] *= rw;
+                            tot[r][2 + j] *= rw;
+                        }
                         if (tp_on) {
                             float* o = a.tp.buf[a.tp.rank] + (size_t)(s_seq & 1u) * a.tp.area_floats;
                             o[(size_t)row0 * GEMV_MAX_M + tok] = tot[r][j];
@@ -574,8 +597,8 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         const int per = (nrows_c + a.ksplit - 1) / a.ksplit;
         const int lr_begin = split * per, lr_end = min(nrows_c, lr_begin + per);
         const uint32_t pbase = sbase + p.off_ring;
-        for (int i = threadIdx.x; i < (lr_end - lr_begin) * a.m; i += blockDim.x) {
-            const int lr = lr_begin + i / a.m, tok = i % a.m;
+        for (int i = threadIdx.x; i < (lr_end - lr_begin) * m_loc; i += blockDim.x) {
+            const int lr = lr_begin + i / m_loc, tok = i % m_loc;
             // all splits' loads first (a cluster has at most 8 CTAs), then the sum in split order
             float v[8];
 #pragma unroll
@@ -590,6 +613,9 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                 }
             }
             const int row = rb_cta0 * TILE_ROWS + lr;
+            if (a.row_w != nullptr) {
+                sum *= a.row_w[row_base + tok];
+            }
             if (a.out_f16) {
                 reinterpret_cast<__half*>(sg.out)[(size_t)tok * sg.n + row] = __float2half_rn(sum);
             } else {
@@ -629,7 +655,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     for (int i = threadIdx.x; i < ROWS_PER_CTA * (GEMV_MAX_M / 2); i += blockDim.x) {
         // one thread sums a (row, token pair): consecutive threads read consecutive float2
         const int lr = i / (GEMV_MAX_M / 2), tp = i % (GEMV_MAX_M / 2);
-        if (lr < nrows && 2 * tp < a.m) {
+        if (lr < nrows && 2 * tp < m_loc) {
             const float* src = a.part + (size_t)blockIdx.x * (ROWS_PER_CTA * GEMV_MAX_M) + lr * GEMV_MAX_M + 2 * tp;
             const size_t stride = (size_t)gridDim.x * (ROWS_PER_CTA * GEMV_MAX_M);
             float2 sum = make_float2(0.f, 0.f);
@@ -643,8 +669,11 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 const int tok = 2 * tp + j;
-                if (tok < a.m) {
-                    const float v = j ? sum.y : sum.x;
+                if (tok < m_loc) {
+                    float v = j ? sum.y : sum.x;
+                    if (a.row_w != nullptr) {
+                        v *= a.row_w[row_base + tok];
+                    }
                     if (tp_on) {
                         a.tp.buf[a.tp.rank][(size_t)(s_seq & 1u) * a.tp.area_floats + (size_t)row * GEMV_MAX_M + tok] = v;
                     } else if (a.out_f16) {

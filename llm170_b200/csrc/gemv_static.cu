@@ -111,6 +111,9 @@ extern "C" int w4a16_sk_single_static(w4a16_dec* dec, const char* name, const vo
     a.ring_stages = d.tune_gemv_stages;
     a.cons_warps = d.tune_gemv_warps;
     a.cluster = 0;  // this entry point exists for its global scratch; keep the ticketed reduce
+    a.grouped = 0;
+    a.row_w = nullptr;
+    a.nrb_w = 0;
     a.tp = TpComm{};
     a.status = d.gemm_status;
     a.dbg = nullptr;

@@ -62,6 +62,17 @@ struct GemvArgs {
     long long* dbg;     // optional timeline buffer (diagnostic), CTA (0,0) only
     int dbg_seq;        // launch sequence number (slot for the per-launch start/end stamps)
     int pdl;            // 1: launch with programmatic stream serialization (overlaps the previous kernel's tail)
+    // grouped (MoE decode) mode: blockIdx.x / ctas_per_seg indexes a device table of <=8-row segments; the
+    // single segment seg[0] then describes the stacked expert matrix (n = rows per expert)
+    int grouped;
+    int ctas_per_seg;
+    int expert0;
+    const int* tile_expert;
+    const int* tile_row0;
+    const int* tile_rows;
+    const int* num_tiles;
+    const float* row_w;   // optional factor per sorted row, applied at the final store
+    int nrb_w;            // 16-row blocks of the whole resident matrix (tile pitch); 0 = seg n / 16
     TpComm tp;          // fused all-reduce over peers (row-parallel); tp.world <= 1: off
     int* status;        // device word that records the first bounded wait that expired
 };

@@ -92,30 +92,39 @@ __global__ void moe_count_kernel(const int* __restrict__ idx, int* __restrict__ 
     }
 }
 
-// One block: exclusive offsets of the local experts' segments and the m-tile table of the grouped GEMM:
-// tile i -> (expert, first sorted row, valid rows).  Also clears the placement cursors.
+// One block of 1024 threads (n_exp <= 1024): exclusive offsets of the local experts' segments and the m-tile
+// table of the grouped GEMM, tile i -> (expert, first sorted row, valid rows), both by a shared-memory scan.
+// Also clears the placement cursors.
 __global__ void moe_offsets_kernel(const int* __restrict__ cnt, int* __restrict__ off, int* __restrict__ cursor,
                                    int* __restrict__ tile_expert, int* __restrict__ tile_row0,
                                    int* __restrict__ tile_rows, int* __restrict__ n_tiles, int* __restrict__ n_rows,
                                    int n_exp, int e0, int e1, int bm) {
-    if (threadIdx.x == 0) {
-        int pos = 0, nt = 0;
-        for (int e = e0; e < e1; ++e) {
-            const int c = cnt[e];
-            off[e] = pos;
-            for (int r = 0; r < c; r += bm) {
-                tile_expert[nt] = e;
-                tile_row0[nt] = pos + r;
-                tile_rows[nt] = min(bm, c - r);
-                ++nt;
-            }
-            pos += c;
-        }
-        *n_tiles = nt;
-        *n_rows = pos;
+    __shared__ int s_rows[1024], s_tiles[1024];
+    const int e = threadIdx.x;
+    const int c = (e >= e0 && e < e1) ? cnt[e] : 0;
+    s_rows[e] = c;
+    s_tiles[e] = (c + bm - 1) / bm;
+    __syncthreads();
+    for (int d = 1; d < 1024; d <<= 1) {   // inclusive Hillis-Steele scan of both arrays
+        const int r = e >= d ? s_rows[e - d] : 0, t = e >= d ? s_tiles[e - d] : 0;
+        __syncthreads();
+        s_rows[e] += r;
+        s_tiles[e] += t;
+        __syncthreads();
     }
-    for (int e = threadIdx.x; e < n_exp; e += blockDim.x) {
+    const int row0 = s_rows[e] - c, tile0 = s_tiles[e] - (c + bm - 1) / bm;
+    if (e < n_exp) {
+        off[e] = row0;
         cursor[e] = 0;
+    }
+    for (int r = 0, i = tile0; r < c; r += bm, ++i) {
+        tile_expert[i] = e;
+        tile_row0[i] = row0 + r;
+        tile_rows[i] = min(bm, c - r);
+    }
+    if (e == 1023) {
+        *n_tiles = s_tiles[e];
+        *n_rows = s_rows[e];
     }
 }
 
@@ -145,15 +154,25 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ x, uint4* __restrict
     }
 }
 
-// act[pos][c] = f16( silu(gate) * up ),  c13 = [rows][2*ffn] with gate in the first half
+// act[pos][c] = f16( silu(gate) * up ),  c13 = [rows][2*ffn] with gate in the first half; 8 outputs per thread
 __global__ void moe_act_silu_kernel(const __half* __restrict__ c13, __half* __restrict__ act, const int* __restrict__ n_rows,
                                     int ffn) {
-    const size_t total = (size_t)(*n_rows) * ffn;
+    const int f8 = ffn / 8;
+    const size_t total = (size_t)(*n_rows) * f8;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t r = i / ffn, c = i % ffn;
-        const float g = __half2float(c13[r * 2 * ffn + c]);
-        const float u = __half2float(c13[r * 2 * ffn + ffn + c]);
-        act[i] = __float2half_rn((g / (1.0f + expf(-g))) * u);
+        const size_t r = i / f8, c = (i % f8) * 8;
+        const uint4 gv = *reinterpret_cast<const uint4*>(c13 + r * 2 * ffn + c);
+        const uint4 uv = *reinterpret_cast<const uint4*>(c13 + r * 2 * ffn + ffn + c);
+        const __half2* gh = reinterpret_cast<const __half2*>(&gv);
+        const __half2* uh = reinterpret_cast<const __half2*>(&uv);
+        uint4 ov;
+        __half2* oh = reinterpret_cast<__half2*>(&ov);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 g = __half22float2(gh[j]), u = __half22float2(uh[j]);
+            oh[j] = __floats2half2_rn((g.x / (1.0f + expf(-g.x))) * u.x, (g.y / (1.0f + expf(-g.y))) * u.y);
+        }
+        *reinterpret_cast<uint4*>(act + r * ffn + c) = ov;
     }
 }
 
@@ -162,20 +181,36 @@ __global__ void moe_act_silu_kernel(const __half* __restrict__ c13, __half* __re
 template <bool OUT_F16>
 __global__ void moe_combine_kernel(const __half* __restrict__ c2, void* __restrict__ out, const int* __restrict__ pos_of_slot,
                                    int t, int h, int k) {
-    const size_t total = (size_t)t * h;
+    const int h8 = h / 8;
+    const size_t total = (size_t)t * h8;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int r = (int)(i / h), c = (int)(i % h);
-        float acc = 0.f;
+        const int r = (int)(i / h8), c = (int)(i % h8) * 8;
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int j = 0; j < k; ++j) {
             const int pos = pos_of_slot[r * k + j];
             if (pos >= 0) {
-                acc += __half2float(c2[(size_t)pos * h + c]);
+                const uint4 v = *reinterpret_cast<const uint4*>(c2 + (size_t)pos * h + c);
+                const __half2* vh = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __half22float2(vh[q]);
+                    acc[2 * q] += f.x;
+                    acc[2 * q + 1] += f.y;
+                }
             }
         }
         if (OUT_F16) {
-            ((__half*)out)[i] = __float2half_rn(acc);
+            uint4 ov;
+            __half2* oh = reinterpret_cast<__half2*>(&ov);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                oh[q] = __floats2half2_rn(acc[2 * q], acc[2 * q + 1]);
+            }
+            *reinterpret_cast<uint4*>((__half*)out + (size_t)r * h + c) = ov;
         } else {
-            ((float*)out)[i] = acc;
+            float4* o = reinterpret_cast<float4*>((float*)out + (size_t)r * h + c);
+            o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
         }
     }
 }
@@ -209,7 +244,7 @@ void launch_moe_topk(const float* logits, int* idx, float* wt, int t, int n_exp,
 void launch_moe_align(const MoeBufs& b, int ns, int n_exp, int e0, int e1, int bm, cudaStream_t st) {
     cudaMemsetAsync(b.cnt, 0, (size_t)n_exp * sizeof(int), st);
     moe_count_kernel<<<blocks_for(ns, 256), 256, 0, st>>>(b.idx, b.cnt, ns, e0, e1);
-    moe_offsets_kernel<<<1, 256, 0, st>>>(b.cnt, b.off, b.cursor, b.tile_expert, b.tile_row0, b.tile_rows, b.n_tiles,
+    moe_offsets_kernel<<<1, 1024, 0, st>>>(b.cnt, b.off, b.cursor, b.tile_expert, b.tile_row0, b.tile_rows, b.n_tiles,
                                           b.n_rows, n_exp, e0, e1, bm);
     moe_place_kernel<<<blocks_for(ns, 256), 256, 0, st>>>(b.idx, b.off, b.cursor, b.pos_of_slot, b.slot_of_pos, ns, e0, e1);
     moe_row_weight_kernel<<<blocks_for(ns, 256), 256, 0, st>>>(b.wt, b.slot_of_pos, b.pos_of_slot, b.row_w, ns);
@@ -221,12 +256,12 @@ void launch_moe_gather(const void* x, const MoeBufs& b, int ns, int k, int h, cu
 }
 
 void launch_moe_act(const MoeBufs& b, int rows_upper, int ffn, cudaStream_t st) {
-    moe_act_silu_kernel<<<blocks_for((size_t)rows_upper * ffn, 256), 256, 0, st>>>((const __half*)b.c13, (__half*)b.act,
+    moe_act_silu_kernel<<<blocks_for((size_t)rows_upper * (ffn / 8), 256), 256, 0, st>>>((const __half*)b.c13, (__half*)b.act,
                                                                                  b.n_rows, ffn);
 }
 
 void launch_moe_combine(const MoeBufs& b, void* out, int t, int h, int k, int out_f16, cudaStream_t st) {
-    const int g = blocks_for((size_t)t * h, 256);
+    const int g = blocks_for((size_t)t * (h / 8), 256);
     if (out_f16) {
         moe_combine_kernel<true><<<g, 256, 0, st>>>((const __half*)b.c2, out, b.pos_of_slot, t, h, k);
     } else {

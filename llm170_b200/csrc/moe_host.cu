@@ -11,7 +11,7 @@
 namespace w4 {
 
 namespace {
-constexpr int MOE_BM = 128;  // rows per m-tile of the grouped GEMM
+constexpr int MOE_BM = 128;  // rows per m-tile of the grouped GEMM (256 when experts get enough rows)
 
 std::string w13_name(int layer) { return "\x01moe." + std::to_string(layer) + ".w13"; }
 std::string w2_name(int layer) { return "\x01moe." + std::to_string(layer) + ".w2"; }
@@ -44,7 +44,7 @@ int Dec::ensure_moe(int t, cudaStream_t st) {
     cudaDeviceSynchronize();
     free_moe();
     const size_t slots = (size_t)t * moe.top_k;
-    const int max_tiles = (int)((slots + MOE_BM - 1) / MOE_BM) + (moe.e1 - moe.e0);
+    const int max_tiles = (int)((slots + 7) / 8) + (moe.e1 - moe.e0);   // worst case: 8-row segments
     cudaError_t e = cudaSuccess;
     auto ok = [&](cudaError_t r) {
         if (e == cudaSuccess) {
@@ -92,17 +92,39 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
         return rc;
     }
     const int ns = t * moe.top_k;
-    const int max_tiles = (ns + MOE_BM - 1) / MOE_BM + (moe.e1 - moe.e0);
+    const int n_local = moe.e1 - moe.e0;
     launch_moe_topk(logits, mb.idx, mb.wt, t, moe.n_experts, moe.top_k, st);
-    launch_moe_align(mb, ns, moe.n_experts, moe.e0, moe.e1, MOE_BM, st);
-    launch_moe_gather(x16, mb, ns, moe.top_k, moe.hidden, st);
     launches += 6;
-    if (int rc = gemm_grouped(&i13->second, mb.xs, ns, mb.c13, 2 * moe.ffn, mb, max_tiles, nullptr, st)) {
-        return rc;
-    }
-    launch_moe_act(mb, ns, moe.ffn, st);
-    if (int rc = gemm_grouped(&i2->second, mb.act, ns, mb.c2, moe.hidden, mb, max_tiles, mb.row_w, st)) {
-        return rc;
+    if ((long long)ns <= 8LL * moe.n_experts) {
+        // decode-sized batches (on average at most 8 rows per expert): the op is weight streaming, so every
+        // <=8-row segment of an expert runs through the GEMV kernel instead of a padded 128-row MMA tile
+        const int max_tiles = (ns + 7) / 8 + n_local;
+        const int est_tiles = ns < n_local ? ns : n_local;   // segments expected to be non-empty (split-K sizing)
+        if (max_tiles > mb.max_tiles) {
+            return fail("w4a16 moe_ffn: tile table too small");
+        }
+        launch_moe_align(mb, ns, moe.n_experts, moe.e0, moe.e1, 8, st);
+        launch_moe_gather(x16, mb, ns, moe.top_k, moe.hidden, st);
+        if (int rc = gemv_grouped(&i13->second, mb.xs, mb.c13, 2 * moe.ffn, mb, max_tiles, est_tiles, nullptr, st)) {
+            return rc;
+        }
+        launch_moe_act(mb, ns, moe.ffn, st);
+        if (int rc = gemv_grouped(&i2->second, mb.act, mb.c2, moe.hidden, mb, max_tiles, est_tiles, mb.row_w, st)) {
+            return rc;
+        }
+    } else {
+        // 256-row tiles (two accumulators per CTA) once the average expert segment fills most of one
+        const int bm = ((long long)ns * 4 >= (long long)moe.n_experts * 3 * 256) ? 256 : MOE_BM;
+        const int max_tiles = (ns + bm - 1) / bm + n_local;
+        launch_moe_align(mb, ns, moe.n_experts, moe.e0, moe.e1, bm, st);
+        launch_moe_gather(x16, mb, ns, moe.top_k, moe.hidden, st);
+        if (int rc = gemm_grouped(&i13->second, mb.xs, ns, mb.c13, 2 * moe.ffn, mb, max_tiles, bm / 128, nullptr, st)) {
+            return rc;
+        }
+        launch_moe_act(mb, ns, moe.ffn, st);
+        if (int rc = gemm_grouped(&i2->second, mb.act, ns, mb.c2, moe.hidden, mb, max_tiles, bm / 128, mb.row_w, st)) {
+            return rc;
+        }
     }
     launch_moe_combine(mb, y, t, moe.hidden, moe.top_k, out_kind == W4A16_OUT_F16, st);
     launches += 2;

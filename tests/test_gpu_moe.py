@@ -42,8 +42,10 @@ def test_topk_matches_oracle(dec, orc, t, n_exp, k):
         assert np.allclose([w for _, w in want], wt[i], rtol=0, atol=2e-7)
 
 
+# small t*k/n_exp -> grouped GEMV segments of <=8 rows; larger -> grouped tensor-core GEMM with 128- or 256-row tiles
 @pytest.mark.parametrize("t,n_exp,k,f,h,group", [(1, 8, 2, 64, 128, 32), (9, 8, 2, 128, 256, 32), (64, 16, 4, 256, 512, 32),
-                                                (300, 8, 2, 192, 256, 32), (40, 4, 2, 256, 256, 128)])
+                                                (300, 8, 2, 192, 256, 32), (40, 4, 2, 256, 256, 128),
+                                                (30, 16, 4, 320, 576, 32), (1000, 4, 2, 128, 256, 32)])
 def test_moe_ffn_vs_oracle(dec, orc, t, n_exp, k, f, h, group):
     w13_q, w13_s, w2_q, w2_s = synth.make_experts(n_exp, f, h, group, seed=7 + t)
     x = synth.make_acts(t, h, seed=11 + t)
