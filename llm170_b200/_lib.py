@@ -9,7 +9,8 @@ import os
 import re
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SO_PATH = os.path.join(HERE, "libw4a16_b200.so")
+# W4A16_B200_LIB names another build of the same library (A/B timing of two builds); default: the in-tree one
+SO_PATH = os.environ.get("W4A16_B200_LIB") or os.path.join(HERE, "libw4a16_b200.so")
 HEADER = os.path.join(os.path.dirname(HERE), "include", "w4a16_b200.h")
 
 _lib = None

@@ -47,6 +47,15 @@ __device__ __forceinline__ void mma16816_z(float (&c)[4], const uint32_t (&a)[4]
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
 }
 
+// first MMA of a group when the accumulator starts from given values (the zero-point term of the group)
+__device__ __forceinline__ void mma16816_c(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
+                                           const float4& c) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c.x), "f"(c.y), "f"(c.z), "f"(c.w));
+}
+
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -93,10 +102,15 @@ __host__ __forceinline__ int max_split_kblocks(int k, int group, int ksplit) {
     return mx;
 }
 
+constexpr int GEMV_SMEM_LIMIT = 112 * 1024;       // two CTAs per SM
+constexpr int SC_STAGE_MAX = 32 * 1024;           // most scale bytes a CTA stages in shared memory
+
 struct SmemPlan {
     int x_stride;   // halves per token row (byte stride = 64 mod 128: conflict-free 128-bit reads)
     int x_rows;     // token rows staged (m, plus one all-zero row when m < 8)
-    int off_xsum;   // f32 [groups][8]: -8 * sum of x over the group, per token
+    int off_xsum;   // f32 [groups][4 lane columns][4]: the zero-point term of each group as MMA C operands
+    int off_sc;     // u32 [16 row blocks][groups][8]: this CTA's scale pairs (when sc_staged)
+    int sc_staged;  // 1: the scales of the CTA's rows and K range are copied to shared memory up front
     int off_ring;   // stages x STAGE_BYTES, 1024-byte aligned
     int off_bars;   // xbar, full[stages], empty[stages]
     int stages;
@@ -107,12 +121,20 @@ __host__ SmemPlan make_plan(int k, int group, int m, int ksplit, int stages) {
     SmemPlan p;
     p.stages = stages < 2 ? 2 : (stages > MAX_STAGES ? MAX_STAGES : stages);
     const int halves = max_split_kblocks(k, group, ksplit) * TILE_K;
+    const int ngl = halves / group;
     p.x_stride = halves + 32;
     p.x_rows = m < GEMV_MAX_M ? m + 1 : m;
     int off = p.x_rows * p.x_stride * 2;
     off = (off + 127) & ~127;
     p.off_xsum = off;
-    off += (halves / group) * GEMV_MAX_M * 4;
+    off += ngl * 16 * 4;
+    p.off_sc = off;
+    const int sc_bytes = ngl * CTA_RB * 32;
+    const int rest = 1024 + p.stages * STAGE_BYTES + (1 + 2 * p.stages) * 8;
+    p.sc_staged = sc_bytes <= SC_STAGE_MAX && off + sc_bytes + rest <= GEMV_SMEM_LIMIT;
+    if (p.sc_staged) {
+        off += sc_bytes;
+    }
     off = (off + 1023) & ~1023;
     p.off_ring = off;
     off += p.stages * STAGE_BYTES;
@@ -261,7 +283,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     }
     if (SUBN && m_loc < GEMV_MAX_M) {
         float* xsum = reinterpret_cast<float*>(smem + p.off_xsum);
-        for (int i = threadIdx.x; i < ngl * GEMV_MAX_M; i += blockDim.x) {
+        for (int i = threadIdx.x; i < ngl * 16; i += blockDim.x) {
             xsum[i] = 0.f;
         }
     }
@@ -278,9 +300,8 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     const unsigned char* wsrc = reinterpret_cast<const unsigned char*>(sg.qt) +
                                 ((size_t)kb0 * nrb_pitch + rb_w0) * (TILE_WORDS * 4);
     const size_t kb_pitch = (size_t)nrb_pitch * (TILE_WORDS * 4);
-    auto issue_chunk = [&](int c) {
+    auto issue_chunk = [&](int c, int s) {
         const int kbs = min(CK, nloc - c * CK);
-        const int s = c % S;
         const uint32_t bytes = (uint32_t)nrbv * (TILE_WORDS * 4);
         mbar_expect_tx(full_bar(s), kbs * bytes);
         for (int i = 0; i < kbs; ++i) {
@@ -291,7 +312,18 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     const bool is_producer = warp == CONS_WARPS;
     if (is_producer && lane == 0) {
         for (int c = 0; c < S && c < nchunks; ++c) {
-            issue_chunk(c);
+            issue_chunk(c, c);
+        }
+    }
+    if (!is_producer && p.sc_staged) {
+        // this CTA's scale pairs, [row block][group][8], fetched while the previous kernel drains
+        uint4* scs = reinterpret_cast<uint4*>(smem + p.off_sc);
+        const int per_rb = ngl * 2;                     // 16-byte pieces per row block
+        const int ng_all = a.k / GROUP;
+        const size_t grp_first = (size_t)kb0 * GROUPS_PER_KB / KB_PER_GROUP;
+        for (int i = threadIdx.x; i < nrbv * per_rb; i += CONS_WARPS * 32) {
+            const int rb = i / per_rb, rest = i - rb * per_rb;
+            scs[i] = __ldg(reinterpret_cast<const uint4*>(sg.st + ((size_t)(rb_w0 + rb) * ng_all + grp_first) * 8) + rest);
         }
     }
     // Programmatic dependent launch: the weight copies above do not depend on the previous kernel in the
@@ -316,11 +348,17 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     if (is_producer) {
         // ------------------------------------------------------------------ producer: refill freed stages
         if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 1;   // chunk c >= S reuses stage s after the consumers' (c / S)-th release of it
             for (int c = S; c < nchunks; ++c) {
-                if (!mbar_wait(empty_bar(c % S), ((c / S) & 1) ^ 1, abort_flag, a.status, (12 << 16) | c)) {
+                if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, a.status, (12 << 16) | c)) {
                     break;
                 }
-                issue_chunk(c);
+                issue_chunk(c, s);
+                if (++s == S) {
+                    s = 0;
+                    ph ^= 1;
+                }
             }
         }
         __syncwarp();
@@ -364,7 +402,10 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                     v += __shfl_xor_sync(0xffffffffu, v, off);
                 }
                 if (live && sub == 0) {
-                    xsum[grp * GEMV_MAX_M + tok] = -8.f * v;
+                    // C operands of the group's first MMA: rows g carry 2^-24 per nibble unit, rows g+8 2^-20
+                    float* zc = xsum + (grp * 4 + (tok >> 1)) * 4 + (tok & 1);
+                    zc[0] = -8.f * v * 5.9604644775390625e-08f;
+                    zc[2] = -8.f * v * 9.5367431640625e-07f;
                 }
             }
         }
@@ -384,30 +425,47 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     const bool warp_active = !is_producer && rbw0 < nrbv;
     const int nvalid = warp_active ? min(RB_PER_WARP, nrbv - rbw0) : 0;
     if (warp_active && ok) {
-        const int ng = a.k / GROUP;
-        const size_t grp0 = (size_t)kb0 * GROUPS_PER_KB / KB_PER_GROUP;
-        const uint32_t* sp[RB_PER_WARP];
+        // scale pairs of rows (g, g+8), one 32-bit word per group at a stride of 8 words: from the staged copy
+        // in shared memory, else straight from global memory
+        const uint32_t* scp[RB_PER_WARP];
 #pragma unroll
         for (int r = 0; r < RB_PER_WARP; ++r) {
-            const int rbg = rb_w0 + rbw0 + (r < nvalid ? r : 0);
-            sp[r] = sg.st + ((size_t)rbg * ng + grp0) * 8 + g;
+            const int rr = r < nvalid ? r : 0;
+            if (p.sc_staged) {
+                scp[r] = reinterpret_cast<const uint32_t*>(smem + p.off_sc) + (size_t)(rbw0 + rr) * ngl * 8 + g;
+            } else {
+                const int ng = a.k / GROUP;
+                const size_t grp0 = (size_t)kb0 * GROUPS_PER_KB / KB_PER_GROUP;
+                scp[r] = sg.st + ((size_t)(rb_w0 + rbw0 + rr) * ng + grp0) * 8 + g;
+            }
         }
         // B fragment source: token g (the zero row when g >= m), this lane's 8 k of each half k-block
         const int xrow_i = g < m_loc ? g : m_loc;
         const unsigned char* xp = smem + (size_t)(xrow_i * p.x_stride + 8 * t) * 2;
-        const unsigned char* zp = smem + p.off_xsum + (2 * t) * 4;
+        const unsigned char* zp = smem + p.off_xsum + t * 16;
         const unsigned char* wbase = smem + p.off_ring + rbw0 * (TILE_WORDS * 4) + lane * 16;
 
-        // independent MMA chains per row block: a warp with two row blocks already has two
-        constexpr int CH = RB_PER_WARP >= 2 ? 1 : 2;
-        float acc[RB_PER_WARP][CH][4];
+        float acc[RB_PER_WARP][4];
         uint32_t sc[RB_PER_WARP];
 #pragma unroll
         for (int r = 0; r < RB_PER_WARP; ++r) {
-            sc[r] = __ldg(sp[r]);
+            sc[r] = *scp[r];
         }
         int gl = 0;
 
+        // one k-block of this warp's row blocks and the matching x fragments, in registers
+        struct KbRegs {
+            uint4 w[RB_PER_WARP];
+            uint4 x0, x1;
+        };
+        auto load_kb = [&](KbRegs& R, const unsigned char* wa, const unsigned char* xa) {
+#pragma unroll
+            for (int r = 0; r < RB_PER_WARP; ++r) {
+                R.w[r] = *reinterpret_cast<const uint4*>(wa + r * (TILE_WORDS * 4));
+            }
+            R.x0 = *reinterpret_cast<const uint4*>(xa);
+            R.x1 = *reinterpret_cast<const uint4*>(xa + 64);
+        };
         auto expand = [&](uint32_t w, uint32_t (&fr)[4]) {
             if (SUBN) {
                 nibbles_as_subnormals(w, fr);
@@ -415,112 +473,116 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                 dequant_word(w, fr);
             }
         };
+        // end of a scale group: tot += acc * scale (still in nibble units: the powers of two come at the end)
         auto finish_group = [&]() {
-            float2 z = make_float2(0.f, 0.f);
-            if (SUBN) {
-                z = *reinterpret_cast<const float2*>(zp);
-                zp += GEMV_MAX_M * 4;
-            }
             ++gl;
 #pragma unroll
             for (int r = 0; r < RB_PER_WARP; ++r) {
                 const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&sc[r]));
                 if (gl < ngl) {
-                    sc[r] = __ldg(sp[r] + (size_t)gl * 8);  // prefetch the next group's scales
+                    sc[r] = scp[r][gl * 8];  // the next group's scales
                 }
-                const float c0 = CH == 2 ? acc[r][0][0] + acc[r][CH - 1][0] : acc[r][0][0];
-                const float c1 = CH == 2 ? acc[r][0][1] + acc[r][CH - 1][1] : acc[r][0][1];
-                const float c2 = CH == 2 ? acc[r][0][2] + acc[r][CH - 1][2] : acc[r][0][2];
-                const float c3 = CH == 2 ? acc[r][0][3] + acc[r][CH - 1][3] : acc[r][0][3];
-                if (SUBN) {
-                    tot[r][0] = fmaf(fmaf(c0, 16777216.f, z.x), sf.x, tot[r][0]);
-                    tot[r][1] = fmaf(fmaf(c1, 16777216.f, z.y), sf.x, tot[r][1]);
-                    tot[r][2] = fmaf(fmaf(c2, 1048576.f, z.x), sf.y, tot[r][2]);
-                    tot[r][3] = fmaf(fmaf(c3, 1048576.f, z.y), sf.y, tot[r][3]);
-                } else {
-                    tot[r][0] = fmaf(c0, sf.x, tot[r][0]);
-                    tot[r][1] = fmaf(c1, sf.x, tot[r][1]);
-                    tot[r][2] = fmaf(c2, sf.y, tot[r][2]);
-                    tot[r][3] = fmaf(c3, sf.y, tot[r][3]);
-                }
+                tot[r][0] = fmaf(acc[r][0], sf.x, tot[r][0]);
+                tot[r][1] = fmaf(acc[r][1], sf.x, tot[r][1]);
+                tot[r][2] = fmaf(acc[r][2], sf.y, tot[r][2]);
+                tot[r][3] = fmaf(acc[r][3], sf.y, tot[r][3]);
             }
         };
-        // half a k-block (32 k = two MMAs) of both row blocks; `first` starts the chains on zero
-        auto half_kblock = [&](const uint4 (&w)[RB_PER_WARP], int hsel, const uint4& x, bool first) {
+        // half a k-block (32 k = two MMAs) of every row block; `init` opens a scale group: the chain starts from
+        // the group's zero-point term, -8 * sum(x), pre-scaled to the nibble units of the accumulator
+        auto half_kblock = [&](const KbRegs& R, int hsel, bool init) {
+            const uint4& x = hsel ? R.x1 : R.x0;
+            float4 cz = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (init && SUBN) {
+                cz = *reinterpret_cast<const float4*>(zp);
+                zp += 64;
+            }
 #pragma unroll
             for (int r = 0; r < RB_PER_WARP; ++r) {
                 uint32_t fr[4];
-                expand(hsel ? w[r].z : w[r].x, fr);
-                if (first) {
-                    mma16816_z(acc[r][0], fr, x.x, x.y);
+                expand(hsel ? R.w[r].z : R.w[r].x, fr);
+                if (init) {
+                    mma16816_c(acc[r], fr, x.x, x.y, cz);
                 } else {
-                    mma16816(acc[r][0], fr, x.x, x.y);
+                    mma16816(acc[r], fr, x.x, x.y);
                 }
-                expand(hsel ? w[r].w : w[r].y, fr);
-                if (first && CH == 2) {
-                    mma16816_z(acc[r][CH - 1], fr, x.z, x.w);
-                } else {
-                    mma16816(acc[r][CH - 1], fr, x.z, x.w);
-                }
+                expand(hsel ? R.w[r].w : R.w[r].y, fr);
+                mma16816(acc[r], fr, x.z, x.w);
             }
         };
         // one k-block; `first`/`last`: it opens / closes a scale group (g128); g32 groups are half k-blocks
-        auto kblock = [&](const unsigned char* wa, const unsigned char* xa, bool first, bool last) {
-            // ordinary shared-memory loads (ordered only against the barrier waits): the compiler overlaps k-blocks
-            uint4 w[RB_PER_WARP];
-#pragma unroll
-            for (int r = 0; r < RB_PER_WARP; ++r) {
-                w[r] = *reinterpret_cast<const uint4*>(wa + r * (TILE_WORDS * 4));
-            }
-            const uint4 x0 = *reinterpret_cast<const uint4*>(xa);
-            const uint4 x1 = *reinterpret_cast<const uint4*>(xa + 64);
-            half_kblock(w, 0, x0, first || GROUP < TILE_K);
+        auto compute_kb = [&](const KbRegs& R, bool first, bool last) {
+            half_kblock(R, 0, first || GROUP < TILE_K);
             if (GROUP < TILE_K) {
                 finish_group();
             }
-            half_kblock(w, 1, x1, GROUP < TILE_K);
+            half_kblock(R, 1, GROUP < TILE_K);
             if (GROUP < TILE_K || last) {
                 finish_group();
             }
         };
 
-        for (int c = 0; c < nchunks; ++c) {
-            const int s = c % S;
-            if (stamp && threadIdx.x == 0 && c < 1000) {
-                a.dbg[16 + 2 * c] = clock64();
-            }
-            ok = mbar_wait(full_bar(s), (c / S) & 1, abort_flag, a.status, (11 << 16) | c);
-            if (!ok) {
-                break;
-            }
-            if (stamp && threadIdx.x == 0 && c < 1000) {
-                a.dbg[17 + 2 * c] = clock64();
-            }
-            const unsigned char* wa = wbase + s * STAGE_BYTES;
-            // group boundaries fall on even k-blocks: splits are whole groups
-            const int kbs = min(CK, nloc - c * CK);
-#pragma unroll
-            for (int kbi = 0; kbi < CK; ++kbi) {
-                if (kbi < kbs) {
-                    kblock(wa + kbi * KB_BYTES, xp + kbi * 128, kbi % KB_PER_GROUP == 0,
-                           kbi % KB_PER_GROUP == KB_PER_GROUP - 1);
+        // Software pipeline over k-blocks: the registers of the next k-block are loaded before the MMAs of the
+        // current one, and a stage goes back to the producer as soon as both of its k-blocks are in registers.
+        // Splits are whole groups, so a g128 chunk (two k-blocks) is exactly one group.
+        static_assert(CK == 2, "the pipeline below is written for two k-blocks per stage");
+        int s = 0;
+        uint32_t ph = 0;
+        KbRegs A, B;
+        ok = mbar_wait(full_bar(0), 0, abort_flag, a.status, (11 << 16));
+        if (ok) {
+            load_kb(A, wbase, xp);
+            for (int c = 0; c < nchunks; ++c) {
+                const bool has_b = c * CK + 1 < nloc;   // false only for a ragged last chunk (g32)
+                if (has_b) {
+                    load_kb(B, wbase + s * STAGE_BYTES + KB_BYTES, xp + 128);
+                }
+                compute_kb(A, true, false);
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(empty_bar(s));
+                }
+                if (++s == S) {
+                    s = 0;
+                    ph ^= 1;
+                }
+                xp += CK * 128;
+                if (c + 1 < nchunks) {
+                    ok = mbar_wait(full_bar(s), ph, abort_flag, a.status, (11 << 16) | (c + 1));
+                    if (!ok) {
+                        break;
+                    }
+                    load_kb(A, wbase + s * STAGE_BYTES, xp);
+                }
+                if (has_b) {
+                    compute_kb(B, false, true);
                 }
             }
-            xp += CK * 128;
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(empty_bar(s));
+        }
+        if (SUBN) {
+#pragma unroll
+            for (int r = 0; r < RB_PER_WARP; ++r) {
+                tot[r][0] *= 16777216.f;
+                tot[r][1] *= 16777216.f;
+                tot[r][2] *= 1048576.f;
+                tot[r][3] *= 1048576.f;
             }
         }
     } else if (!is_producer && ok) {
         // a consumer warp without rows still releases every stage
+        int s = 0;
+        uint32_t ph = 0;
         for (int c = 0; c < nchunks; ++c) {
-            if (!mbar_wait(full_bar(c % S), (c / S) & 1, abort_flag, a.status, (13 << 16) | c)) {
+            if (!mbar_wait(full_bar(s), ph, abort_flag, a.status, (13 << 16) | c)) {
                 break;
             }
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(empty_bar(c % S));
+                mbar_arrive(empty_bar(s));
+            }
+            if (++s == S) {
+                s = 0;
+                ph ^= 1;
             }
         }
     }
@@ -692,8 +754,6 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         tp_exchange(a, sg, rb_cta0, nrows, s_seq, abort_flag);
     }
 }
-
-constexpr int GEMV_SMEM_LIMIT = 112 * 1024;
 
 }  // namespace
 
