@@ -61,8 +61,10 @@ W4A16_API int w4a16_sync(w4a16_dec* dec);
  * status word instead of hanging; the reference's only guard is its host watchdog
  * (crates/diag/src/watchdog.rs:46-90). w4a16_sync() includes this check. */
 W4A16_API int w4a16_kernel_status(w4a16_dec* dec);
-/* Diagnostic: after set_tuning("debug_timeline", 1), the first CTA of every kernel stamps the SM
- * cycle counter at its pipeline events into a device buffer; this copies up to max_slots entries out.
+/* Diagnostic: after set_tuning("debug_timeline", 1), every CTA of a decode GEMV stamps the global
+ * nanosecond timer at its pipeline events (entry, previous kernel complete, x staged, main loop start,
+ * main loop end, exit; then its SM id and chunk count) into a device buffer laid out
+ * [launch number mod 64][CTA < 384][8]; this copies up to max_slots entries out.
  * Plays the role of the reference's per-launch event profiler
  * (crates/backend-gpu/src/rawcuda/ctx/prof.rs:56-131) at a finer grain. */
 W4A16_API int w4a16_debug_timeline(w4a16_dec* dec, long long* out, int max_slots);

@@ -185,7 +185,7 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
     a.subnormal = tune_gemv_subnormal;
     a.pdl = tune_pdl;
     a.dbg = dbg_buf;
-    a.dbg_seq = (int)(launches % 400);
+    a.dbg_seq = (int)(launches % DBG_LAUNCHES);
     a.ring_stages = tune_gemv_stages;
     a.cons_warps = tune_gemv_warps;
     a.status = gemm_status;

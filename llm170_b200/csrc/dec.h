@@ -7,7 +7,7 @@
 
 namespace w4 {
 
-constexpr int DBG_SLOTS = 8192;
+constexpr int DBG_SLOTS = DBG_LAUNCHES * DBG_CTAS * 8;   // 8 stamps per CTA and launch
 
 struct Lin {
     uint32_t* qt = nullptr;  // T64 tiles (layout.cuh)

@@ -19,6 +19,7 @@
 // The kernel is HBM-bound.
 #include <cuda_fp16.h>
 
+#include "gemv_common.cuh"
 #include "internal.h"
 #include "ptx.cuh"
 
@@ -26,61 +27,7 @@ namespace w4 {
 
 namespace {
 
-constexpr int CTA_RB = 16;                        // 16 row blocks = 256 rows per CTA
-constexpr int ROWS_PER_CTA = CTA_RB * TILE_ROWS;
-constexpr int CK = 2;                             // k-blocks per ring stage
-constexpr int KB_BYTES = CTA_RB * TILE_WORDS * 4; // 8 KB: one k-block of the CTA's rows
-constexpr int STAGE_BYTES = CK * KB_BYTES;        // 16 KB
 constexpr int MAX_STAGES = 8;
-
-__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-// first MMA of a group: accumulates onto zero
-__device__ __forceinline__ void mma16816_z(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%10,%10,%10,%10};"
-        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
-}
-
-// first MMA of a group when the accumulator starts from given values (the zero-point term of the group)
-__device__ __forceinline__ void mma16816_c(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1,
-                                           const float4& c) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%10,%11,%12,%13};"
-        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c.x), "f"(c.y), "f"(c.z), "f"(c.w));
-}
-
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
-    float v;
-    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-    return v;
-}
-
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, unsigned cta_rank) {
-    uint32_t ra;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(cta_rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
-    return v;
-}
 
 // K range of split `s` in units of max(group, 64) input channels; ragged splits allowed.
 __device__ __host__ __forceinline__ void split_range(int k, int group, int ksplit, int s, int* kb0, int* kb1) {
@@ -144,64 +91,6 @@ __host__ SmemPlan make_plan(int k, int group, int m, int ksplit, int stages) {
     return p;
 }
 
-// Fused all-reduce of a row-parallel GEMV: the CTA that holds the local sums of rows [row0, row0+nrows) has
-// just written them (f32) to this rank's parity buffer.  It tells every peer (one flag per rank and row
-// block, written with release.sys into the PEER's flag array), waits -- bounded -- until every peer's flag for
-// this row block has reached this launch's number, then adds the peers' partial rows in rank order with
-// plain peer loads over NVLink and writes the final output.  No multicast, no second kernel, no NCCL call.
-// Parity buffers: a peer can be at most one launch ahead, and then writes the other buffer.
-__device__ __forceinline__ void tp_exchange(const GemvArgs& a, const GemvSeg& sg, int rb_cta0, int nrows, unsigned seq,
-                                            volatile int* abort_flag) {
-    const TpComm& tp = a.tp;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        for (int p = 0; p < tp.world; ++p) {
-            if (p != tp.rank) {
-                st_release_sys(tp.flags[p] + tp.rank * TP_MAX_CTAS + blockIdx.x, seq);
-            }
-        }
-    }
-    if ((int)threadIdx.x < tp.world && (int)threadIdx.x != tp.rank) {
-        const unsigned* f = tp.flags[tp.rank] + threadIdx.x * TP_MAX_CTAS + blockIdx.x;
-        const long long t0 = clock64();
-        while ((int)(ld_acquire_sys(f) - seq) < 0) {
-            if (*abort_flag || clock64() - t0 > (1ll << 31)) {
-                *abort_flag = 1;
-                atomicCAS(a.status, 0, (20 << 16) | (int)threadIdx.x);   // peer never arrived
-                break;
-            }
-        }
-    }
-    __syncthreads();
-    if (!*abort_flag) {
-        const size_t par = (size_t)(seq & 1u) * tp.area_floats;
-        const int row0 = rb_cta0 * TILE_ROWS;
-        for (int i = threadIdx.x; i < nrows * a.m; i += blockDim.x) {
-            const int lr = i % nrows, tok = i / nrows;
-            const size_t off = par + (size_t)(row0 + lr) * GEMV_MAX_M + tok;
-            float v = 0.f;
-            for (int p = 0; p < tp.world; ++p) {
-                v += ld_relaxed_sys_f32(tp.buf[p] + off);
-            }
-            if (a.out_f16) {
-                reinterpret_cast<__half*>(sg.out)[(size_t)tok * sg.n + row0 + lr] = __float2half_rn(v);
-            } else {
-                reinterpret_cast<float*>(sg.out)[(size_t)tok * sg.n + row0 + lr] = v;
-            }
-        }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        // the last row block of this launch to finish advances the launch number
-        if (atomicAdd(tp.done, 1u) == gridDim.x - 1) {
-            *tp.done = 0;
-            *tp.seq = seq;
-            __threadfence();
-        }
-    }
-}
-
 // CONS_WARPS consumer warps (8 or 16) own 16/CONS_WARPS row blocks each; warp CONS_WARPS is the producer.
 template <int GROUP, bool SUBN, int CONS_WARPS>
 __global__ void __launch_bounds__((CONS_WARPS + 1) * 32)
@@ -261,17 +150,26 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     auto full_bar = [&](int s) { return xbar + 8u + 8u * s; };
     auto empty_bar = [&](int s) { return xbar + 8u + 8u * (S + s); };
     volatile int* abort_flag = &s_abort;
-    const bool stamp = a.dbg != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+    // optional timeline: 8 wall-clock stamps per CTA and launch (diagnostic; a.dbg is null in normal runs)
+    const int dbg_cta = (int)(blockIdx.y * gridDim.x + blockIdx.x);
+    const bool stamp = a.dbg != nullptr && dbg_cta < DBG_CTAS;
+    long long* dbg = stamp ? a.dbg + ((size_t)a.dbg_seq * DBG_CTAS + dbg_cta) * 8 : nullptr;
+    auto stamp_now = [&](int j) {
+        unsigned long long ns;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+        dbg[j] = (long long)ns;
+    };
 
     __shared__ unsigned s_seq;
     const bool tp_on = a.tp.world > 1;
     if (threadIdx.x == 0) {
         s_seq = tp_on ? *a.tp.seq + 1u : 0u;   // this launch's exchange number (advanced by the last CTA to finish)
         if (stamp) {
-            a.dbg[0] = clock64();
-            unsigned long long ns;
-            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
-            a.dbg[7000 + a.dbg_seq] = (long long)ns;   // kernel start (first CTA), wall-clock ns
+            stamp_now(0);   // CTA entry
+            unsigned smid;
+            asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+            dbg[6] = smid;
+            dbg[7] = nchunks;
         }
         s_abort = 0;
         mbar_init(xbar, 1);
@@ -341,7 +239,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
             bulk_load(sbase + tok * p.x_stride * 2, x_loc + (size_t)tok * a.k + (size_t)kb0 * TILE_K, halves * 2, xbar);
         }
         if (stamp) {
-            a.dbg[1] = clock64();
+            stamp_now(1);   // the previous kernel of the stream is complete; x requested
         }
     }
 
@@ -367,7 +265,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     if (!is_producer) {
         ok = mbar_wait(xbar, 0, abort_flag, a.status, (10 << 16));
         if (stamp && threadIdx.x == 0) {
-            a.dbg[2] = clock64();
+            stamp_now(2);   // x in shared memory
         }
         if (SUBN && ok) {
             // xsum[grp][tok] = -8 * sum_{k in grp} x[tok][k] for tok < m (entries of tokens >= m stay zero):
@@ -412,7 +310,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         // consumers only: the producer warp is busy refilling the ring
         asm volatile("bar.sync 1, %0;" ::"n"(CONS_WARPS * 32) : "memory");
         if (stamp && threadIdx.x == 0) {
-            a.dbg[3] = clock64();
+            stamp_now(3);   // main loop starts
         }
     }
     // ---------------------------------------------------------------------- consumers: stream and accumulate
@@ -587,13 +485,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         }
     }
     if (stamp && threadIdx.x == 0) {
-        a.dbg[4] = clock64();
-        a.dbg[5] = nchunks;
-    }
-    if (a.dbg != nullptr && threadIdx.x == 0) {
-        unsigned long long ns;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
-        atomicMax(reinterpret_cast<unsigned long long*>(a.dbg) + 7400 + a.dbg_seq, ns);  // last CTA's main-loop end
+        stamp_now(4);   // main loop done (warp 0)
     }
 
     // the next kernel of the stream may start its weight stream now (it waits for our completion
@@ -635,7 +527,10 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
             }
         }
         if (tp_on) {
-            tp_exchange(a, sg, rb_cta0, nrbv * TILE_ROWS, s_seq, abort_flag);
+            tp_exchange(a, sg, rb_cta0, nrbv * TILE_ROWS, s_seq, abort_flag, (int)blockIdx.x, gridDim.x);
+        }
+        if (stamp && threadIdx.x == 0) {
+            stamp_now(5);
         }
         return;
     }
@@ -686,7 +581,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         }
         cluster_sync_all();  // peers may still be reading this CTA's buffer
         if (stamp && threadIdx.x == 0) {
-            a.dbg[6] = clock64();
+            stamp_now(5);   // reduced and stored
         }
         return;
     }
@@ -751,7 +646,10 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         a.counters[blockIdx.x] = 0;  // ready for the next launch (graph replay needs no memset)
     }
     if (tp_on) {
-        tp_exchange(a, sg, rb_cta0, nrows, s_seq, abort_flag);
+        tp_exchange(a, sg, rb_cta0, nrows, s_seq, abort_flag, (int)blockIdx.x, gridDim.x);
+    }
+    if (stamp && threadIdx.x == 0) {
+        stamp_now(5);
     }
 }
 

@@ -36,6 +36,9 @@ struct TpComm {
     unsigned* done;                   // local: CTAs that finished the current launch's exchange
 };
 
+constexpr int DBG_LAUNCHES = 64;   // launches kept by the diagnostic timeline (slot = launch number mod 64)
+constexpr int DBG_CTAS = 384;      // CTAs stamped per launch
+
 struct GemvSeg {
     const uint4* qt;
     const uint32_t* st;  // scale pairs, one u32 = (row j, row j+8)
@@ -59,8 +62,8 @@ struct GemvArgs {
     int cluster;        // 1: the K splits of a row block form a thread-block cluster and reduce through DSMEM
     int cons_warps;     // consumer warps per CTA: 8 (two row blocks each) or 16 (one each)
     int ring_stages;    // 2 KB chunks in flight per warp (2..4)
-    long long* dbg;     // optional timeline buffer (diagnostic), CTA (0,0) only
-    int dbg_seq;        // launch sequence number (slot for the per-launch start/end stamps)
+    long long* dbg;     // optional timeline buffer (diagnostic): [DBG_LAUNCHES][DBG_CTAS][8] wall-clock stamps
+    int dbg_seq;        // launch slot in that buffer
     int pdl;            // 1: launch with programmatic stream serialization (overlaps the previous kernel's tail)
     // grouped (MoE decode) mode: blockIdx.x / ctas_per_seg indexes a device table of <=8-row segments; the
     // single segment seg[0] then describes the stacked expert matrix (n = rows per expert)
