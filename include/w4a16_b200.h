@@ -63,8 +63,8 @@ W4A16_API int w4a16_sync(w4a16_dec* dec);
 W4A16_API int w4a16_kernel_status(w4a16_dec* dec);
 /* Diagnostic: after set_tuning("debug_timeline", 1), every CTA of a decode GEMV stamps the global
  * nanosecond timer at its pipeline events (entry, previous kernel complete, x staged, main loop start,
- * main loop end, exit; then its SM id and chunk count) into a device buffer laid out
- * [launch number mod 64][CTA < 384][8]; this copies up to max_slots entries out.
+ * main loop end, exit; then its SM id, unit count, and the steps of the cross-CTA reduce) into a device buffer
+ * laid out [launch number mod 64][CTA < 384][16]; this copies up to max_slots entries out.
  * Plays the role of the reference's per-launch event profiler
  * (crates/backend-gpu/src/rawcuda/ctx/prof.rs:56-131) at a finer grain. */
 W4A16_API int w4a16_debug_timeline(w4a16_dec* dec, long long* out, int max_slots);
@@ -72,7 +72,11 @@ W4A16_API int w4a16_debug_timeline(w4a16_dec* dec, long long* out, int max_slots
  * HOST_LAUNCH_CALLS (crates/backend-gpu/src/rawcuda/ctx/mod.rs:10-11,311-315). */
 W4A16_API unsigned long long w4a16_launch_count(w4a16_dec* dec);
 /* Kernel-selection knobs, the analogue of the reference's LLM170_* environment flags
- * (crates/diag/src/flag.rs:3-27). Keys: "gemv_ksplit" (0 = automatic),
+ * (crates/diag/src/flag.rs:3-27). Keys: "gemv_persistent" (which form of the decode GEMV runs: 1 = default,
+ * two persistent CTAs per SM with equal ranges of work for up to 4 tokens and the (row block, K split) grid
+ * above that; 2 = always persistent; 0 = never), "gemv_sk_stages" (2..6) and "gemv_sk_prefetch" (0..6): ring
+ * stages of the persistent form and how many of them are requested before the previous kernel of the stream is
+ * complete; the remaining gemv_* keys tune the (row block, K split) form: "gemv_ksplit" (0 = automatic),
  * "gemv_stages" (16 KB weight stages in flight per CTA, 2..8), "gemv_warps" (consumer warps per CTA, 8 or 16), "gemv_cluster" (1 = default: 2..8 K splits of a row
  * block run as a thread-block cluster and reduce through distributed shared memory),
  * "gemv_subnormal" (1 = default arithmetic, 0 = exact nibble-8 operands), "gemm_mt" (128-token blocks per prefill GEMM tile: 0 = automatic, 1, 2), "debug_timeline" (0/1, see w4a16_debug_timeline), "pdl" (1 = default: kernels are

@@ -164,7 +164,43 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
     a.m = t;
     a.out_f16 = out_kind == W4A16_OUT_F16;
     a.x = (const uint16_t*)x;
-    const int grid_x = gemv_plan_ctas(a);
+    const int grid_x = gemv_plan_ctas(a);   // 256-row blocks over all segments
+    if (((uintptr_t)x & 15) != 0) {
+        return fail("w4a16 gemv: x must be 16-byte aligned");
+    }
+    const SkPlan sp = sk_make_plan(a.k, a.group, t, grid_x, sm_count, tune_gemv_sk_stages, tune_gemv_sk_prefetch);
+    // measured on B200: the persistent form wins up to 4 tokens; at 5..8 its single-CTA sum of a row block costs
+    // more than the cluster reduce of the (row block, K split) form
+    if (tune_gemv_persistent && sp.ctas > 0 && (t <= 4 || tune_gemv_persistent > 1)) {
+        a.ksplit = 1;
+        a.subnormal = tune_gemv_subnormal;
+        a.pdl = tune_pdl;
+        a.dbg = dbg_buf;
+        a.dbg_seq = (int)(launches % DBG_LAUNCHES);
+        a.status = gemm_status;
+        a.tp = TpComm{};
+        if (allreduce) {
+            if (tp.world < 2 || tp_peer[(tp.rank + 1) % tp.world] == nullptr) {
+                return fail("w4a16 allreduce gemv: call w4a16_tp_create and w4a16_tp_connect first");
+            }
+            if (nseg != 1 || ls[0]->n > tp_max_rows || grid_x > TP_MAX_CTAS) {
+                return fail("w4a16 allreduce gemv: n=%d exceeds the exchange buffer (%d rows)", ls[0]->n, tp_max_rows);
+            }
+            a.tp = tp;
+            a.pdl = 0;  // the exchange buffers are reused by the next launch: no early start
+        }
+        if (int rc = ensure_scratch(sk_part_floats(sp), grid_x, st)) {
+            return rc;
+        }
+        a.part = part;
+        a.counters = counters;
+        cudaError_t e = launch_gemv_sk(a, sp, st);
+        if (e != cudaSuccess) {
+            return cuda_fail("launch gemv", e);
+        }
+        launches++;
+        return 0;
+    }
     int ks = tune_gemv_ksplit > 0 ? tune_gemv_ksplit
                                   : gemv_pick_ksplit(grid_x, a.k, a.group, t, sm_count,
                                                      (tune_gemv_cluster && !allreduce) ? 8 : 16, tune_gemv_stages);
@@ -177,9 +213,6 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
     }
     if (gemv_smem_bytes(a.k, a.group, t, ks, tune_gemv_stages) > 112 * 1024) {
         return fail("w4a16 gemv: k=%d too large for t=%d", a.k, t);
-    }
-    if (((uintptr_t)x & 15) != 0) {
-        return fail("w4a16 gemv: x must be 16-byte aligned");
     }
     a.ksplit = ks;
     a.subnormal = tune_gemv_subnormal;
@@ -335,6 +368,9 @@ int w4a16_dec_new(int device, w4a16_dec** out) {
     }
     if (e == cudaSuccess) {
         e = w4::gemv_init_device();
+        if (e == cudaSuccess) {
+            e = w4::gemv_sk_init_device();
+        }
     }
     if (e == cudaSuccess) {
         e = w4::gemm_init_device();
@@ -436,6 +472,10 @@ int w4a16_kernel_status(w4a16_dec* dec) {
     }
     if (st != 0) {
         cudaMemset(d.gemm_status, 0, sizeof(int));
+        // an abandoned launch may have left tickets taken
+        if (d.counters) {
+            cudaMemset(d.counters, 0, d.counters_cap * sizeof(unsigned));
+        }
         return d.fail("w4a16: a bounded pipeline wait expired (role %d, step %d); results are invalid", st >> 16,
                       st & 0xFFFF);
     }
@@ -462,6 +502,24 @@ int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
     }
     if (!strcmp(key, "gemv_cluster")) {
         d.tune_gemv_cluster = value != 0;
+        return 0;
+    }
+    if (!strcmp(key, "gemv_persistent")) {
+        d.tune_gemv_persistent = value;   // 0 = never, 1 = up to 4 tokens (default), 2 = always
+        return 0;
+    }
+    if (!strcmp(key, "gemv_sk_prefetch")) {
+        if (value < 0 || value > 6) {
+            return d.fail("w4a16 tuning: gemv_sk_prefetch must be 0..6");
+        }
+        d.tune_gemv_sk_prefetch = value;
+        return 0;
+    }
+    if (!strcmp(key, "gemv_sk_stages")) {
+        if (value < 2 || value > 6) {
+            return d.fail("w4a16 tuning: gemv_sk_stages must be 2..6");
+        }
+        d.tune_gemv_sk_stages = value;
         return 0;
     }
     if (!strcmp(key, "gemv_warps")) {

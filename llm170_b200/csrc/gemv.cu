@@ -153,7 +153,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     // optional timeline: 8 wall-clock stamps per CTA and launch (diagnostic; a.dbg is null in normal runs)
     const int dbg_cta = (int)(blockIdx.y * gridDim.x + blockIdx.x);
     const bool stamp = a.dbg != nullptr && dbg_cta < DBG_CTAS;
-    long long* dbg = stamp ? a.dbg + ((size_t)a.dbg_seq * DBG_CTAS + dbg_cta) * 8 : nullptr;
+    long long* dbg = stamp ? a.dbg + ((size_t)a.dbg_seq * DBG_CTAS + dbg_cta) * DBG_STAMPS : nullptr;
     auto stamp_now = [&](int j) {
         unsigned long long ns;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));

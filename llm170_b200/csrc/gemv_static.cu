@@ -85,7 +85,36 @@ extern "C" int w4a16_sk_single_static(w4a16_dec* dec, const char* name, const vo
     a.m = t;
     a.out_f16 = out_kind == W4A16_OUT_F16;
     a.x = (const uint16_t*)x16_dev;
-    const int grid_x = gemv_plan_ctas(a);
+    const int grid_x = gemv_plan_ctas(a);   // 256-row blocks
+    cudaStream_t st = stream ? (cudaStream_t)stream : d.stream;
+    const SkPlan sp = sk_make_plan(a.k, a.group, t, grid_x, d.sm_count, d.tune_gemv_sk_stages, d.tune_gemv_sk_prefetch);
+    if (d.tune_gemv_persistent && sp.ctas > 0 && (t <= 4 || d.tune_gemv_persistent > 1)) {
+        // the same kernel and plan as w4a16_sk_single_dev, so the two give identical results
+        const size_t need = sk_part_floats(sp) * sizeof(float);
+        if (need > STATIC_PART_BYTES || (size_t)grid_x > STATIC_TICKETS) {
+            return d.fail("w4a16 sk_single_static: %s needs %zu bytes of partial-sum scratch and %d tickets; the "
+                          "built-in array holds %zu bytes and %zu tickets (use w4a16_sk_single_dev)",
+                          name, need, grid_x, STATIC_PART_BYTES, STATIC_TICKETS);
+        }
+        a.ksplit = 1;
+        a.subnormal = d.tune_gemv_subnormal;
+        a.pdl = 0;  // ordinary launch: the shared array must not be touched while an earlier kernel still runs
+        a.tp = TpComm{};
+        a.status = d.gemm_status;
+        a.dbg = nullptr;
+        a.counters = reinterpret_cast<unsigned*>(base);
+        a.part = reinterpret_cast<float*>(base + STATIC_TICKETS * sizeof(unsigned));
+        // tickets must start at zero; the previous call may have been abandoned half-way
+        e = cudaMemsetAsync(a.counters, 0, (size_t)grid_x * sizeof(unsigned), st);
+        if (e == cudaSuccess) {
+            e = launch_gemv_sk(a, sp, st);
+        }
+        if (e != cudaSuccess) {
+            return d.cuda_fail("launch gemv (static scratch)", e);
+        }
+        d.launches++;
+        return 0;
+    }
     int ks = d.tune_gemv_ksplit > 0
                  ? d.tune_gemv_ksplit
                  : gemv_pick_ksplit(grid_x, a.k, a.group, t, d.sm_count, d.tune_gemv_cluster ? 8 : 16, d.tune_gemv_stages);
@@ -120,7 +149,6 @@ extern "C" int w4a16_sk_single_static(w4a16_dec* dec, const char* name, const vo
     a.dbg_seq = 0;
     a.counters = reinterpret_cast<unsigned*>(base);
     a.part = reinterpret_cast<float*>(base + STATIC_TICKETS * sizeof(unsigned));
-    cudaStream_t st = stream ? (cudaStream_t)stream : d.stream;
     // tickets must start at zero; the previous call may have been abandoned half-way
     e = cudaMemsetAsync(a.counters, 0, (size_t)grid_x * sizeof(unsigned), st);
     if (e == cudaSuccess) {

@@ -38,6 +38,7 @@ struct TpComm {
 
 constexpr int DBG_LAUNCHES = 64;   // launches kept by the diagnostic timeline (slot = launch number mod 64)
 constexpr int DBG_CTAS = 384;      // CTAs stamped per launch
+constexpr int DBG_STAMPS = 16;     // stamps per CTA and launch
 
 struct GemvSeg {
     const uint4* qt;
@@ -62,7 +63,7 @@ struct GemvArgs {
     int cluster;        // 1: the K splits of a row block form a thread-block cluster and reduce through DSMEM
     int cons_warps;     // consumer warps per CTA: 8 (two row blocks each) or 16 (one each)
     int ring_stages;    // 2 KB chunks in flight per warp (2..4)
-    long long* dbg;     // optional timeline buffer (diagnostic): [DBG_LAUNCHES][DBG_CTAS][8] wall-clock stamps
+    long long* dbg;     // optional timeline buffer (diagnostic): [DBG_LAUNCHES][DBG_CTAS][DBG_STAMPS] wall-clock stamps
     int dbg_seq;        // launch slot in that buffer
     int pdl;            // 1: launch with programmatic stream serialization (overlaps the previous kernel's tail)
     // grouped (MoE decode) mode: blockIdx.x / ctas_per_seg indexes a device table of <=8-row segments; the
@@ -89,6 +90,28 @@ size_t gemv_part_floats(int grid_x, int ksplit);
 cudaError_t launch_gemv(const GemvArgs& a, int grid_x, cudaStream_t st);
 // Raises the dynamic shared-memory limit of the GEMV kernels on the current device.
 cudaError_t gemv_init_device();
+
+// ---- gemv_sk.cu: the persistent (two CTAs per SM, equal unit ranges) form of the decode GEMV ------
+struct SkPlan {
+    int units_per_row;  // 128-channel units (two k-blocks; the last may hold one) along K
+    int rows;           // 256-row blocks over all segments
+    long long units;    // rows * units_per_row
+    int ctas;           // grid size; CTA p owns units [units*p/ctas, units*(p+1)/ctas)
+    int nu_max;         // most units one CTA owns
+    int x_stride;       // halves per staged token row (byte stride = 64 mod 128)
+    int x_rows;         // token rows staged (m, plus one all-zero row when m < 8)
+    int off_zc;         // f32 [local group][4 lane columns][4]: zero-point terms as MMA C operands
+    int off_sc;         // u32 [16 row blocks][local group][8]: the CTA's scale pairs
+    int off_ring;       // stages x 16 KB, 1024-byte aligned
+    int off_bars;       // xbar, full[stages], empty[stages], scbar
+    int stages;
+    int prefetch;       // stages requested before griddepcontrol.wait (the rest right after it)
+    int total;          // dynamic shared memory requested (at least 77 KB: never three CTAs on an SM)
+};
+SkPlan sk_make_plan(int k, int group, int m, int rows, int sm_count, int max_stages, int prefetch);
+size_t sk_part_floats(const SkPlan& p);   // scratch for parked partial sums; counters: one per row block
+cudaError_t launch_gemv_sk(const GemvArgs& a, const SkPlan& p, cudaStream_t st);
+cudaError_t gemv_sk_init_device();
 
 // ---- gemm_tc.cu ------------------------------------------------------------------------------
 // Raises the dynamic shared-memory limit of the tensor-core GEMM kernels on the current device.

@@ -74,7 +74,7 @@ class W4a16Dec:
     def sync(self):
         self._ck(self._L.w4a16_sync(self._h))
 
-    def debug_timeline(self, slots: int = 64 * 384 * 8) -> np.ndarray:
+    def debug_timeline(self, slots: int = 64 * 384 * 16) -> np.ndarray:
         out = np.zeros(slots, np.int64)
         self._ck(self._L.w4a16_debug_timeline(self._h, out.ctypes.data, slots))
         return out

@@ -33,21 +33,30 @@ def test_static_scratch_matches_regular_entry_twice():
             ref16 = dec.sk_single_dev("na", x, t=t, out_f16=True)
             assert torch.equal(dec.sk_single_static("na", x, t=t, out_f16=True), ref16)
         dec.kernel_status()
-        # a launch that would need more than the built-in 8 MiB is refused, nothing runs
-        n, k = 34816, 5120
+        # a launch that would need more than the built-in 8 MiB is refused, nothing runs: 8 tokens of a
+        # 17408-channel input leave room for 31 units per CTA, so this 34816 x 17408 linear takes 597 CTAs
+        # with two 8 KB parking slots each
+        n, k = 34816, 17408
         q, s = synth.make_linear_cuda(n, k, 128, seed=1, device=torch.device("cuda", 0))
         dec.upload_lin_g_dev("big", q, s, n, k, 128)
-        x = torch.randn((1, k), device="cuda").half()
-        out = torch.full((1, n), 7.0, device="cuda")
+        x = torch.randn((8, k), device="cuda").half()
+        out = torch.full((8, n), 7.0, device="cuda")
+        with pytest.raises(W4a16Error, match="scratch"):
+            dec.sk_single_static("big", x, out=out, t=8)
+        torch.cuda.synchronize()
+        assert bool((out == 7.0).all())
+        # one token fits (two CTAs per SM) and agrees
+        assert torch.equal(dec.sk_single_static("big", x[:1], t=1), dec.sk_single_dev("big", x[:1], t=1))
+        # the (row block, K split) form of the kernel has the same guard
+        dec.set_tuning("gemv_persistent", 0)
         dec.set_tuning("gemv_ksplit", 16)            # 16 splits x 136 row blocks x 8 KB = 17 MB
         try:
             with pytest.raises(W4a16Error, match="scratch"):
-                dec.sk_single_static("big", x, out=out, t=1)
+                dec.sk_single_static("big", x[:1], out=out[:1], t=1)
+            dec.set_tuning("gemv_ksplit", 0)
+            assert torch.equal(dec.sk_single_static("big", x[:1], t=1), dec.sk_single_dev("big", x[:1], t=1))
         finally:
             dec.set_tuning("gemv_ksplit", 0)
-        torch.cuda.synchronize()
-        assert bool((out == 7.0).all())
-        # with the automatic split it fits and agrees
-        assert torch.equal(dec.sk_single_static("big", x, t=1), dec.sk_single_dev("big", x, t=1))
+            dec.set_tuning("gemv_persistent", 1)
     finally:
         dec.close()
