@@ -523,7 +523,7 @@ def main():
                        "l2": f"inputs larger than L2 ({bytes_step / 1e9:.2f} GB of weights per step)",
                        "launch": "cuda graph replay" + (", all-reduce fused into the row-parallel GEMV (peer loads)" if world > 1 else ""),
                        "build_s": round(t_build, 1)},
-            "roofline": {"bound": "hbm", "kernel": "gemv_w4a16_kernel<128,true,8>", "achieved": ach,
+            "roofline": {"bound": "hbm", "kernel": "gemv_sk_kernel<128,true>", "achieved": ach,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                          "peak_kind": peak_kind, "frac_of_nominal_8TBps": ach / 8000.0,
                          "traffic": 43.37e6 if world == 1 else None,   # dram read+write per launch, ncu (profiles/gemv_decode_stack_launch_list.md)

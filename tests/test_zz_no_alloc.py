@@ -41,8 +41,12 @@ def test_static_scratch_matches_regular_entry_twice():
         dec.upload_lin_g_dev("big", q, s, n, k, 128)
         x = torch.randn((8, k), device="cuda").half()
         out = torch.full((8, n), 7.0, device="cuda")
-        with pytest.raises(W4a16Error, match="scratch"):
-            dec.sk_single_static("big", x, out=out, t=8)
+        dec.set_tuning("gemv_persistent", 2)         # the persistent form at every token count
+        try:
+            with pytest.raises(W4a16Error, match="scratch"):
+                dec.sk_single_static("big", x, out=out, t=8)
+        finally:
+            dec.set_tuning("gemv_persistent", 1)
         torch.cuda.synchronize()
         assert bool((out == 7.0).all())
         # one token fits (two CTAs per SM) and agrees
