@@ -413,6 +413,70 @@ def main():
                                "frac_measured_hbm": round(b / us / 1e3 / peaks["hbm_gbs"], 4)}
                 extras[f"M{m}"] = per
 
+    # ---- extras (N > 1, every rank takes part): per-shard decode launches and one prefill layer ---------
+    if world > 1 and not args.no_extras:
+        with torch.cuda.stream(st):
+            per = {}
+            for nm in LAYER_ORDER:
+                k, n, kind = shapes[nm]
+                def shape_pass():
+                    for li in range(L):
+                        if kind == "row":
+                            dec.sk_single_allreduce(f"l{li}.{nm}", xb[nm][:1], out=yb[nm][:1], t=1, out_f16=True)
+                        else:
+                            dec.sk_single_dev(f"l{li}.{nm}", xb[nm][:1], out=yb[nm][:1], t=1, out_f16=True)
+                shape_pass()
+                st.synchronize()
+                dist.barrier()
+                dec.capture_begin()
+                shape_pass()
+                gsh = dec.capture_end()
+                for _ in range(3):
+                    dec.graph_launch(gsh)
+                st.synchronize()
+                dist.barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 5
+                e0.record(st)
+                for _ in range(reps):
+                    dec.graph_launch(gsh)
+                e1.record(st)
+                e1.synchronize()
+                tus = torch.tensor([e0.elapsed_time(e1) * 1e3 / (reps * L)], device=device)
+                dist.all_reduce(tus, op=dist.ReduceOp.MAX)
+                dec.graph_destroy(gsh)
+                per[nm] = {"us": round(float(tus.item()), 3), "shard": [n, k], "kind": kind}
+            extras["tp_M1_per_launch"] = per
+            # prefill, M = 4096: column-parallel GEMMs need no exchange; the f16 outputs of the row-parallel
+            # ones are summed with NCCL (the in-kernel exchange serves decode-sized outputs only)
+            m = 4096
+            xg = {nm: (torch.randn((m, shapes[nm][0]), generator=g, device=device, dtype=torch.float32)
+                       / (shapes[nm][0] ** 0.5)).to(torch.float16) for nm in LAYER_ORDER}
+            yg = {nm: torch.empty((m, shapes[nm][1]), device=device, dtype=torch.float16) for nm in LAYER_ORDER}
+            nl = min(L, 4)
+            def prefill_layers():
+                for li in range(nl):
+                    for nm in LAYER_ORDER:
+                        dec.lin_forward(f"l{li}.{nm}", xg[nm], m, dst=yg[nm], out_f16=True)
+                        if shapes[nm][2] == "row":
+                            dist.all_reduce(yg[nm])
+            prefill_layers()
+            st.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(st)
+            for _ in range(2):
+                prefill_layers()
+            e1.record(st)
+            e1.synchronize()
+            tms = torch.tensor([e0.elapsed_time(e1) / (2 * nl)], device=device)
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+            fl = sum(synth.gemm_flops(synth.DENSE_27B[nm][1], synth.DENSE_27B[nm][0], m) for nm in LAYER_ORDER)
+            extras["tp_prefill_M4096"] = {"ms_per_layer": round(float(tms.item()), 4),
+                                          "TFLOPs_all_gpus": round(fl / float(tms.item()) / 1e9, 1),
+                                          "allreduce": "NCCL f16 sum on o_proj and down outputs"}
+        dec.kernel_status()
+
     # ---- extras: prefill GEMM sweep (tensor-core kernel), TFLOP/s per shape, rotating over 8 layers ----
     if world == 1 and not args.no_extras:
         pre = {}

@@ -716,7 +716,7 @@ int w4a16_sk_single_dev(w4a16_dec* dec, const char* name, const void* x16_dev, v
 }
 
 // ---- row-parallel tensor parallelism ----------------------------------------------------------------
-// exchange block layout: [flags world*TP_MAX_CTAS u32][seq u32][done u32][pad -> 4096 B][2 x max_rows x 8 f32]
+// exchange block layout: [seq u32][done u32][pad -> 4096 B][2 parities x world sources x 8 x max_rows f32, all ones]
 static const size_t TP_HEADER = 4096;
 
 int w4a16_tp_create(w4a16_dec* dec, int rank, int world, int max_rows, void* handle_out64) {
@@ -732,9 +732,13 @@ int w4a16_tp_create(w4a16_dec* dec, int rank, int world, int max_rows, void* han
         return d.fail("w4a16 tp_create: already created");
     }
     const size_t area = (size_t)max_rows * w4::GEMV_MAX_M;
-    const size_t bytes = TP_HEADER + 2 * area * sizeof(float);
+    if (max_rows % 4 != 0) {
+        return d.fail("w4a16 tp_create: max_rows must be a multiple of 4");
+    }
+    const size_t bytes = TP_HEADER + 2 * (size_t)world * area * sizeof(float);
     cudaError_t e = cudaMalloc(&d.tp_block, bytes);
-    if (e == cudaSuccess) e = cudaMemset(d.tp_block, 0, bytes);
+    if (e == cudaSuccess) e = cudaMemset(d.tp_block, 0, TP_HEADER);
+    if (e == cudaSuccess) e = cudaMemset((char*)d.tp_block + TP_HEADER, 0xff, bytes - TP_HEADER);   // the sentinel
     cudaIpcMemHandle_t h;
     if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, d.tp_block);
     if (e != cudaSuccess) {
@@ -746,6 +750,7 @@ int w4a16_tp_create(w4a16_dec* dec, int rank, int world, int max_rows, void* han
     d.tp.rank = rank;
     d.tp.world = world;
     d.tp.area_floats = (int)area;
+    d.tp.max_rows = max_rows;
     d.tp_max_rows = max_rows;
     d.tp_peer[rank] = d.tp_block;
     return 0;
@@ -768,12 +773,11 @@ int w4a16_tp_connect(w4a16_dec* dec, const void* handles_world_x64) {
         }
     }
     for (int p = 0; p < d.tp.world; ++p) {
-        d.tp.flags[p] = (unsigned*)d.tp_peer[p];
         d.tp.buf[p] = (float*)((char*)d.tp_peer[p] + TP_HEADER);
     }
     unsigned* local = (unsigned*)d.tp_block;
-    d.tp.seq = local + w4::TP_MAX_WORLD * w4::TP_MAX_CTAS;
-    d.tp.done = d.tp.seq + 1;
+    d.tp.seq = local;
+    d.tp.done = local + 1;
     return 0;
 }
 

@@ -510,9 +510,9 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                             tot[r][2 + j] *= rw;
                         }
                         if (tp_on) {
-                            float* o = a.tp.buf[a.tp.rank] + (size_t)(s_seq & 1u) * a.tp.area_floats;
-                            o[(size_t)row0 * GEMV_MAX_M + tok] = tot[r][j];
-                            o[(size_t)row1 * GEMV_MAX_M + tok] = tot[r][2 + j];
+                            float* o = tp_own_area(a.tp, s_seq);
+                            o[(size_t)tok * a.tp.max_rows + row0] = tot[r][j];
+                            o[(size_t)tok * a.tp.max_rows + row1] = tot[r][2 + j];
                         } else if (a.out_f16) {
                             __half* o = reinterpret_cast<__half*>(sg.out) + (size_t)tok * sg.n;
                             o[row0] = __float2half_rn(tot[r][j]);
@@ -527,7 +527,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
             }
         }
         if (tp_on) {
-            tp_exchange(a, sg, rb_cta0, nrbv * TILE_ROWS, s_seq, abort_flag, (int)blockIdx.x, gridDim.x);
+            tp_exchange(a, sg, rb_cta0, nrbv * TILE_ROWS, s_seq, abort_flag, gridDim.x);
         }
         if (stamp && threadIdx.x == 0) {
             stamp_now(5);
@@ -632,7 +632,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                         v *= a.row_w[row_base + tok];
                     }
                     if (tp_on) {
-                        a.tp.buf[a.tp.rank][(size_t)(s_seq & 1u) * a.tp.area_floats + (size_t)row * GEMV_MAX_M + tok] = v;
+                        tp_own_area(a.tp, s_seq)[(size_t)tok * a.tp.max_rows + row] = v;
                     } else if (a.out_f16) {
                         reinterpret_cast<__half*>(sg.out)[(size_t)tok * sg.n + row] = __float2half_rn(v);
                     } else {
@@ -646,7 +646,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         a.counters[blockIdx.x] = 0;  // ready for the next launch (graph replay needs no memset)
     }
     if (tp_on) {
-        tp_exchange(a, sg, rb_cta0, nrows, s_seq, abort_flag, (int)blockIdx.x, gridDim.x);
+        tp_exchange(a, sg, rb_cta0, nrows, s_seq, abort_flag, gridDim.x);
     }
     if (stamp && threadIdx.x == 0) {
         stamp_now(5);

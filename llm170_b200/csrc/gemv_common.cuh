@@ -62,48 +62,84 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t local_addr, unsigned cta_
     return v;
 }
 
-// Fused all-reduce of a row-parallel GEMV: the CTA that holds the local sums of rows [row0, row0+nrows) has
-// just written them (f32) to this rank's parity buffer.  It tells every peer (one flag per rank and row
-// block, written with release.sys into the PEER's flag array), waits -- bounded -- until every peer's flag for
-// this row block has reached this launch's number, then adds the peers' partial rows in rank order with
-// plain peer loads over NVLink and writes the final output.  No multicast, no second kernel, no NCCL call.
-// Parity buffers: a peer can be at most one launch ahead, and then writes the other buffer.
-// `flag_idx` numbers the row block within the launch (the same on every rank); the launch number advances when
-// `done_target` row blocks of this launch have been exchanged.
+// ---- fused all-reduce of a row-parallel GEMV --------------------------------------------------------------
+// Where this rank's own sums of a launch go: its own source slot of its own receive area.
+__device__ __forceinline__ float* tp_own_area(const TpComm& tp, unsigned seq) {
+    return tp.buf[tp.rank] + ((size_t)(seq & 1u) * tp.world + tp.rank) * tp.area_floats;
+}
+__device__ __forceinline__ void st_relaxed_sys_f32(float* p, float v) {
+    asm volatile("st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+
+// The CTA that holds the local sums of rows [row0, row0+nrows) has just written them (f32, [token][row]) to its
+// own area.  It PUSHES them into the same slot of every peer's receive area with plain peer stores over NVLink,
+// then polls its own receive area until the word of every peer has replaced the sentinel -- bounded -- adds the
+// ranks' values in rank order, writes the output and puts the sentinel back.  Every word says by itself whether
+// it has arrived, so the exchange needs no flag and, above all, no system-scope fence (measured here at 5 us
+// each with weight copies in flight).  No multicast, no second kernel, no NCCL call.  Two parities: a peer can
+// be at most one launch ahead, and then writes the other half.
+// The launch number advances when `done_target` row blocks of this launch have been exchanged.
 __device__ __forceinline__ void tp_exchange(const GemvArgs& a, const GemvSeg& sg, int rb_cta0, int nrows, unsigned seq,
-                                            volatile int* abort_flag, int flag_idx, unsigned done_target) {
+                                            volatile int* abort_flag, unsigned done_target, long long* dbg = nullptr) {
     const TpComm& tp = a.tp;
+    auto stamp = [&](int j) {
+        if (dbg != nullptr && threadIdx.x == 0) {
+            unsigned long long ns;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+            dbg[j] = (long long)ns;
+        }
+    };
     __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence_system();
+    stamp(12);   // local sums written
+    const int row0 = rb_cta0 * TILE_ROWS;
+    const size_t par_base = (size_t)(seq & 1u) * tp.world * tp.area_floats;
+    const float* own = tp_own_area(tp, seq);
+    for (int i = threadIdx.x; i < nrows * a.m; i += blockDim.x) {
+        const int tok = i / nrows, lr = i - tok * nrows;
+        const size_t off = (size_t)tok * tp.max_rows + row0 + lr;
+        const float v = own[off];
         for (int p = 0; p < tp.world; ++p) {
             if (p != tp.rank) {
-                st_release_sys(tp.flags[p] + tp.rank * TP_MAX_CTAS + flag_idx, seq);
+                st_relaxed_sys_f32(tp.buf[p] + par_base + (size_t)tp.rank * tp.area_floats + off, v);
             }
         }
     }
-    if ((int)threadIdx.x < tp.world && (int)threadIdx.x != tp.rank) {
-        const unsigned* f = tp.flags[tp.rank] + threadIdx.x * TP_MAX_CTAS + flag_idx;
+    stamp(13);   // pushed to every peer
+    float* recv = tp.buf[tp.rank] + par_base;
+    for (int i = threadIdx.x; i < nrows * a.m; i += blockDim.x) {
+        const int tok = i / nrows, lr = i - tok * nrows;
+        const size_t off = (size_t)tok * tp.max_rows + row0 + lr;
+        float pv[TP_MAX_WORLD];
         const long long t0 = clock64();
-        while ((int)(ld_acquire_sys(f) - seq) < 0) {
-            if (*abort_flag || clock64() - t0 > (1ll << 31)) {
+        bool all;
+        do {
+            // all ranks' loads in flight before the first word is looked at
+#pragma unroll
+            for (int p = 0; p < TP_MAX_WORLD; ++p) {
+                pv[p] = p < tp.world ? ld_relaxed_sys_f32(recv + (size_t)p * tp.area_floats + off) : 0.f;
+            }
+            all = true;
+#pragma unroll
+            for (int p = 0; p < TP_MAX_WORLD; ++p) {
+                all = all && (p >= tp.world || p == tp.rank || __float_as_uint(pv[p]) != 0xffffffffu);
+            }
+            if (!all && (*abort_flag || clock64() - t0 > (1ll << 31))) {
                 *abort_flag = 1;
-                atomicCAS(a.status, 0, (20 << 16) | (int)threadIdx.x);   // peer never arrived
+                atomicCAS(a.status, 0, (20 << 16) | (rb_cta0 & 0xffff));   // a peer never delivered this row block
                 break;
             }
-        }
-    }
-    __syncthreads();
-    if (!*abort_flag) {
-        const size_t par = (size_t)(seq & 1u) * tp.area_floats;
-        const int row0 = rb_cta0 * TILE_ROWS;
-        for (int i = threadIdx.x; i < nrows * a.m; i += blockDim.x) {
-            const int lr = i % nrows, tok = i / nrows;
-            const size_t off = par + (size_t)(row0 + lr) * GEMV_MAX_M + tok;
-            float v = 0.f;
-            for (int p = 0; p < tp.world; ++p) {
-                v += ld_relaxed_sys_f32(tp.buf[p] + off);
+        } while (!all);
+        float v = 0.f;
+#pragma unroll
+        for (int p = 0; p < TP_MAX_WORLD; ++p) {
+            if (p < tp.world) {
+                v += pv[p];   // rank order; the own slot holds this rank's sums
+                if (p != tp.rank) {
+                    recv[(size_t)p * tp.area_floats + off] = __uint_as_float(0xffffffffu);
+                }
             }
+        }
+        if (all) {
             if (a.out_f16) {
                 reinterpret_cast<__half*>(sg.out)[(size_t)tok * sg.n + row0 + lr] = __float2half_rn(v);
             } else {
@@ -111,7 +147,9 @@ __device__ __forceinline__ void tp_exchange(const GemvArgs& a, const GemvSeg& sg
             }
         }
     }
+    stamp(14);
     __syncthreads();
+    stamp(15);   // summed and stored
     if (threadIdx.x == 0) {
         // the last row block of this launch to finish advances the launch number
         if (atomicAdd(tp.done, 1u) == done_target - 1u) {

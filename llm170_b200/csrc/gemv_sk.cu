@@ -501,9 +501,9 @@ gemv_sk_kernel(const GemvArgs a, const SkPlan p) {
                                 park[tok * ROWS_PER_CTA + lr0] = tot[r][j];
                                 park[tok * ROWS_PER_CTA + lr1] = tot[r][2 + j];
                             } else if (tp_on) {
-                                float* o = a.tp.buf[a.tp.rank] + (size_t)(s_seq & 1u) * a.tp.area_floats;
-                                o[(size_t)row0 * GEMV_MAX_M + tok] = tot[r][j];
-                                o[(size_t)row1 * GEMV_MAX_M + tok] = tot[r][2 + j];
+                                float* o = tp_own_area(a.tp, s_seq);
+                                o[(size_t)tok * a.tp.max_rows + row0] = tot[r][j];
+                                o[(size_t)tok * a.tp.max_rows + row1] = tot[r][2 + j];
                             } else if (a.out_f16) {
                                 __half* o = reinterpret_cast<__half*>(cq.sg.out) + (size_t)tok * cq.sg.n;
                                 o[row0] = __float2half_rn(tot[r][j]);
@@ -642,11 +642,7 @@ gemv_sk_kernel(const GemvArgs a, const SkPlan p) {
             }
             const int row = r * ROWS_PER_CTA + l4 * 4;
             if (tp_on) {
-                float* o = a.tp.buf[a.tp.rank] + (size_t)(s_seq & 1u) * a.tp.area_floats + (size_t)row * GEMV_MAX_M + tok;
-                o[0] = sum.x;
-                o[GEMV_MAX_M] = sum.y;
-                o[2 * GEMV_MAX_M] = sum.z;
-                o[3 * GEMV_MAX_M] = sum.w;
+                *reinterpret_cast<float4*>(tp_own_area(a.tp, s_seq) + (size_t)tok * a.tp.max_rows + row) = sum;
             } else if (a.out_f16) {
                 const __half2 h0 = __floats2half2_rn(sum.x, sum.y), h1 = __floats2half2_rn(sum.z, sum.w);
                 uint2 pk;
@@ -668,14 +664,14 @@ gemv_sk_kernel(const GemvArgs a, const SkPlan p) {
             GemvSeg sg;
             int r, nrbv;
             row_info(rg, sg, r, nrbv);
-            tp_exchange(a, sg, r * CTA_RB, nrbv * TILE_ROWS, s_seq, abort_flag, rg, (unsigned)p.rows);
+            tp_exchange(a, sg, r * CTA_RB, nrbv * TILE_ROWS, s_seq, abort_flag, (unsigned)p.rows, dbg);
         }
         for (int sl = 0; sl < 2; ++sl) {
             if (prow[sl] >= 0 && s_last[sl]) {
                 GemvSeg sg;
                 int r, nrbv;
                 row_info(prow[sl], sg, r, nrbv);
-                tp_exchange(a, sg, r * CTA_RB, nrbv * TILE_ROWS, s_seq, abort_flag, prow[sl], (unsigned)p.rows);
+                tp_exchange(a, sg, r * CTA_RB, nrbv * TILE_ROWS, s_seq, abort_flag, (unsigned)p.rows, dbg);
             }
         }
     }

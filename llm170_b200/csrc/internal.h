@@ -23,17 +23,19 @@ void launch_dequant(const uint32_t* qt, const uint16_t* stl, void* out, int n, i
 constexpr int GEMV_MAX_SEG = 4;
 constexpr int GEMV_MAX_M = 8;
 
-// Row-parallel tensor parallelism: peers' partial-sum buffers and flag arrays, mapped into this device's
-// address space (CUDA IPC).  world <= 1 disables the fused all-reduce.
+// Row-parallel tensor parallelism: every rank's receive areas, mapped into this device's address space (CUDA
+// IPC).  world <= 1 disables the fused all-reduce.  A receive area holds, per launch parity and per source rank,
+// that rank's partial sums [8 tokens][max_rows] f32; every word is the sentinel 0xffffffff until its source has
+// written it, and the reader puts the sentinel back.
 constexpr int TP_MAX_WORLD = 8;
 constexpr int TP_MAX_CTAS = 64;   // 256-row blocks per row-parallel linear (n <= 16384)
 struct TpComm {
     int rank, world;
-    int area_floats;                  // floats per parity buffer (max_rows * 8)
-    float* buf[TP_MAX_WORLD];         // rank p's partial sums: [2 parities][max_rows][8 tokens] f32
-    unsigned* flags[TP_MAX_WORLD];    // rank p's flags: [world][TP_MAX_CTAS]; writer q sets flags[p][q][cta]
+    int max_rows;                     // rows per token of an area
+    int area_floats;                  // floats per (parity, source) area = max_rows * 8
+    float* buf[TP_MAX_WORLD];         // rank p's receive areas: [2 parities][world sources][8][max_rows] f32
     unsigned* seq;                    // local: number of fused launches completed
-    unsigned* done;                   // local: CTAs that finished the current launch's exchange
+    unsigned* done;                   // local: row blocks that finished the current launch's exchange
 };
 
 constexpr int DBG_LAUNCHES = 64;   // launches kept by the diagnostic timeline (slot = launch number mod 64)
