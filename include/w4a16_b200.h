@@ -159,8 +159,9 @@ W4A16_API int w4a16_gptq4_gemm(w4a16_dec* dec, const void* x16_host, int t, cons
 /* ---- row-parallel tensor parallelism (no counterpart in the reference, which has no collective:
  *      crates/server/src/main.rs:245-247) ------------------------------------------------------ */
 
-/* Allocates this rank's exchange block (flags + two parity buffers of max_rows x 8 f32 partial sums) and
- * returns its 64-byte CUDA IPC handle. rank/world describe the tensor-parallel group on one node
+/* Allocates this rank's exchange block (a launch counter and, for each of two launch parities and each source
+ * rank, a receive area of 8 x max_rows f32 partial sums; max_rows a multiple of 4) and returns its 64-byte CUDA
+ * IPC handle. rank/world describe the tensor-parallel group on one node
  * (world 2..8, one process per GPU). The reference has no such variant. */
 W4A16_API int w4a16_tp_create(w4a16_dec* dec, int rank, int world, int max_rows, void* handle_out64);
 /* Maps the peers' exchange blocks: `handles` holds world x 64 bytes, the handles of all ranks in rank
@@ -168,9 +169,10 @@ W4A16_API int w4a16_tp_create(w4a16_dec* dec, int rank, int world, int max_rows,
 W4A16_API int w4a16_tp_connect(w4a16_dec* dec, const void* handles_world_x64);
 /* Row-parallel decode GEMV with the all-reduce fused into the kernel: each rank holds a K slice of the
  * linear (whole scale groups), x16 is that slice of the activations, and out receives the SUM over ranks
- * of the partial products -- the kernel that reduces the split-K partials also publishes the local sums,
- * waits (bounded) for the peers' flags and adds their rows with peer loads over NVLink. Every rank must
- * make the same sequence of these calls. Replaces sk_single_dev + an NCCL all-reduce for o_proj / down
+ * of the partial products -- the kernel that reduces the split-K partials also pushes the local sums into
+ * every peer's receive area with peer stores over NVLink, waits (bounded) until the peers' sums have arrived
+ * in its own and adds them in rank order. After an abandoned launch, w4a16_kernel_status (which reports it on
+ * every rank) re-arms the exchange block. Every rank must make the same sequence of these calls. Replaces sk_single_dev + an NCCL all-reduce for o_proj / down
  * (the reference runs them on one GPU: crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:89-127). */
 W4A16_API int w4a16_sk_single_allreduce(w4a16_dec* dec, const char* name, const void* x16_dev, void* out_dev, int t,
                                         int out_kind, void* stream);

@@ -187,7 +187,6 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
                 return fail("w4a16 allreduce gemv: n=%d exceeds the exchange buffer (%d rows)", ls[0]->n, tp_max_rows);
             }
             a.tp = tp;
-            a.pdl = 0;  // the exchange buffers are reused by the next launch: no early start
         }
         if (int rc = ensure_scratch(sk_part_floats(sp), grid_x, st)) {
             return rc;
@@ -235,7 +234,6 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
             return fail("w4a16 allreduce gemv: n=%d exceeds the exchange buffer (%d rows)", ls[0]->n, tp_max_rows);
         }
         a.tp = tp;
-        a.pdl = 0;  // the exchange buffers are reused by the next launch: no early start
     }
     if (int rc = ensure_scratch(gemv_part_floats(grid_x, ks), grid_x, st)) {
         return rc;
@@ -317,6 +315,9 @@ using w4::Lin;
 static cudaStream_t pick_stream(w4a16_dec* dec, void* stream) {
     return stream ? (cudaStream_t)stream : dec->d.stream;
 }
+
+// exchange block of the fused all-reduce: header (launch counter, done counter), then the receive areas
+static const size_t TP_HEADER = 4096;
 
 extern "C" {
 
@@ -472,9 +473,14 @@ int w4a16_kernel_status(w4a16_dec* dec) {
     }
     if (st != 0) {
         cudaMemset(d.gemm_status, 0, sizeof(int));
-        // an abandoned launch may have left tickets taken
+        // an abandoned launch may have left tickets taken and peers' sums unread
         if (d.counters) {
             cudaMemset(d.counters, 0, d.counters_cap * sizeof(unsigned));
+        }
+        if (d.tp_block) {
+            const size_t data = 2 * (size_t)d.tp.world * d.tp.area_floats * sizeof(float);
+            cudaMemset(d.tp_block, 0, TP_HEADER);
+            cudaMemset((char*)d.tp_block + TP_HEADER, 0xff, data);
         }
         return d.fail("w4a16: a bounded pipeline wait expired (role %d, step %d); results are invalid", st >> 16,
                       st & 0xFFFF);
@@ -717,8 +723,6 @@ int w4a16_sk_single_dev(w4a16_dec* dec, const char* name, const void* x16_dev, v
 
 // ---- row-parallel tensor parallelism ----------------------------------------------------------------
 // exchange block layout: [seq u32][done u32][pad -> 4096 B][2 parities x world sources x 8 x max_rows f32, all ones]
-static const size_t TP_HEADER = 4096;
-
 int w4a16_tp_create(w4a16_dec* dec, int rank, int world, int max_rows, void* handle_out64) {
     Dec& d = dec->d;
     if (world < 2 || world > w4::TP_MAX_WORLD || rank < 0 || rank >= world || max_rows < 16 ||

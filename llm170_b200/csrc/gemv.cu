@@ -163,7 +163,6 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     __shared__ unsigned s_seq;
     const bool tp_on = a.tp.world > 1;
     if (threadIdx.x == 0) {
-        s_seq = tp_on ? *a.tp.seq + 1u : 0u;   // this launch's exchange number (advanced by the last CTA to finish)
         if (stamp) {
             stamp_now(0);   // CTA entry
             unsigned smid;
@@ -234,6 +233,8 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x == 0) {
+        // this launch's exchange number: read only now, the previous launch advances it as it ends
+        s_seq = tp_on ? *reinterpret_cast<volatile unsigned*>(a.tp.seq) + 1u : 0u;
         mbar_expect_tx(xbar, m_loc * halves * 2);
         for (int tok = 0; tok < m_loc; ++tok) {
             bulk_load(sbase + tok * p.x_stride * 2, x_loc + (size_t)tok * a.k + (size_t)kb0 * TILE_K, halves * 2, xbar);
@@ -527,7 +528,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
             }
         }
         if (tp_on) {
-            tp_exchange(a, sg, rb_cta0, nrbv * TILE_ROWS, s_seq, abort_flag, gridDim.x);
+            tp_exchange(a, sg, rb_cta0, nrbv * TILE_ROWS, &s_seq, abort_flag, gridDim.x);
         }
         if (stamp && threadIdx.x == 0) {
             stamp_now(5);
@@ -646,7 +647,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         a.counters[blockIdx.x] = 0;  // ready for the next launch (graph replay needs no memset)
     }
     if (tp_on) {
-        tp_exchange(a, sg, rb_cta0, nrows, s_seq, abort_flag, gridDim.x);
+        tp_exchange(a, sg, rb_cta0, nrows, &s_seq, abort_flag, gridDim.x);
     }
     if (stamp && threadIdx.x == 0) {
         stamp_now(5);

@@ -79,8 +79,11 @@ __device__ __forceinline__ void st_relaxed_sys_f32(float* p, float v) {
 // each with weight copies in flight).  No multicast, no second kernel, no NCCL call.  Two parities: a peer can
 // be at most one launch ahead, and then writes the other half.
 // The launch number advances when `done_target` row blocks of this launch have been exchanged.
-__device__ __forceinline__ void tp_exchange(const GemvArgs& a, const GemvSeg& sg, int rb_cta0, int nrows, unsigned seq,
-                                            volatile int* abort_flag, unsigned done_target, long long* dbg = nullptr) {
+// `seq_smem`: this launch's exchange number in shared memory (thread 0 reads it from the device counter after the
+// launch's dependency wait); it is read here after the first barrier.
+__device__ __forceinline__ void tp_exchange(const GemvArgs& a, const GemvSeg& sg, int rb_cta0, int nrows,
+                                            const unsigned* seq_smem, volatile int* abort_flag, unsigned done_target,
+                                            long long* dbg = nullptr) {
     const TpComm& tp = a.tp;
     auto stamp = [&](int j) {
         if (dbg != nullptr && threadIdx.x == 0) {
@@ -90,6 +93,7 @@ __device__ __forceinline__ void tp_exchange(const GemvArgs& a, const GemvSeg& sg
         }
     };
     __syncthreads();
+    const unsigned seq = *seq_smem;
     stamp(12);   // local sums written
     const int row0 = rb_cta0 * TILE_ROWS;
     const size_t par_base = (size_t)(seq & 1u) * tp.world * tp.area_floats;

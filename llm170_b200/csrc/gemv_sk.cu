@@ -160,7 +160,6 @@ gemv_sk_kernel(const GemvArgs a, const SkPlan p) {
 
     const bool tp_on = a.tp.world > 1;
     if (threadIdx.x == 0) {
-        s_seq = tp_on ? *a.tp.seq + 1u : 0u;
         if (stamp) {
             stamp_now(0);
             unsigned smid;
@@ -275,6 +274,10 @@ gemv_sk_kernel(const GemvArgs a, const SkPlan p) {
     // Programmatic dependent launch: weights and scales do not depend on the previous kernel of the stream and
     // are already in flight while it drains; x, scratch and outputs are touched only after this wait.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (threadIdx.x == 0) {
+        // this launch's exchange number: read only now, the previous launch advances it as it ends
+        s_seq = tp_on ? *reinterpret_cast<volatile unsigned*>(a.tp.seq) + 1u : 0u;
+    }
 
     if (is_producer) {
         if (lane == 0) {
@@ -664,14 +667,14 @@ gemv_sk_kernel(const GemvArgs a, const SkPlan p) {
             GemvSeg sg;
             int r, nrbv;
             row_info(rg, sg, r, nrbv);
-            tp_exchange(a, sg, r * CTA_RB, nrbv * TILE_ROWS, s_seq, abort_flag, (unsigned)p.rows, dbg);
+            tp_exchange(a, sg, r * CTA_RB, nrbv * TILE_ROWS, &s_seq, abort_flag, (unsigned)p.rows, dbg);
         }
         for (int sl = 0; sl < 2; ++sl) {
             if (prow[sl] >= 0 && s_last[sl]) {
                 GemvSeg sg;
                 int r, nrbv;
                 row_info(prow[sl], sg, r, nrbv);
-                tp_exchange(a, sg, r * CTA_RB, nrbv * TILE_ROWS, s_seq, abort_flag, (unsigned)p.rows, dbg);
+                tp_exchange(a, sg, r * CTA_RB, nrbv * TILE_ROWS, &s_seq, abort_flag, (unsigned)p.rows, dbg);
             }
         }
     }
