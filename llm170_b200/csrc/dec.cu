@@ -253,7 +253,8 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
 // w4a16_gemv_experts_* kernels (crates/backend-gpu/src/rawcuda/assets/gptq4.cu:317-374,
 // crates/backend-gpu/src/rawcuda/w4a16_dec/moe/moe_gemv.rs:92-114).
 int Dec::gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert, const MoeBufs& b, int max_tiles,
-                      int est_tiles, const float* row_w, cudaStream_t st) {
+                      int est_tiles, const float* row_w, cudaStream_t st, const int* x_slot_of_pos,
+                      int x_slots_per_token) {
     GemvArgs a{};
     a.nseg = 1;
     a.k = l->k;
@@ -295,6 +296,8 @@ int Dec::gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert,
     a.tile_rows = b.tile_rows;
     a.num_tiles = b.n_tiles;
     a.row_w = row_w;
+    a.x_slot_of_pos = x_slot_of_pos;
+    a.x_slots_per_token = x_slots_per_token;
     a.nrb_w = l->n / TILE_ROWS;
     a.tp = TpComm{};
     a.part = part;

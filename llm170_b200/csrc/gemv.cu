@@ -237,7 +237,12 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         s_seq = tp_on ? *reinterpret_cast<volatile unsigned*>(a.tp.seq) + 1u : 0u;
         mbar_expect_tx(xbar, m_loc * halves * 2);
         for (int tok = 0; tok < m_loc; ++tok) {
-            bulk_load(sbase + tok * p.x_stride * 2, x_loc + (size_t)tok * a.k + (size_t)kb0 * TILE_K, halves * 2, xbar);
+            const uint16_t* xr = x_loc + (size_t)tok * a.k;
+            if (a.x_slot_of_pos != nullptr) {
+                // the activations were not gathered into sorted order: fetch the token's row
+                xr = a.x + (size_t)(a.x_slot_of_pos[row_base + tok] / a.x_slots_per_token) * a.k;
+            }
+            bulk_load(sbase + tok * p.x_stride * 2, xr + (size_t)kb0 * TILE_K, halves * 2, xbar);
         }
         if (stamp) {
             stamp_now(1);   // the previous kernel of the stream is complete; x requested

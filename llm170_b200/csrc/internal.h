@@ -78,6 +78,8 @@ struct GemvArgs {
     const int* tile_rows;
     const int* num_tiles;
     const float* row_w;   // optional factor per sorted row, applied at the final store
+    const int* x_slot_of_pos;   // optional gather: sorted row r reads x row x_slot_of_pos[r] / x_slots_per_token
+    int x_slots_per_token;
     int nrb_w;            // 16-row blocks of the whole resident matrix (tile pitch); 0 = seg n / 16
     TpComm tp;          // fused all-reduce over peers (row-parallel); tp.world <= 1: off
     int* status;        // device word that records the first bounded wait that expired
@@ -124,6 +126,9 @@ struct MoeBufs;
 void launch_moe_topk(const float* logits, int* idx, float* wt, int t, int n_exp, int k, cudaStream_t st);
 // histogram -> offsets + m-tile table (tiles of `bm` rows) -> placement of the local experts' slots
 void launch_moe_align(const MoeBufs& b, int ns, int n_exp, int e0, int e1, int bm, cudaStream_t st);
+// the same tables as topk + align for at most 1024 slots, in one launch of one block
+void launch_moe_route_small(const float* logits, const MoeBufs& b, int t, int n_exp, int k, int e0, int e1, int bm,
+                            cudaStream_t st);
 void launch_moe_gather(const void* x, const MoeBufs& b, int ns, int k, int h, cudaStream_t st);
 void launch_moe_act(const MoeBufs& b, int rows_upper, int ffn, cudaStream_t st);
 void launch_moe_combine(const MoeBufs& b, void* out, int t, int h, int k, int out_f16, cudaStream_t st);

@@ -24,14 +24,8 @@ constexpr int TOPK_WARPS = 8;
 // One warp per token. p_e = exp(l_e - max); pick k times the largest remaining p (ties: lower index);
 // weights = p / sum of the picked p. Same selection rule as select_topk
 // (crates/core/src/qwen35/stages/moe.rs:8-31), which divides by the full softmax sum first; that factor cancels.
-__global__ void moe_topk_kernel(const float* __restrict__ lg, int* __restrict__ idx, float* __restrict__ wt, int t,
-                                int n, int k) {
-    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ti = blockIdx.x * TOPK_WARPS + w;
-    if (ti >= t) {
-        return;
-    }
-    const float* l = lg + (size_t)ti * n;
+__device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* __restrict__ idx, float* __restrict__ wt,
+                                              int n, int k, int lane) {
     float mx = -INFINITY;
     for (int i = lane; i < n; i += 32) {
         mx = fmaxf(mx, l[i]);
@@ -71,7 +65,7 @@ __global__ void moe_topk_kernel(const float* __restrict__ lg, int* __restrict__ 
             used |= 1u << (bi >> 5);
         }
         if (lane == 0) {
-            idx[(size_t)ti * k + r] = bi;
+            idx[r] = bi;
         }
         if (lane == (r & 31)) {
             mine = bv;
@@ -79,7 +73,81 @@ __global__ void moe_topk_kernel(const float* __restrict__ lg, int* __restrict__ 
         wsum += bv;
     }
     if (lane < k) {
-        wt[(size_t)ti * k + lane] = mine / wsum;
+        wt[lane] = mine / wsum;
+    }
+}
+
+__global__ void moe_topk_kernel(const float* __restrict__ lg, int* __restrict__ idx, float* __restrict__ wt, int t,
+                                int n, int k) {
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ti = blockIdx.x * TOPK_WARPS + w;
+    if (ti >= t) {
+        return;
+    }
+    topk_of_token(lg + (size_t)ti * n, idx + (size_t)ti * k, wt + (size_t)ti * k, n, k, lane);
+}
+
+// Decode-sized batches (at most 1024 (token, expert) slots): routing, histogram, offsets, tile table, placement
+// and sorted routing weights in ONE block of 1024 threads -- the six launches they take otherwise cost more
+// than the expert matmuls of a single token.  Same tables as the separate kernels below.
+__global__ void __launch_bounds__(1024)
+moe_route_small_kernel(const float* __restrict__ lg, int* __restrict__ idx, float* __restrict__ wt,
+                       int* __restrict__ off, int* __restrict__ pos_of_slot, int* __restrict__ slot_of_pos,
+                       int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ tile_rows,
+                       int* __restrict__ n_tiles, int* __restrict__ n_rows, float* __restrict__ row_w, int t, int n_exp,
+                       int k, int e0, int e1, int bm) {
+    __shared__ int s_rows[1024], s_tiles[1024], s_off[1024], s_cursor[1024];
+    const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+    s_rows[tid] = 0;
+    s_cursor[tid] = 0;
+    for (int ti = w; ti < t; ti += 32) {
+        topk_of_token(lg + (size_t)ti * n_exp, idx + (size_t)ti * k, wt + (size_t)ti * k, n_exp, k, lane);
+    }
+    __syncthreads();   // idx / wt of every token are visible to the block
+    const int ns = t * k;
+    int my_e = -1;
+    if (tid < ns) {
+        my_e = idx[tid];
+        if (my_e >= e0 && my_e < e1) {
+            atomicAdd(&s_rows[my_e], 1);
+        } else {
+            my_e = -1;
+        }
+    }
+    __syncthreads();
+    const int c = s_rows[tid];
+    s_tiles[tid] = (c + bm - 1) / bm;
+    __syncthreads();
+    for (int d = 1; d < 1024; d <<= 1) {   // inclusive Hillis-Steele scan of both arrays
+        const int r = tid >= d ? s_rows[tid - d] : 0, tt = tid >= d ? s_tiles[tid - d] : 0;
+        __syncthreads();
+        s_rows[tid] += r;
+        s_tiles[tid] += tt;
+        __syncthreads();
+    }
+    const int row0 = s_rows[tid] - c, tile0 = s_tiles[tid] - (c + bm - 1) / bm;
+    s_off[tid] = row0;
+    if (tid < n_exp) {
+        off[tid] = row0;
+    }
+    for (int r = 0, i = tile0; r < c; r += bm, ++i) {
+        tile_expert[i] = tid;
+        tile_row0[i] = row0 + r;
+        tile_rows[i] = min(bm, c - r);
+    }
+    if (tid == 1023) {
+        *n_tiles = s_tiles[tid];
+        *n_rows = s_rows[tid];
+    }
+    __syncthreads();
+    if (tid < ns) {
+        int pos = -1;
+        if (my_e >= 0) {
+            pos = s_off[my_e] + atomicAdd(&s_cursor[my_e], 1);
+            slot_of_pos[pos] = tid;
+            row_w[pos] = wt[tid];
+        }
+        pos_of_slot[tid] = pos;  // -1: the expert lives on another rank
     }
 }
 
@@ -239,6 +307,13 @@ inline int blocks_for(size_t total, int threads) {
 
 void launch_moe_topk(const float* logits, int* idx, float* wt, int t, int n_exp, int k, cudaStream_t st) {
     moe_topk_kernel<<<(t + TOPK_WARPS - 1) / TOPK_WARPS, TOPK_WARPS * 32, 0, st>>>(logits, idx, wt, t, n_exp, k);
+}
+
+void launch_moe_route_small(const float* logits, const MoeBufs& b, int t, int n_exp, int k, int e0, int e1, int bm,
+                            cudaStream_t st) {
+    moe_route_small_kernel<<<1, 1024, 0, st>>>(logits, b.idx, b.wt, b.off, b.pos_of_slot, b.slot_of_pos, b.tile_expert,
+                                               b.tile_row0, b.tile_rows, b.n_tiles, b.n_rows, b.row_w, t, n_exp, k, e0,
+                                               e1, bm);
 }
 
 void launch_moe_align(const MoeBufs& b, int ns, int n_exp, int e0, int e1, int bm, cudaStream_t st) {

@@ -91,10 +91,11 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
     if (int rc = ensure_moe(t, st)) {
         return rc;
     }
+    if (((uintptr_t)x16 & 15) != 0) {
+        return fail("w4a16 moe_ffn: x must be 16-byte aligned");
+    }
     const int ns = t * moe.top_k;
     const int n_local = moe.e1 - moe.e0;
-    launch_moe_topk(logits, mb.idx, mb.wt, t, moe.n_experts, moe.top_k, st);
-    launches += 6;
     if ((long long)ns <= 8LL * moe.n_experts) {
         // decode-sized batches (on average at most 8 rows per expert): the op is weight streaming, so every
         // <=8-row segment of an expert runs through the GEMV kernel instead of a padded 128-row MMA tile
@@ -103,10 +104,22 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
         if (max_tiles > mb.max_tiles) {
             return fail("w4a16 moe_ffn: tile table too small");
         }
-        launch_moe_align(mb, ns, moe.n_experts, moe.e0, moe.e1, 8, st);
-        launch_moe_gather(x16, mb, ns, moe.top_k, moe.hidden, st);
-        if (int rc = gemv_grouped(&i13->second, mb.xs, mb.c13, 2 * moe.ffn, mb, max_tiles, est_tiles, nullptr, st)) {
-            return rc;
+        if (ns <= 1024) {
+            // routing and all dispatch tables in one launch; the first grouped GEMV fetches each row's token itself
+            launch_moe_route_small(logits, mb, t, moe.n_experts, moe.top_k, moe.e0, moe.e1, 8, st);
+            launches += 1;
+            if (int rc = gemv_grouped(&i13->second, x16, mb.c13, 2 * moe.ffn, mb, max_tiles, est_tiles, nullptr, st,
+                                      mb.slot_of_pos, moe.top_k)) {
+                return rc;
+            }
+        } else {
+            launch_moe_topk(logits, mb.idx, mb.wt, t, moe.n_experts, moe.top_k, st);
+            launch_moe_align(mb, ns, moe.n_experts, moe.e0, moe.e1, 8, st);
+            launch_moe_gather(x16, mb, ns, moe.top_k, moe.hidden, st);
+            launches += 6;
+            if (int rc = gemv_grouped(&i13->second, mb.xs, mb.c13, 2 * moe.ffn, mb, max_tiles, est_tiles, nullptr, st)) {
+                return rc;
+            }
         }
         launch_moe_act(mb, ns, moe.ffn, st);
         if (int rc = gemv_grouped(&i2->second, mb.act, mb.c2, moe.hidden, mb, max_tiles, est_tiles, mb.row_w, st)) {
@@ -116,6 +129,8 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
         // 256-row tiles (two accumulators per CTA) once the average expert segment fills most of one
         const int bm = ((long long)ns * 4 >= (long long)moe.n_experts * 3 * 256) ? 256 : MOE_BM;
         const int max_tiles = (ns + bm - 1) / bm + n_local;
+        launch_moe_topk(logits, mb.idx, mb.wt, t, moe.n_experts, moe.top_k, st);
+        launches += 6;
         launch_moe_align(mb, ns, moe.n_experts, moe.e0, moe.e1, bm, st);
         launch_moe_gather(x16, mb, ns, moe.top_k, moe.hidden, st);
         if (int rc = gemm_grouped(&i13->second, mb.xs, ns, mb.c13, 2 * moe.ffn, mb, max_tiles, bm / 128, nullptr, st)) {
