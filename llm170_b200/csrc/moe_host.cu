@@ -99,8 +99,10 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
     if ((long long)ns <= 8LL * moe.n_experts) {
         // decode-sized batches (on average at most 8 rows per expert): the op is weight streaming, so every
         // <=8-row segment of an expert runs through the GEMV kernel instead of a padded 128-row MMA tile
-        const int max_tiles = (ns + 7) / 8 + n_local;
+        // every expert with rows adds at most one partial segment to the ns / 8 full ones: the grid is sized for
+        // this bound, and CTAs beyond the actual count leave at once
         const int est_tiles = ns < n_local ? ns : n_local;   // segments expected to be non-empty (split-K sizing)
+        const int max_tiles = est_tiles + ns / 8;
         if (max_tiles > mb.max_tiles) {
             return fail("w4a16 moe_ffn: tile table too small");
         }
