@@ -144,7 +144,7 @@ def run_reference_arm(args, rank: int):
     for _ in range(args.steps):
         tot += one_step()[0]
     per_layer_s = tot / (args.steps * sample_layers)
-    gbs = (step_bytes() / 64) / per_layer_s / 1e9
+    gbs = step_bytes() / per_layer_s / 1e9   # step_bytes(): algorithmic bytes of ONE layer at M=1
     ms_step = per_layer_s * 64 * 1e3
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,

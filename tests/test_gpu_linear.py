@@ -98,7 +98,7 @@ def test_bf16_scales_exact_or_rejected(dec, orc):
 
 
 @pytest.mark.parametrize("subn", [1, 0])
-@pytest.mark.parametrize("ksplit", [1, 2, 4])
+@pytest.mark.parametrize("ksplit", [1, 2, 4, -1])
 def test_decode_selfcheck_kat(dec, ksplit, subn):
     # crates/backend-gpu/src/rawcuda/w4a16_dec/probe.rs:1291-1426: scale = x = 1 -> y = sum(nib-8), bit-exact,
     # for split-K 1/2/4 and for a two-segment launch.
@@ -110,7 +110,9 @@ def test_decode_selfcheck_kat(dec, ksplit, subn):
     want = nib.reshape(n, -1).sum(axis=1).astype(np.float32)
     dec.upload_lin_g("sc", q, s, n, k, 128)
     x = torch.ones(k, dtype=torch.float16, device="cuda")
-    dec.set_tuning("gemv_ksplit", ksplit)
+    # ksplit >= 1: the (row block, K split) form of the kernel; -1: the persistent form
+    dec.set_tuning("gemv_persistent", 2 if ksplit < 0 else 0)
+    dec.set_tuning("gemv_ksplit", max(ksplit, 0))
     dec.set_tuning("gemv_subnormal", subn)
     try:
         y = dec.sk_single_dev("sc", x).cpu().numpy()[0]
@@ -120,6 +122,7 @@ def test_decode_selfcheck_kat(dec, ksplit, subn):
     finally:
         dec.set_tuning("gemv_ksplit", 0)
         dec.set_tuning("gemv_subnormal", 1)
+        dec.set_tuning("gemv_persistent", 1)
 
 
 @pytest.mark.parametrize("subn", [1, 0])
@@ -155,15 +158,20 @@ def test_gemv_vs_lane_oracle(dec, orc, n, k, group, t):
     q, s = synth.make_linear(n, k, group, seed=100 + n % 97 + t)
     x = synth.make_acts(t, k, seed=200 + t)
     dec.upload_lin_g("g", q, s, n, k, group)
-    y = dec.lin_forward("g", x_dev(x), t)
     rows = (0, n) if n * k * t <= (1 << 28) else (n // 2 - 256, n // 2 + 256)
     want = orc.linear_lane(q, s, x, t, n, k, group, rows=rows)
-    got = y.cpu().numpy()[:, rows[0]:rows[1]]
-    err = np.abs(got.astype(np.float64) - want[:, rows[0]:rows[1]]).max()
-    assert err <= TOL, err
-    # f16 output is the f32 result rounded once
-    y16 = dec.lin_forward("g", x_dev(x), t, out_f16=True).cpu().numpy()
-    assert np.array_equal(y16.view(np.uint16), y.cpu().numpy().astype(np.float16).view(np.uint16))
+    try:
+        for form in (2, 0):                  # the persistent form, then the (row block, K split) form
+            dec.set_tuning("gemv_persistent", form)
+            y = dec.lin_forward("g", x_dev(x), t)
+            got = y.cpu().numpy()[:, rows[0]:rows[1]]
+            err = np.abs(got.astype(np.float64) - want[:, rows[0]:rows[1]]).max()
+            assert err <= TOL, (form, err)
+            # f16 output is the f32 result rounded once
+            y16 = dec.lin_forward("g", x_dev(x), t, out_f16=True).cpu().numpy()
+            assert np.array_equal(y16.view(np.uint16), y.cpu().numpy().astype(np.float16).view(np.uint16))
+    finally:
+        dec.set_tuning("gemv_persistent", 1)
     dec.drop_lin("g")
 
 
