@@ -45,7 +45,10 @@ def test_topk_matches_oracle(dec, orc, t, n_exp, k):
 # small t*k/n_exp -> grouped GEMV segments of <=8 rows; larger -> grouped tensor-core GEMM with 128- or 256-row tiles
 @pytest.mark.parametrize("t,n_exp,k,f,h,group", [(1, 8, 2, 64, 128, 32), (9, 8, 2, 128, 256, 32), (64, 16, 4, 256, 512, 32),
                                                 (300, 8, 2, 192, 256, 32), (40, 4, 2, 256, 256, 128),
-                                                (30, 16, 4, 320, 576, 32), (1000, 4, 2, 128, 256, 32)])
+                                                (30, 16, 4, 320, 576, 32), (1000, 4, 2, 128, 256, 32),
+                                                # 1024 slots: the largest batch of the one-launch routing; and a
+                                                # decode-sized batch beyond it (separate routing kernels, GEMV tiles)
+                                                (128, 128, 8, 64, 128, 32), (200, 256, 8, 64, 128, 32)])
 def test_moe_ffn_vs_oracle(dec, orc, t, n_exp, k, f, h, group):
     w13_q, w13_s, w2_q, w2_s = synth.make_experts(n_exp, f, h, group, seed=7 + t)
     x = synth.make_acts(t, h, seed=11 + t)
@@ -79,9 +82,11 @@ def test_moe_empty_experts_and_all_to_one(dec, orc):
     assert np.abs(y.cpu().numpy() - orc.moe_ffn(x, lg, *w, k, 32)).max() <= TOL
 
 
-def test_expert_parallel_partials_sum_to_full(dec, orc):
+@pytest.mark.parametrize("t", [48, 16, 1])
+def test_expert_parallel_partials_sum_to_full(dec, orc, t):
     # two "ranks" emulated in sequence on one GPU: each holds half the experts, partial outputs add up
-    t, n_exp, k, f, h = 48, 8, 2, 128, 256
+    # (48 tokens take the grouped GEMM, 16 and 1 the decode path with its one-launch routing)
+    n_exp, k, f, h = 8, 2, 128, 256
     w13_q, w13_s, w2_q, w2_s = synth.make_experts(n_exp, f, h, 32, seed=5)
     x = synth.make_acts(t, h, seed=6)
     lg = synth.make_router_logits(t, n_exp, seed=7)
