@@ -160,6 +160,8 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
     }
     const int nkb = a.k / BK;
     const int nrbv = min(BN, a.n - n0) / TILE_ROWS;  // valid 16-row blocks in this tile
+    // 128-token blocks of this tile that hold rows: an empty second block is neither fetched nor multiplied
+    const int mt_live = (MT == 2 && rows_valid <= BM) ? 1 : MT;
 
     const bool stamp = a.dbg != nullptr && blockIdx.x == 0;
     if (stamp && threadIdx.x == 0) {
@@ -201,10 +203,12 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                 if (stamp && it < 1000) {
                     a.dbg[it] = clock64();
                 }
-                mbar_expect_tx(full_bar(s), A_STAGE + nrbv * (TILE_WORDS * 4));
+                mbar_expect_tx(full_bar(s), mt_live * A_BYTES + nrbv * (TILE_WORDS * 4));
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    tma_load_2d(a_addr(s) + mt * A_BYTES, &tmap_x, it * BK, m0 + mt * BM, full_bar(s));
+                    if (mt < mt_live) {
+                        tma_load_2d(a_addr(s) + mt * A_BYTES, &tmap_x, it * BK, m0 + mt * BM, full_bar(s));
+                    }
                 }
                 // the tile's row blocks are contiguous at one k-block (k-block-major layout): one copy
                 bulk_load(raw_addr(s), a.qt + ((size_t)it * a.nrb_w + rb0) * TILE_WORDS,
@@ -231,10 +235,12 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                 const uint64_t db = umma_desc(b_addr(sb));
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
-                    const uint64_t da = umma_desc(a_addr(s) + mt * A_BYTES);
+                    if (mt < mt_live) {
+                        const uint64_t da = umma_desc(a_addr(s) + mt * A_BYTES);
 #pragma unroll
-                    for (int j = 0; j < BK / 16; ++j) {
-                        umma_f16(tmem + mt * 256, da + 2 * j, db + 2 * j, IDESC, (it > 0 || j > 0) ? 1u : 0u);
+                        for (int j = 0; j < BK / 16; ++j) {
+                            umma_f16(tmem + mt * 256, da + 2 * j, db + 2 * j, IDESC, (it > 0 || j > 0) ? 1u : 0u);
+                        }
                     }
                 }
                 umma_commit(empty_bar(s));
@@ -327,7 +333,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int quad = warp & 3;
                 const int ncols = min(BN, a.n - n0);
-                for (int mc = 0; mc < MT * (BN / 32); ++mc) {
+                for (int mc = 0; mc < mt_live * (BN / 32); ++mc) {
                     const int mt = mc / (BN / 32), c0 = (mc % (BN / 32)) * 32;
                     if (c0 >= ncols || (mc & 3) != (dw >> 2)) {
                         continue;
