@@ -196,14 +196,18 @@ __global__ void moe_offsets_kernel(const int* __restrict__ cnt, int* __restrict_
     }
 }
 
-__global__ void moe_place_kernel(const int* __restrict__ idx, const int* __restrict__ off, int* __restrict__ cursor,
-                                 int* __restrict__ pos_of_slot, int* __restrict__ slot_of_pos, int ns, int e0, int e1) {
+// placement of the local experts' slots in sorted order, with the routing weight of each sorted row
+// (grouped matmul 2 multiplies by it)
+__global__ void moe_place_kernel(const int* __restrict__ idx, const float* __restrict__ wt, const int* __restrict__ off,
+                                 int* __restrict__ cursor, int* __restrict__ pos_of_slot, int* __restrict__ slot_of_pos,
+                                 float* __restrict__ row_w, int ns, int e0, int e1) {
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ns; i += gridDim.x * blockDim.x) {
         const int e = idx[i];
         int pos = -1;
         if (e >= e0 && e < e1) {
             pos = off[e] + atomicAdd(cursor + e, 1);
             slot_of_pos[pos] = i;
+            row_w[pos] = wt[i];
         }
         pos_of_slot[i] = pos;  // -1: the expert lives on another rank
     }
@@ -283,18 +287,6 @@ __global__ void moe_combine_kernel(const __half* __restrict__ c2, void* __restri
     }
 }
 
-// sorted routing weight of each row (GEMM-2 multiplies by it)
-__global__ void moe_row_weight_kernel(const float* __restrict__ wt, const int* __restrict__ slot_of_pos,
-                                      const int* __restrict__ pos_of_slot, float* __restrict__ row_w, int ns) {
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < ns; i += gridDim.x * blockDim.x) {
-        const int pos = pos_of_slot[i];
-        if (pos >= 0) {
-            row_w[pos] = wt[i];
-        }
-    }
-    (void)slot_of_pos;
-}
-
 inline int blocks_for(size_t total, int threads) {
     size_t b = (total + threads - 1) / threads;
     if (b > 148 * 16) {
@@ -321,8 +313,8 @@ void launch_moe_align(const MoeBufs& b, int ns, int n_exp, int e0, int e1, int b
     moe_count_kernel<<<blocks_for(ns, 256), 256, 0, st>>>(b.idx, b.cnt, ns, e0, e1);
     moe_offsets_kernel<<<1, 1024, 0, st>>>(b.cnt, b.off, b.cursor, b.tile_expert, b.tile_row0, b.tile_rows, b.n_tiles,
                                           b.n_rows, n_exp, e0, e1, bm);
-    moe_place_kernel<<<blocks_for(ns, 256), 256, 0, st>>>(b.idx, b.off, b.cursor, b.pos_of_slot, b.slot_of_pos, ns, e0, e1);
-    moe_row_weight_kernel<<<blocks_for(ns, 256), 256, 0, st>>>(b.wt, b.slot_of_pos, b.pos_of_slot, b.row_w, ns);
+    moe_place_kernel<<<blocks_for(ns, 256), 256, 0, st>>>(b.idx, b.wt, b.off, b.cursor, b.pos_of_slot, b.slot_of_pos, b.row_w,
+                                                          ns, e0, e1);
 }
 
 void launch_moe_gather(const void* x, const MoeBufs& b, int ns, int k, int h, cudaStream_t st) {

@@ -118,7 +118,7 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
             launch_moe_topk(logits, mb.idx, mb.wt, t, moe.n_experts, moe.top_k, st);
             launch_moe_align(mb, ns, moe.n_experts, moe.e0, moe.e1, 8, st);
             launch_moe_gather(x16, mb, ns, moe.top_k, moe.hidden, st);
-            launches += 6;
+            launches += 5;
             if (int rc = gemv_grouped(&i13->second, mb.xs, mb.c13, 2 * moe.ffn, mb, max_tiles, est_tiles, nullptr, st)) {
                 return rc;
             }
@@ -132,7 +132,7 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
         const int bm = ((long long)ns * 4 >= (long long)moe.n_experts * 3 * 256) ? 256 : MOE_BM;
         const int max_tiles = (ns + bm - 1) / bm + n_local;
         launch_moe_topk(logits, mb.idx, mb.wt, t, moe.n_experts, moe.top_k, st);
-        launches += 6;
+        launches += 5;
         launch_moe_align(mb, ns, moe.n_experts, moe.e0, moe.e1, bm, st);
         launch_moe_gather(x16, mb, ns, moe.top_k, moe.hidden, st);
         if (int rc = gemm_grouped(&i13->second, mb.xs, ns, mb.c13, 2 * moe.ffn, mb, max_tiles, bm / 128, nullptr, st)) {
