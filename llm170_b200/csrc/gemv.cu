@@ -1,4 +1,6 @@
-// Decode-time W4A16 split-K GEMV for 1..8 tokens:  y[m][n] = sum_k x[m][k] * (q[n][k]-8) * s[n][k/group].
+// Decode-time W4A16 split-K GEMV for 1..8 tokens:  y[m][n] = sum_k x[m][k] * (q[n][k]-8) * s[n][k/group],
+// (row block, K split) form: grid (256-row blocks, K splits).  Dec::gemv uses it for 5..8 tokens, the MoE decode
+// path uses its table-driven "grouped" mode; up to 4 tokens run the persistent form in gemv_sk.cu.
 //
 // Takes the place of the reference's split-K GEMV pair (crates/backend-gpu/src/rawcuda/assets/decode.cu:46-267,
 // launched from crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:23-127) and of its FFMA
@@ -6,14 +8,18 @@
 //   * the 16 rows of each mma.sync m16n8k16 are WEIGHT rows and the 8 columns are tokens, so
 //     m = 1..8 all use the same kernel and no MMA row is padding;
 //   * weights never become rounded f16 values: the MMA multiplies the raw nibble (as an exact f16
-//     subnormal, nibble * 2^-24 or 2^-20) by x, and the power of two, the zero point 8 (through a
-//     per-group sum of x) and the f32 group scale are applied to the f32 accumulator once per group;
+//     subnormal, nibble * 2^-24 or 2^-20) by x; the zero point 8 enters as the C operand of a group's first
+//     MMA (-8 * sum of x over the group, pre-scaled), the f32 group scale is applied to the accumulator once
+//     per group and the power of two once at the end;
 //   * a CTA owns 256 weight rows and a K range.  One producer lane streams them through a ring of
 //     16 KB stages in shared memory with 8 KB bulk (TMA) copies -- the 16 row blocks of a CTA are
 //     contiguous at each k-block in the T64 layout -- and 8 consumer warps (two row blocks each, sharing
-//     the x fragments) only wait on a "full" mbarrier and arrive on an "empty" one;
-//   * split-K partials are reduced by the last CTA to arrive (atomic ticket, no spin, fixed summation
-//     order): no second launch, reproducible results, and the tickets are left at zero for graph replay;
+//     the x fragments) keep the next k-block in registers while they multiply the current one, wait only on a
+//     "full" mbarrier and arrive on an "empty" one as soon as a stage is in registers;
+//   * the K splits of a row block form a thread-block cluster and sum their partials through distributed
+//     shared memory (2..8 splits); otherwise the partials go to global scratch and the last CTA to arrive
+//     reduces them (atomic ticket, no spin).  Either way: fixed summation order, no second launch, and the
+//     tickets are left at zero for graph replay;
 //   * launched with programmatic stream serialization: the weight stream starts while the previous
 //     kernel of the stream drains; x, scratch and outputs are touched only after griddepcontrol.wait.
 // The kernel is HBM-bound.
