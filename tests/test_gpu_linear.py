@@ -271,3 +271,28 @@ def test_host_buffer_forward_and_gptq4_gate(dec, orc):
     dec.upload_lin_g("hb", q, s, n, k, group)
     y = dec.lin_forward_host("hb", x, 8)
     assert np.array_equal(y, got8)
+
+
+def test_debug_timeline_stamps_are_ordered(dec):
+    # w4a16_debug_timeline: every CTA of a decode launch stamps entry <= dependency wait <= x staged <= main loop
+    # start <= main loop end <= exit (nanoseconds of the global timer), then its SM id and unit count
+    n, k = 2048, 1024
+    q, s = synth.make_linear(n, k, 128, seed=3)
+    dec.upload_lin_g("tl", q, s, n, k, 128)
+    x = x_dev(synth.make_acts(1, k, seed=4))
+    ref = dec.sk_single_dev("tl", x).clone()
+    dec.set_tuning("debug_timeline", 1)
+    try:
+        c0 = dec.launch_count()
+        y = dec.sk_single_dev("tl", x)
+        tl = dec.debug_timeline().reshape(64, 384, 16)[c0 % 64]
+        live = tl[tl[:, 0] > 0]
+        assert len(live) > 0 and len(live) <= 384
+        for a, b in ((0, 1), (1, 2), (2, 3), (3, 4), (4, 5)):
+            assert (live[:, a] <= live[:, b]).all(), (a, b)
+        assert (live[:, 7] >= 1).all() and (live[:, 6] >= 0).all() and (live[:, 6] < 256).all()
+        assert torch.equal(y, ref)            # the stamps do not change the result
+    finally:
+        dec.set_tuning("debug_timeline", 0)
+    with pytest.raises(Exception):
+        dec.debug_timeline()                  # off again: the call says so
