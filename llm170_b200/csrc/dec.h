@@ -57,7 +57,7 @@ struct Dec {
     // knobs
     int tune_gemv_stages = 4;
     int tune_gemv_warps = 8;
-    int tune_gemv_sk_stages = 6;   // most 16 KB ring stages of the persistent GEMV (2..6; fewer when x needs the room)
+    int tune_gemv_sk_stages = 4;   // most 16 KB ring stages of the persistent GEMV (2..6; fewer when x needs the room)
     int tune_gemv_sk_prefetch = 2; // ring stages the persistent GEMV requests before the previous kernel is complete
     int tune_gemv_persistent = 1;  // dense decode GEMV as two persistent CTAs per SM with equal unit ranges (gemv_sk.cu)
     int tune_gemv_cluster = 1;   // K splits of a row block as a thread-block cluster (DSMEM reduce) when 2 <= ksplit <= 8
