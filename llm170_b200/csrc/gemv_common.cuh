@@ -76,7 +76,7 @@ __device__ __forceinline__ void st_relaxed_sys_f32(float* p, float v) {
 // then polls its own receive area until the word of every peer has replaced the sentinel -- bounded -- adds the
 // ranks' values in rank order, writes the output and puts the sentinel back.  Every word says by itself whether
 // it has arrived, so the exchange needs no flag and, above all, no system-scope fence (measured here at 5 us
-// each with weight copies in flight).  No multicast, no second kernel, no NCCL call.  Two parities: a peer can
+// each with weight copies in flight).  Plain peer stores and local loads only, no second kernel, no NCCL call.  Two parities: a peer can
 // be at most one launch ahead, and then writes the other half.
 // The launch number advances when `done_target` row blocks of this launch have been exchanged.
 // `seq_smem`: this launch's exchange number in shared memory (thread 0 reads it from the device counter after the

@@ -67,7 +67,7 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                  : "memory");
 }
 
-// 2-D tiled TMA load (no multicast). c0 = innermost coordinate (elements), c1 = row.
+// 2-D tiled TMA load into this CTA only. c0 = innermost coordinate (elements), c1 = row.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
