@@ -115,17 +115,41 @@ moe_route_small_kernel(const float* __restrict__ lg, int* __restrict__ idx, floa
         }
     }
     __syncthreads();
+    // inclusive scan of (rows, tiles) over the 1024 experts slots: shuffles inside a warp, then the 32 warp totals
     const int c = s_rows[tid];
-    s_tiles[tid] = (c + bm - 1) / bm;
-    __syncthreads();
-    for (int d = 1; d < 1024; d <<= 1) {   // inclusive Hillis-Steele scan of both arrays
-        const int r = tid >= d ? s_rows[tid - d] : 0, tt = tid >= d ? s_tiles[tid - d] : 0;
-        __syncthreads();
-        s_rows[tid] += r;
-        s_tiles[tid] += tt;
-        __syncthreads();
+    const int ct = (c + bm - 1) / bm;
+    int vr = c, vt = ct;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int r = __shfl_up_sync(0xffffffffu, vr, d), tt = __shfl_up_sync(0xffffffffu, vt, d);
+        if (lane >= d) {
+            vr += r;
+            vt += tt;
+        }
     }
-    const int row0 = s_rows[tid] - c, tile0 = s_tiles[tid] - (c + bm - 1) / bm;
+    __syncthreads();          // every thread has read its s_rows entry
+    if (lane == 31) {
+        s_rows[w] = vr;       // warp totals reuse the first 32 entries
+        s_tiles[w] = vt;
+    }
+    __syncthreads();
+    if (w == 0) {
+        int tr = s_rows[lane], tl = s_tiles[lane];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int r = __shfl_up_sync(0xffffffffu, tr, d), tt = __shfl_up_sync(0xffffffffu, tl, d);
+            if (lane >= d) {
+                tr += r;
+                tl += tt;
+            }
+        }
+        s_rows[lane] = tr;    // inclusive totals of warps 0..lane
+        s_tiles[lane] = tl;
+    }
+    __syncthreads();
+    const int base_r = w > 0 ? s_rows[w - 1] : 0, base_t = w > 0 ? s_tiles[w - 1] : 0;
+    const int row0 = base_r + vr - c, tile0 = base_t + vt - ct;
+    const int total_rows = s_rows[31], total_tiles = s_tiles[31];
     s_off[tid] = row0;
     if (tid < n_exp) {
         off[tid] = row0;
@@ -136,8 +160,8 @@ moe_route_small_kernel(const float* __restrict__ lg, int* __restrict__ idx, floa
         tile_rows[i] = min(bm, c - r);
     }
     if (tid == 1023) {
-        *n_tiles = s_tiles[tid];
-        *n_rows = s_rows[tid];
+        *n_tiles = total_tiles;
+        *n_rows = total_rows;
     }
     __syncthreads();
     if (tid < ns) {
