@@ -71,10 +71,15 @@ W4A16_API int w4a16_debug_timeline(w4a16_dec* dec, long long* out, int max_slots
 /* Kernels launched by forward calls since creation: the launch counter the reference keeps in
  * HOST_LAUNCH_CALLS (crates/backend-gpu/src/rawcuda/ctx/mod.rs:10-11,311-315). */
 W4A16_API unsigned long long w4a16_launch_count(w4a16_dec* dec);
+/* Name of the kernel instantiation the last forward call on `dec` launched (e.g. "gemv_sk_kernel<128,true>"),
+ * for reports; the reference names its kernels by fatbin symbol
+ * (crates/backend-gpu/src/rawcuda/gptq4.rs:60-70). Valid until the next forward call. */
+W4A16_API const char* w4a16_last_kernel(w4a16_dec* dec);
 /* Kernel-selection knobs, the analogue of the reference's LLM170_* environment flags
  * (crates/diag/src/flag.rs:3-27). Keys: "gemv_persistent" (which form of the decode GEMV runs: 1 = default,
  * two persistent CTAs per SM with equal ranges of work for up to 4 tokens and the (row block, K split) grid
- * above that; 2 = always persistent; 0 = never), "gemv_sk_stages" (2..6) and "gemv_sk_prefetch" (0..6): ring
+ * above that; 2 = always persistent; 0 = never), "tp_wait_log2" (16..40, default 31: the fused all-reduce gives up
+ * on its peers after 2^n cycles), "gemv_sk_stages" (2..6) and "gemv_sk_prefetch" (0..6): ring
  * stages of the persistent form and how many of them are requested before the previous kernel of the stream is
  * complete; the remaining gemv_* keys tune the (row block, K split) form: "gemv_ksplit" (0 = automatic),
  * "gemv_stages" (16 KB weight stages in flight per CTA, 2..8), "gemv_warps" (consumer warps per CTA, 8 or 16), "gemv_cluster" (1 = default: 2..8 K splits of a row
@@ -167,12 +172,19 @@ W4A16_API int w4a16_tp_create(w4a16_dec* dec, int rank, int world, int max_rows,
 /* Maps the peers' exchange blocks: `handles` holds world x 64 bytes, the handles of all ranks in rank
  * order (exchanged by the host, e.g. over its process group). The reference has no such variant. */
 W4A16_API int w4a16_tp_connect(w4a16_dec* dec, const void* handles_world_x64);
+/* Puts this rank's exchange block back into its initial state (launch number 0, every word "not arrived") and
+ * clears the kernel status. To be called by EVERY rank after any rank saw a fused all-reduce give up
+ * (w4a16_kernel_status / w4a16_sync returned an error), between two host barriers: barrier, rearm, barrier.
+ * The ranks then agree on the launch number again and no stale word of the abandoned launch survives.
+ * The reference has no such variant. */
+W4A16_API int w4a16_tp_rearm(w4a16_dec* dec);
 /* Row-parallel decode GEMV with the all-reduce fused into the kernel: each rank holds a K slice of the
  * linear (whole scale groups), x16 is that slice of the activations, and out receives the SUM over ranks
  * of the partial products -- the kernel that reduces the split-K partials also pushes the local sums into
  * every peer's receive area with peer stores over NVLink, waits (bounded) until the peers' sums have arrived
- * in its own and adds them in rank order. After an abandoned launch, w4a16_kernel_status (which reports it on
- * every rank) re-arms the exchange block. Every rank must make the same sequence of these calls. Replaces sk_single_dev + an NCCL all-reduce for o_proj / down
+ * in its own and adds them in rank order. The wait is bounded (about a second, "tp_wait_log2"): ranks whose
+ * hosts drift further apart than that give up, w4a16_kernel_status reports it, and all ranks must then call
+ * w4a16_tp_rearm. Every rank must make the same sequence of these calls. Replaces sk_single_dev + an NCCL all-reduce for o_proj / down
  * (the reference runs them on one GPU: crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:89-127). */
 W4A16_API int w4a16_sk_single_allreduce(w4a16_dec* dec, const char* name, const void* x16_dev, void* out_dev, int t,
                                         int out_kind, void* stream);

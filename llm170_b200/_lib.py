@@ -25,6 +25,7 @@ _SIGS = {
     "w4a16_kernel_status": (_i, [_vp]),
     "w4a16_debug_timeline": (_i, [_vp, _vp, _i]),
     "w4a16_launch_count": (C.c_ulonglong, [_vp]),
+    "w4a16_last_kernel": (C.c_char_p, [_vp]),
     "w4a16_set_tuning": (_i, [_vp, C.c_char_p, _i]),
     "w4a16_check_shapes": (_i, [_sz] * 7),
     "w4a16_upload_lin_g": (_i, [_vp, C.c_char_p, _vp, _sz, _vp, _sz, _i, _i, _i, _i]),
@@ -39,6 +40,7 @@ _SIGS = {
     "w4a16_sk_single_static": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
     "w4a16_tp_create": (_i, [_vp, _i, _i, _i, _vp]),
     "w4a16_tp_connect": (_i, [_vp, _vp]),
+    "w4a16_tp_rearm": (_i, [_vp]),
     "w4a16_sk_single_allreduce": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
     "w4a16_sk_multi_dev": (_i, [_vp, C.POINTER(C.c_char_p), _i, _vp, C.POINTER(_vp), _i, _i, _vp]),
     "w4a16_lin_forward_host": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i]),

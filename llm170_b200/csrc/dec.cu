@@ -56,9 +56,11 @@ int Dec::ensure_scratch(size_t part_floats, int grid_x, cudaStream_t st) {
     if (e != cudaSuccess) {
         return cuda_fail("sync before scratch growth", e);
     }
+    // A graph instantiated earlier keeps the addresses of the blocks it was captured with, so a superseded
+    // block is only retired here (freed with the decoder), never freed while such a graph may still replay.
     if (part_floats > part_cap) {
         if (part) {
-            cudaFree(part);
+            retired.push_back(part);
             part = nullptr;
             part_cap = 0;
         }
@@ -70,7 +72,7 @@ int Dec::ensure_scratch(size_t part_floats, int grid_x, cudaStream_t st) {
     }
     if ((size_t)grid_x > counters_cap) {
         if (counters) {
-            cudaFree(counters);
+            retired.push_back(counters);
             counters = nullptr;
             counters_cap = 0;
         }
@@ -98,12 +100,16 @@ void Dec::free_lin(Lin& l) {
 
 int Dec::upload_common(const char* name, const void* q_dev, const void* s_dev, int n, int k, int group,
                        int scale_bf16) {
-    // q_dev/s_dev: boundary format already on the device
+    // q_dev/s_dev: boundary format already on the device.  Groups of 64 channels (accepted by the reference's loader,
+    // crates/core/src/w4a16.rs:225-234) are kept as two groups of 32 with the same scale: the dequantised weight
+    // (nibble-8)*scale is the same number, and the kernels need no third group size.
     Lin l;
     l.n = n;
     l.k = k;
-    l.group = group;
-    const size_t qb = (size_t)n * (size_t)(k / 2), sb = (size_t)n * (size_t)(k / group) * 2;
+    l.group_src = group;
+    l.group = group == 64 ? 32 : group;
+    const int src_div = group == 64 ? 2 : 1;
+    const size_t qb = (size_t)n * (size_t)(k / 2), sb = (size_t)n * (size_t)(k / l.group) * 2;
     cudaError_t e = cudaMalloc(&l.qt, qb);
     if (e != cudaSuccess) {
         return cuda_fail("alloc weights", e);
@@ -113,9 +119,39 @@ int Dec::upload_common(const char* name, const void* q_dev, const void* s_dev, i
         cudaFree(l.qt);
         return cuda_fail("alloc scales", e);
     }
+    // bf16 scales are stored as f16.  Every bf16 value between 2^-17 and 2^15 is an f16 value; a linear whose
+    // scales leave that window is shifted into it by a power of two that the kernels take out again at the end.
+    int shift = 0;
+    if (scale_bf16) {
+        const int preset[2] = {255, 0};
+        cudaMemcpyAsync(err_flag + 1, preset, sizeof(preset), cudaMemcpyHostToDevice, stream);
+        launch_scale_range((const uint16_t*)s_dev, (size_t)n * (size_t)(k / group), err_flag + 1, stream);
+        int range[2] = {255, 0};
+        e = cudaMemcpyAsync(range, err_flag + 1, sizeof(range), cudaMemcpyDeviceToHost, stream);
+        if (e == cudaSuccess) {
+            e = cudaStreamSynchronize(stream);
+        }
+        if (e != cudaSuccess) {
+            cudaFree(l.qt);
+            cudaFree(l.st);
+            return cuda_fail("scale range", e);
+        }
+        if (range[0] <= range[1]) {
+            // admissible shifts: the smallest scale stays an f16 value (2^-17 and up), and 8 times the largest one
+            // -- the largest dequantised weight the tensor-core GEMM forms in f16 -- stays finite (below 2^16)
+            const int lo = -17 - (range[0] - 127), hi = 12 - (range[1] - 127);
+            if (lo > hi) {
+                cudaFree(l.qt);
+                cudaFree(l.st);
+                return fail("w4a16 upload %s: bf16 scales span more than the 29 binades f16 weights can hold", name);
+            }
+            shift = lo > 0 ? lo : (hi < 0 ? hi : 0);
+        }
+    }
+    l.out_mul = ldexpf(1.0f, -shift);
     cudaMemsetAsync(err_flag, 0, sizeof(int), stream);
     launch_repack_q((const uint32_t*)q_dev, l.qt, n, k, stream);
-    launch_repack_s((const uint16_t*)s_dev, l.st, n, k, group, scale_bf16, err_flag, stream);
+    launch_repack_s((const uint16_t*)s_dev, l.st, n, k, l.group, src_div, scale_bf16, shift, err_flag, stream);
     int bad = 0;
     e = cudaMemcpyAsync(&bad, err_flag, sizeof(int), cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) {
@@ -127,7 +163,7 @@ int Dec::upload_common(const char* name, const void* q_dev, const void* s_dev, i
         if (e != cudaSuccess) {
             return cuda_fail("repack", e);
         }
-        return fail("w4a16 upload %s: a bf16 scale is not representable in f16", name);
+        return fail("w4a16 upload %s: a bf16 scale is not representable in f16 even after shifting", name);
     }
     l.bytes = qb + sb;
     auto it = lins.find(name);
@@ -137,6 +173,82 @@ int Dec::upload_common(const char* name, const void* q_dev, const void* s_dev, i
     }
     weights_bytes += l.bytes;
     lins[name] = l;
+    return 0;
+}
+
+// Which form of the decode GEMV serves a call, with its plan and the scratch it needs.  Shared by Dec::gemv and
+// the allocation-free entry point, so that both launch the same kernel with the same plan.
+int Dec::gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& c) {
+    const int t = a.m;
+    c = GemvChoice{};
+    c.grid_x = gemv_plan_ctas(a);   // 256-row blocks over all segments
+    a.subnormal = tune_gemv_subnormal;
+    a.status = gemm_status;
+    a.tp = TpComm{};
+    a.grouped = 0;
+    a.row_w = nullptr;
+    a.nrb_w = 0;
+    if (allreduce) {
+        if (tp.world < 2 || tp_peer[(tp.rank + 1) % tp.world] == nullptr) {
+            return fail("w4a16 allreduce gemv: call w4a16_tp_create and w4a16_tp_connect first");
+        }
+        if (a.nseg != 1 || a.seg[0].n > tp_max_rows || c.grid_x > TP_MAX_CTAS) {
+            return fail("w4a16 allreduce gemv: n=%d exceeds the exchange buffer (%d rows)", a.seg[0].n, tp_max_rows);
+        }
+        a.tp = tp;
+    }
+    c.sk = sk_make_plan(a.k, a.group, t, c.grid_x, sm_count, tune_gemv_sk_stages, tune_gemv_sk_prefetch);
+    // measured on B200: the persistent form wins up to 4 tokens; at 5..8 its single-CTA sum of a row block costs
+    // more than the cluster reduce of the (row block, K split) form
+    if (tune_gemv_persistent && c.sk.ctas > 0 && (t <= 4 || tune_gemv_persistent > 1)) {
+        c.form = GemvChoice::PERSISTENT;
+        c.part_floats = sk_part_floats(c.sk);
+        c.tickets = (size_t)c.grid_x;
+        a.ksplit = 1;
+        snprintf(c.name, sizeof(c.name), "gemv_sk_kernel<%d,%s>", a.group, a.subnormal ? "true" : "false");
+        return 0;
+    }
+    // with its own fixed scratch the call keeps the ticketed global reduce (that scratch is what it exists for)
+    const bool cluster_ok = tune_gemv_cluster && !allreduce && !own_scratch;
+    int ks = tune_gemv_ksplit > 0 ? tune_gemv_ksplit
+                                  : gemv_pick_ksplit(c.grid_x, a.k, a.group, t, sm_count,
+                                                     (tune_gemv_cluster && !allreduce) ? 8 : 16, tune_gemv_stages);
+    const int unit = a.group > TILE_K ? a.group : TILE_K;
+    if (ks > a.k / unit) {
+        ks = a.k / unit;
+    }
+    while (gemv_smem_bytes(a.k, a.group, t, ks, tune_gemv_stages) > 112 * 1024 && ks < a.k / unit) {
+        ++ks;
+    }
+    if (gemv_smem_bytes(a.k, a.group, t, ks, tune_gemv_stages) > 112 * 1024) {
+        return fail("w4a16 gemv: k=%d too large for t=%d", a.k, t);
+    }
+    a.ksplit = ks;
+    a.ring_stages = tune_gemv_stages;
+    a.cons_warps = tune_gemv_warps;
+    a.cluster = (cluster_ok && ks >= 2 && ks <= 8) ? 1 : 0;
+    c.form = GemvChoice::SPLIT;
+    c.part_floats = gemv_part_floats(c.grid_x, ks);
+    c.tickets = (size_t)c.grid_x;
+    snprintf(c.name, sizeof(c.name), "gemv_w4a16_kernel<%d,%s,%d>", a.group, a.subnormal ? "true" : "false", a.cons_warps);
+    return 0;
+}
+
+int Dec::gemv_run(GemvArgs& a, const GemvChoice& c, cudaStream_t st) {
+    cudaError_t e;
+    switch (c.form) {
+    case GemvChoice::PERSISTENT:
+        e = launch_gemv_sk(a, c.sk, st);
+        break;
+    default:
+        e = launch_gemv(a, c.grid_x, st);
+        break;
+    }
+    if (e != cudaSuccess) {
+        return cuda_fail("launch gemv", e);
+    }
+    last_kernel = c.name;
+    launches++;
     return 0;
 }
 
@@ -160,92 +272,33 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
         a.seg[i].st = (const uint32_t*)ls[i]->st;
         a.seg[i].out = outs[i];
         a.seg[i].n = ls[i]->n;
+        a.seg[i].out_mul = ls[i]->out_mul;
     }
     a.m = t;
     a.out_f16 = out_kind == W4A16_OUT_F16;
     a.x = (const uint16_t*)x;
-    const int grid_x = gemv_plan_ctas(a);   // 256-row blocks over all segments
     if (((uintptr_t)x & 15) != 0) {
         return fail("w4a16 gemv: x must be 16-byte aligned");
     }
-    const SkPlan sp = sk_make_plan(a.k, a.group, t, grid_x, sm_count, tune_gemv_sk_stages, tune_gemv_sk_prefetch);
-    // measured on B200: the persistent form wins up to 4 tokens; at 5..8 its single-CTA sum of a row block costs
-    // more than the cluster reduce of the (row block, K split) form
-    if (tune_gemv_persistent && sp.ctas > 0 && (t <= 4 || tune_gemv_persistent > 1)) {
-        a.ksplit = 1;
-        a.subnormal = tune_gemv_subnormal;
-        a.pdl = tune_pdl;
-        a.dbg = dbg_buf;
-        a.dbg_seq = (int)(launches % DBG_LAUNCHES);
-        a.status = gemm_status;
-        a.tp = TpComm{};
-        if (allreduce) {
-            if (tp.world < 2 || tp_peer[(tp.rank + 1) % tp.world] == nullptr) {
-                return fail("w4a16 allreduce gemv: call w4a16_tp_create and w4a16_tp_connect first");
-            }
-            if (nseg != 1 || ls[0]->n > tp_max_rows || grid_x > TP_MAX_CTAS) {
-                return fail("w4a16 allreduce gemv: n=%d exceeds the exchange buffer (%d rows)", ls[0]->n, tp_max_rows);
-            }
-            a.tp = tp;
+    for (int i = 0; i < nseg; ++i) {
+        // the kernels store four f32 or four f16 at a time
+        if (((uintptr_t)outs[i] & 15) != 0) {
+            return fail("w4a16 gemv: output %d must be 16-byte aligned", i);
         }
-        if (int rc = ensure_scratch(sk_part_floats(sp), grid_x, st)) {
-            return rc;
-        }
-        a.part = part;
-        a.counters = counters;
-        cudaError_t e = launch_gemv_sk(a, sp, st);
-        if (e != cudaSuccess) {
-            return cuda_fail("launch gemv", e);
-        }
-        launches++;
-        return 0;
     }
-    int ks = tune_gemv_ksplit > 0 ? tune_gemv_ksplit
-                                  : gemv_pick_ksplit(grid_x, a.k, a.group, t, sm_count,
-                                                     (tune_gemv_cluster && !allreduce) ? 8 : 16, tune_gemv_stages);
-    const int unit = a.group > TILE_K ? a.group : TILE_K;
-    if (ks > a.k / unit) {
-        ks = a.k / unit;
+    GemvChoice c;
+    if (int rc = gemv_select(a, allreduce, false, c)) {
+        return rc;
     }
-    while (gemv_smem_bytes(a.k, a.group, t, ks, tune_gemv_stages) > 112 * 1024 && ks < a.k / unit) {
-        ++ks;
+    if (int rc = ensure_scratch(c.part_floats, (int)c.tickets, st)) {
+        return rc;
     }
-    if (gemv_smem_bytes(a.k, a.group, t, ks, tune_gemv_stages) > 112 * 1024) {
-        return fail("w4a16 gemv: k=%d too large for t=%d", a.k, t);
-    }
-    a.ksplit = ks;
-    a.subnormal = tune_gemv_subnormal;
     a.pdl = tune_pdl;
     a.dbg = dbg_buf;
     a.dbg_seq = (int)(launches % DBG_LAUNCHES);
-    a.ring_stages = tune_gemv_stages;
-    a.cons_warps = tune_gemv_warps;
-    a.status = gemm_status;
-    a.cluster = (tune_gemv_cluster && ks >= 2 && ks <= 8 && !allreduce) ? 1 : 0;
-    a.grouped = 0;
-    a.row_w = nullptr;
-    a.nrb_w = 0;
-    a.tp = TpComm{};
-    if (allreduce) {
-        if (tp.world < 2 || tp_peer[(tp.rank + 1) % tp.world] == nullptr) {
-            return fail("w4a16 allreduce gemv: call w4a16_tp_create and w4a16_tp_connect first");
-        }
-        if (nseg != 1 || ls[0]->n > tp_max_rows || grid_x > TP_MAX_CTAS) {
-            return fail("w4a16 allreduce gemv: n=%d exceeds the exchange buffer (%d rows)", ls[0]->n, tp_max_rows);
-        }
-        a.tp = tp;
-    }
-    if (int rc = ensure_scratch(gemv_part_floats(grid_x, ks), grid_x, st)) {
-        return rc;
-    }
     a.part = part;
     a.counters = counters;
-    cudaError_t e = launch_gemv(a, grid_x, st);
-    if (e != cudaSuccess) {
-        return cuda_fail("launch gemv", e);
-    }
-    launches++;
-    return 0;
+    return gemv_run(a, c, st);
 }
 
 // Decode-time MoE: every <=8-row segment of an expert (device table from moe.cu) is one GEMV over that
@@ -266,6 +319,7 @@ int Dec::gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert,
     a.seg[0].st = (const uint32_t*)l->st;
     a.seg[0].out = out;
     a.seg[0].n = n_per_expert;
+    a.seg[0].out_mul = l->out_mul;
     a.m = GEMV_MAX_M;            // sizes the staging area; each segment brings its own row count
     a.out_f16 = 1;
     a.x = (const uint16_t*)xs;
@@ -365,7 +419,7 @@ int w4a16_dec_new(int device, w4a16_dec** out) {
     d.sm_count = prop.multiProcessorCount;
     e = cudaStreamCreateWithFlags(&d.stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) {
-        e = cudaMalloc(&d.err_flag, sizeof(int));
+        e = cudaMalloc(&d.err_flag, 4 * sizeof(int));
     }
     if (e == cudaSuccess) {
         e = cudaMalloc(&d.gemm_status, sizeof(int));
@@ -408,6 +462,10 @@ void w4a16_dec_free(w4a16_dec* dec) {
         d.free_lin(kv.second);
     }
     d.lins.clear();
+    for (void* p : d.retired) {
+        cudaFree(p);
+    }
+    d.retired.clear();
     if (d.part) {
         cudaFree(d.part);
     }
@@ -483,18 +541,18 @@ int w4a16_kernel_status(w4a16_dec* dec) {
         if (d.counters) {
             cudaMemset(d.counters, 0, d.counters_cap * sizeof(unsigned));
         }
-        if (d.tp_block) {
-            const size_t data = 2 * (size_t)d.tp.world * d.tp.area_floats * sizeof(float);
-            cudaMemset(d.tp_block, 0, TP_HEADER);
-            cudaMemset((char*)d.tp_block + TP_HEADER, 0xff, data);
-        }
-        return d.fail("w4a16: a bounded pipeline wait expired (role %d, step %d); results are invalid", st >> 16,
-                      st & 0xFFFF);
+        // the exchange block of the fused all-reduce is NOT re-armed here: the peers may still be pushing into
+        // it, and all ranks must restart from the same launch number (w4a16_tp_rearm, between two host barriers)
+        return d.fail("w4a16: a bounded pipeline wait expired (role %d, step %d); results are invalid%s", st >> 16,
+                      st & 0xFFFF,
+                      d.tp_block ? "; call w4a16_tp_rearm on every rank before the next fused all-reduce" : "");
     }
     return 0;
 }
 
 unsigned long long w4a16_launch_count(w4a16_dec* dec) { return dec->d.launches; }
+
+const char* w4a16_last_kernel(w4a16_dec* dec) { return dec->d.last_kernel.c_str(); }
 
 int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
     Dec& d = dec->d;
@@ -562,6 +620,14 @@ int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
         d.tune_pdl = value;
         return 0;
     }
+    if (!strcmp(key, "tp_wait_log2")) {
+        if (value < 16 || value > 40) {
+            return d.fail("w4a16 tuning: tp_wait_log2 must be 16..40");
+        }
+        d.tune_tp_wait_log2 = value;
+        d.tp.wait_cycles = 1ll << value;
+        return 0;
+    }
     if (!strcmp(key, "gemv_subnormal")) {
         d.tune_gemv_subnormal = value != 0;
         return 0;
@@ -579,7 +645,7 @@ int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
 int w4a16_check_shapes(size_t t, size_t qlen, size_t slen, size_t xlen, size_t n, size_t k, size_t group) {
     // crates/backend-gpu/src/rawcuda/gptq4.rs:31-48. The reference's extra t==1 limit
     // (k <= group*256, its GEMV keeps scales in shared memory, :51-56) does not apply here.
-    if ((group != 128 && group != 32) || k % group != 0 || t == 0 || qlen != n * (k / 8) ||
+    if ((group != 128 && group != 64 && group != 32) || k % group != 0 || t == 0 || qlen != n * (k / 8) ||
         slen != n * (k / group) || xlen != t * k) {
         return 1;
     }
@@ -590,7 +656,7 @@ static int validate_upload(Dec& d, const char* name, size_t q_bytes, size_t s_by
     if (!name || !*name) {
         return d.fail("w4a16 upload: empty name");
     }
-    if (n <= 0 || k <= 0 || (group != 128 && group != 32) || k % group != 0) {
+    if (n <= 0 || k <= 0 || (group != 128 && group != 64 && group != 32) || k % group != 0) {
         return d.fail("w4a16 upload %s: unsupported n=%d k=%d group=%d", name, n, k, group);
     }
     if (q_bytes != (size_t)n * (size_t)(k / 2) || s_bytes != (size_t)n * (size_t)(k / group) * 2) {
@@ -644,7 +710,7 @@ int w4a16_upload_lin_g_dev(w4a16_dec* dec, const char* name, const void* q_dev, 
         return d.fail("w4a16 upload: bad shape");
     }
     if (int rc = validate_upload(d, name, (size_t)n * (size_t)(k / 2),
-                                 (group == 128 || group == 32) && k % group == 0
+                                 (group == 128 || group == 64 || group == 32) && k % group == 0
                                      ? (size_t)n * (size_t)(k / group) * 2
                                      : 0,
                                  n, k, group)) {
@@ -671,7 +737,7 @@ int w4a16_lin_spec(w4a16_dec* dec, const char* name, int* n, int* k, int* group)
     }
     if (n) *n = l->n;
     if (k) *k = l->k;
-    if (group) *group = l->group;
+    if (group) *group = l->group_src;
     return 0;
 }
 
@@ -696,9 +762,12 @@ int w4a16_unpack_lin(w4a16_dec* dec, const char* name, void* q_dev, void* s_dev,
     if (!l) {
         return 1;
     }
+    if (l->out_mul != 1.0f) {
+        return d.fail("w4a16 unpack %s: its bf16 scales are not f16 values (use w4a16_dequant_lin)", name);
+    }
     cudaStream_t st = pick_stream(dec, stream);
     w4::launch_unpack_q(l->qt, (uint32_t*)q_dev, l->n, l->k, st);
-    w4::launch_unpack_s(l->st, (uint16_t*)s_dev, l->n, l->k, l->group, st);
+    w4::launch_unpack_s(l->st, (uint16_t*)s_dev, l->n, l->k, l->group, l->group_src == 64 ? 2 : 1, st);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : d.cuda_fail("unpack", e);
 }
@@ -709,7 +778,7 @@ int w4a16_dequant_lin(w4a16_dec* dec, const char* name, void* out_dev, int out_k
     if (!l) {
         return 1;
     }
-    w4::launch_dequant(l->qt, l->st, out_dev, l->n, l->k, l->group, out_kind == W4A16_OUT_F16,
+    w4::launch_dequant(l->qt, l->st, out_dev, l->n, l->k, l->group, out_kind == W4A16_OUT_F16, l->out_mul,
                        pick_stream(dec, stream));
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : d.cuda_fail("dequant", e);
@@ -761,6 +830,7 @@ int w4a16_tp_create(w4a16_dec* dec, int rank, int world, int max_rows, void* han
     d.tp.world = world;
     d.tp.area_floats = (int)area;
     d.tp.max_rows = max_rows;
+    d.tp.wait_cycles = 1ll << d.tune_tp_wait_log2;
     d.tp_max_rows = max_rows;
     d.tp_peer[rank] = d.tp_block;
     return 0;
@@ -789,6 +859,22 @@ int w4a16_tp_connect(w4a16_dec* dec, const void* handles_world_x64) {
     d.tp.seq = local;
     d.tp.done = local + 1;
     return 0;
+}
+
+int w4a16_tp_rearm(w4a16_dec* dec) {
+    Dec& d = dec->d;
+    if (!d.tp_block) {
+        return d.fail("w4a16 tp_rearm: call w4a16_tp_create first");
+    }
+    cudaSetDevice(d.device);
+    cudaError_t e = cudaDeviceSynchronize();
+    const size_t data = 2 * (size_t)d.tp.world * d.tp.area_floats * sizeof(float);
+    if (e == cudaSuccess) e = cudaMemset(d.tp_block, 0, TP_HEADER);                      // launch number and done count
+    if (e == cudaSuccess) e = cudaMemset((char*)d.tp_block + TP_HEADER, 0xff, data);     // every word: not arrived
+    if (e == cudaSuccess && d.counters) e = cudaMemset(d.counters, 0, d.counters_cap * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(d.gemm_status, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    return e == cudaSuccess ? 0 : d.cuda_fail("tp_rearm", e);
 }
 
 int w4a16_sk_single_allreduce(w4a16_dec* dec, const char* name, const void* x16_dev, void* out_dev, int t,
@@ -881,7 +967,7 @@ int w4a16_lin_forward_host(w4a16_dec* dec, const char* name, const void* x16_hos
 int w4a16_gptq4_gemm(w4a16_dec* dec, const void* x16_host, int t, const void* q_host, const void* s_host,
                      int n, int k, int group, int scale_bf16, float* out_host) {
     Dec& d = dec->d;
-    if (n <= 0 || k <= 0 || t <= 0 || (group != 128 && group != 32) || k % group != 0) {
+    if (n <= 0 || k <= 0 || t <= 0 || (group != 128 && group != 64 && group != 32) || k % group != 0) {
         return d.fail("gptq4: shape contract violated n=%d k=%d t=%d group=%d", n, k, t, group);
     }
     static const char* TMP = "\x01gptq4.tmp";

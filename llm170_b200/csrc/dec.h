@@ -2,6 +2,7 @@
 #pragma once
 #include <map>
 #include <string>
+#include <vector>
 
 #include "internal.h"
 
@@ -12,7 +13,9 @@ constexpr int DBG_SLOTS = DBG_LAUNCHES * DBG_CTAS * DBG_STAMPS;
 struct Lin {
     uint32_t* qt = nullptr;  // T64 tiles (layout.cuh)
     uint16_t* st = nullptr;  // tiled f16 scale pairs
-    int n = 0, k = 0, group = 0;
+    int n = 0, k = 0, group = 0;   // group: of the resident scale tiles (128 or 32)
+    int group_src = 0;             // group of the uploaded scales (64 is stored as two groups of 32)
+    float out_mul = 1.0f;          // 2^-shift when bf16 scales had to be shifted into the f16 range (else 1)
     size_t bytes = 0;
 };
 
@@ -36,6 +39,16 @@ struct MoeBufs {
     int max_tiles = 0;
 };
 
+// The form of the decode GEMV chosen for a call (Dec::gemv_select).
+struct GemvChoice {
+    enum Form { PERSISTENT, SPLIT } form = SPLIT;
+    SkPlan sk{};
+    int grid_x = 0;            // 256-row blocks over all segments
+    size_t part_floats = 0;    // partial-sum scratch the launch needs
+    size_t tickets = 0;        // arrival tickets the launch needs
+    char name[64] = {0};       // the kernel instantiation, for reports
+};
+
 struct Dec {
     int device = 0;
     int sm_count = 148;
@@ -47,7 +60,8 @@ struct Dec {
     size_t part_cap = 0;
     unsigned* counters = nullptr;
     size_t counters_cap = 0;
-    int* err_flag = nullptr;
+    std::vector<void*> retired;   // scratch blocks superseded by larger ones: freed with the decoder (graphs may hold them)
+    int* err_flag = nullptr;       // device int[4]: repack error flag, bf16 exponent range (min, max)
     int* gemm_status = nullptr;  // device word: first bounded wait that expired in any kernel (0 = none)
     // device staging for the host-buffer entry points
     void* xh = nullptr;
@@ -63,6 +77,7 @@ struct Dec {
     int tune_gemv_cluster = 1;   // K splits of a row block as a thread-block cluster (DSMEM reduce) when 2 <= ksplit <= 8
     int tune_gemv_subnormal = 1;
     int tune_pdl = 1;
+    int tune_tp_wait_log2 = 31;  // the fused all-reduce gives up on its peers after 2^this cycles
     int tune_gemm_mt = 0;        // 128-token blocks per GEMM tile: 0 = automatic, 1 or 2
     long long* dbg_buf = nullptr;  // device timeline buffer (DBG_SLOTS entries) when the knob is on
     int tune_gemv_ksplit = 0;
@@ -77,6 +92,9 @@ struct Dec {
     void free_lin(Lin& l);
     int upload_common(const char* name, const void* q_dev, const void* s_dev, int n, int k, int group,
                       int scale_bf16);
+    std::string last_kernel;   // instantiation launched by the last forward call
+    int gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& c);
+    int gemv_run(GemvArgs& a, const GemvChoice& c, cudaStream_t st);
     int gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, int t, int out_kind,
              cudaStream_t st, bool allreduce = false);
     int gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaStream_t st);
@@ -93,7 +111,7 @@ struct Dec {
     MoeCfg moe;
     MoeBufs mb;
     int ensure_moe(int t, cudaStream_t st);
-    void free_moe();
+    void free_moe(bool retire = false);
     int moe_ffn(int layer, const float* logits, const void* x16, void* y, int t, int out_kind, cudaStream_t st);
 };
 

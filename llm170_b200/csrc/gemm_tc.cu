@@ -27,6 +27,10 @@
 
 namespace w4 {
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
 namespace {
 
 constexpr int BM = 128;           // tokens per tile (UMMA M)
@@ -64,6 +68,7 @@ struct GemmArgs {
     const int* num_tiles;
     int expert0;          // first expert held by this decoder
     const float* row_w;   // optional per-row factor applied in the epilogue (routing weight)
+    float out_mul;        // power of two applied to every sum (undoes the shift of bf16 scales; normally 1)
     int* status;  // 0 = ok; otherwise code<<16 | detail of the first wait that expired
     long long* dbg;  // optional timeline buffer (diagnostic), CTA 0 only
 };
@@ -344,10 +349,16 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                     uint32_t v[32];
                     tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * 256 + c0), v);
                     if (row_l < rows_valid) {
+                        if (a.out_mul != 1.0f) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                v[i] = __float_as_uint(__uint_as_float(v[i]) * a.out_mul);
+                            }
+                        }
                         if (a.row_w != nullptr) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
-                                v[i] = __float_as_uint(__uint_as_float(v[i]) * rw);
+                                v[i] = __float_as_uint(mul_row_w(__uint_as_float(v[i]), rw));
                             }
                         }
                         if (a.out_f16) {
@@ -392,10 +403,6 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
 }
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn encode_fn() {
     static EncodeTiledFn fn = nullptr;
@@ -463,6 +470,7 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.tile_expert = a.tile_row0 = a.tile_rows = a.num_tiles = nullptr;
     a.expert0 = 0;
     a.row_w = nullptr;
+    a.out_mul = l->out_mul;
     a.status = gemm_status;
     a.dbg = dbg_buf;
     const int grid = a.m_tiles * a.n_tiles;
@@ -524,6 +532,7 @@ int Dec::gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int 
     a.num_tiles = b.n_tiles;
     a.expert0 = moe.e0;
     a.row_w = row_w;
+    a.out_mul = l->out_mul;
     a.status = gemm_status;
     a.dbg = nullptr;
     const int grid = a.m_tiles * a.n_tiles;

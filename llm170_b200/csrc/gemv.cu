@@ -469,13 +469,15 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                 }
             }
         }
-        if (SUBN) {
+        {
+            // the powers of two of the subnormal operands, and of shifted bf16 scales (1 for f16 scales)
+            const float m_lo = (SUBN ? 16777216.f : 1.f) * sg.out_mul, m_hi = (SUBN ? 1048576.f : 1.f) * sg.out_mul;
 #pragma unroll
             for (int r = 0; r < RB_PER_WARP; ++r) {
-                tot[r][0] *= 16777216.f;
-                tot[r][1] *= 16777216.f;
-                tot[r][2] *= 1048576.f;
-                tot[r][3] *= 1048576.f;
+                tot[r][0] *= m_lo;
+                tot[r][1] *= m_lo;
+                tot[r][2] *= m_hi;
+                tot[r][3] *= m_hi;
             }
         }
     } else if (!is_producer && ok) {
@@ -518,8 +520,8 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                     if (tok < m_loc) {
                         if (a.row_w != nullptr) {
                             const float rw = a.row_w[row_base + tok];
-                            tot[r][j] *= rw;
-                            tot[r][2 + j] *= rw;
+                            tot[r][j] = mul_row_w(tot[r][j], rw);
+                            tot[r][2 + j] = mul_row_w(tot[r][2 + j], rw);
                         }
                         if (tp_on) {
                             float* o = tp_own_area(a.tp, s_seq);
@@ -583,7 +585,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
             }
             const int row = rb_cta0 * TILE_ROWS + lr;
             if (a.row_w != nullptr) {
-                sum *= a.row_w[row_base + tok];
+                sum = mul_row_w(sum, a.row_w[row_base + tok]);
             }
             if (a.out_f16) {
                 reinterpret_cast<__half*>(sg.out)[(size_t)tok * sg.n + row] = __float2half_rn(sum);
@@ -641,7 +643,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
                 if (tok < m_loc) {
                     float v = j ? sum.y : sum.x;
                     if (a.row_w != nullptr) {
-                        v *= a.row_w[row_base + tok];
+                        v = mul_row_w(v, a.row_w[row_base + tok]);
                     }
                     if (tp_on) {
                         tp_own_area(a.tp, s_seq)[(size_t)tok * a.tp.max_rows + row] = v;

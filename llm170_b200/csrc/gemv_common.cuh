@@ -127,7 +127,7 @@ __device__ __forceinline__ void tp_exchange(const GemvArgs& a, const GemvSeg& sg
             for (int p = 0; p < TP_MAX_WORLD; ++p) {
                 all = all && (p >= tp.world || p == tp.rank || __float_as_uint(pv[p]) != 0xffffffffu);
             }
-            if (!all && (*abort_flag || clock64() - t0 > (1ll << 31))) {
+            if (!all && (*abort_flag || clock64() - t0 > tp.wait_cycles)) {
                 *abort_flag = 1;
                 atomicCAS(a.status, 0, (20 << 16) | (rb_cta0 & 0xffff));   // a peer never delivered this row block
                 break;
@@ -138,7 +138,9 @@ __device__ __forceinline__ void tp_exchange(const GemvArgs& a, const GemvSeg& sg
         for (int p = 0; p < TP_MAX_WORLD; ++p) {
             if (p < tp.world) {
                 v += pv[p];   // rank order; the own slot holds this rank's sums
-                if (p != tp.rank) {
+                // a word that never arrived is left alone: its sentinel is still in place, and writing it again
+                // could erase the peer's late store, which would then be missing for good
+                if (p != tp.rank && __float_as_uint(pv[p]) != 0xffffffffu) {
                     recv[(size_t)p * tp.area_floats + off] = __uint_as_float(0xffffffffu);
                 }
             }

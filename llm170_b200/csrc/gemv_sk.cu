@@ -480,13 +480,15 @@ gemv_sk_kernel(const GemvArgs a, const SkPlan p) {
         bool first_seg = true;
         // end of a segment: the sums of a whole row block go to the output, those of a part of one are parked
         auto flush = [&](int c_end) {
-            if (SUBN) {
+            {
+                // the powers of two of the subnormal operands, and of shifted bf16 scales (1 for f16 scales)
+                const float m_lo = (SUBN ? 16777216.f : 1.f) * cq.sg.out_mul, m_hi = (SUBN ? 1048576.f : 1.f) * cq.sg.out_mul;
 #pragma unroll
                 for (int r = 0; r < RBW; ++r) {
-                    tot[r][0] *= 16777216.f;
-                    tot[r][1] *= 16777216.f;
-                    tot[r][2] *= 1048576.f;
-                    tot[r][3] *= 1048576.f;
+                    tot[r][0] *= m_lo;
+                    tot[r][1] *= m_lo;
+                    tot[r][2] *= m_hi;
+                    tot[r][3] *= m_hi;
                 }
             }
             const bool whole = seg_c_begin == 0 && c_end == C;

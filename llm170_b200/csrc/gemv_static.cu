@@ -60,8 +60,8 @@ extern "C" int w4a16_sk_single_static(w4a16_dec* dec, const char* name, const vo
     if (t < 1 || t > GEMV_MAX_M) {
         return d.fail("w4a16 sk_single_static: t=%d outside 1..%d", t, GEMV_MAX_M);
     }
-    if (((uintptr_t)x16_dev & 15) != 0) {
-        return d.fail("w4a16 sk_single_static: x must be 16-byte aligned");
+    if (((uintptr_t)x16_dev & 15) != 0 || ((uintptr_t)out_dev & 15) != 0) {
+        return d.fail("w4a16 sk_single_static: x and out must be 16-byte aligned");
     }
     int cur = -1;
     cudaError_t e = cudaGetDevice(&cur);
@@ -82,81 +82,31 @@ extern "C" int w4a16_sk_single_static(w4a16_dec* dec, const char* name, const vo
     a.seg[0].st = (const uint32_t*)l.st;
     a.seg[0].out = out_dev;
     a.seg[0].n = l.n;
+    a.seg[0].out_mul = l.out_mul;
     a.m = t;
     a.out_f16 = out_kind == W4A16_OUT_F16;
     a.x = (const uint16_t*)x16_dev;
-    const int grid_x = gemv_plan_ctas(a);   // 256-row blocks
     cudaStream_t st = stream ? (cudaStream_t)stream : d.stream;
-    const SkPlan sp = sk_make_plan(a.k, a.group, t, grid_x, d.sm_count, d.tune_gemv_sk_stages, d.tune_gemv_sk_prefetch);
-    if (d.tune_gemv_persistent && sp.ctas > 0 && (t <= 4 || d.tune_gemv_persistent > 1)) {
-        // the same kernel and plan as w4a16_sk_single_dev, so the two give identical results
-        const size_t need = sk_part_floats(sp) * sizeof(float);
-        if (need > STATIC_PART_BYTES || (size_t)grid_x > STATIC_TICKETS) {
-            return d.fail("w4a16 sk_single_static: %s needs %zu bytes of partial-sum scratch and %d tickets; the "
-                          "built-in array holds %zu bytes and %zu tickets (use w4a16_sk_single_dev)",
-                          name, need, grid_x, STATIC_PART_BYTES, STATIC_TICKETS);
-        }
-        a.ksplit = 1;
-        a.subnormal = d.tune_gemv_subnormal;
-        a.pdl = 0;  // ordinary launch: the shared array must not be touched while an earlier kernel still runs
-        a.tp = TpComm{};
-        a.status = d.gemm_status;
-        a.dbg = nullptr;
-        a.counters = reinterpret_cast<unsigned*>(base);
-        a.part = reinterpret_cast<float*>(base + STATIC_TICKETS * sizeof(unsigned));
-        // tickets must start at zero; the previous call may have been abandoned half-way
-        e = cudaMemsetAsync(a.counters, 0, (size_t)grid_x * sizeof(unsigned), st);
-        if (e == cudaSuccess) {
-            e = launch_gemv_sk(a, sp, st);
-        }
-        if (e != cudaSuccess) {
-            return d.cuda_fail("launch gemv (static scratch)", e);
-        }
-        d.launches++;
-        return 0;
+    // the same kernel form and plan as w4a16_sk_single_dev (shared selection), so the two give identical results
+    GemvChoice c;
+    if (int rc = d.gemv_select(a, false, true, c)) {
+        return rc;
     }
-    int ks = d.tune_gemv_ksplit > 0
-                 ? d.tune_gemv_ksplit
-                 : gemv_pick_ksplit(grid_x, a.k, a.group, t, d.sm_count, d.tune_gemv_cluster ? 8 : 16, d.tune_gemv_stages);
-    const int unit = a.group > TILE_K ? a.group : TILE_K;
-    if (ks > a.k / unit) {
-        ks = a.k / unit;
+    const size_t need = c.part_floats * sizeof(float);
+    if (need > STATIC_PART_BYTES || c.tickets > STATIC_TICKETS) {
+        return d.fail("w4a16 sk_single_static: %s needs %zu bytes of partial-sum scratch and %zu tickets; the built-in "
+                      "array holds %zu bytes and %zu tickets (use w4a16_sk_single_dev)",
+                      name, need, c.tickets, STATIC_PART_BYTES, STATIC_TICKETS);
     }
-    while (gemv_smem_bytes(a.k, a.group, t, ks, d.tune_gemv_stages) > 112 * 1024 && ks < a.k / unit) {
-        ++ks;
-    }
-    if (gemv_smem_bytes(a.k, a.group, t, ks, d.tune_gemv_stages) > 112 * 1024) {
-        return d.fail("w4a16 sk_single_static: k=%d too large for t=%d", a.k, t);
-    }
-    const size_t need = gemv_part_floats(grid_x, ks) * sizeof(float);
-    if (need > STATIC_PART_BYTES || (size_t)grid_x > STATIC_TICKETS) {
-        return d.fail("w4a16 sk_single_static: %s needs %zu bytes of split-K scratch and %d tickets; the built-in "
-                      "array holds %zu bytes and %zu tickets (use w4a16_sk_single_dev, or fewer K splits)",
-                      name, need, grid_x, STATIC_PART_BYTES, STATIC_TICKETS);
-    }
-    a.ksplit = ks;
-    a.subnormal = d.tune_gemv_subnormal;
     a.pdl = 0;  // ordinary launch: the shared array must not be touched while an earlier kernel still runs
-    a.ring_stages = d.tune_gemv_stages;
-    a.cons_warps = d.tune_gemv_warps;
-    a.cluster = 0;  // this entry point exists for its global scratch; keep the ticketed reduce
-    a.grouped = 0;
-    a.row_w = nullptr;
-    a.nrb_w = 0;
-    a.tp = TpComm{};
-    a.status = d.gemm_status;
     a.dbg = nullptr;
     a.dbg_seq = 0;
     a.counters = reinterpret_cast<unsigned*>(base);
     a.part = reinterpret_cast<float*>(base + STATIC_TICKETS * sizeof(unsigned));
     // tickets must start at zero; the previous call may have been abandoned half-way
-    e = cudaMemsetAsync(a.counters, 0, (size_t)grid_x * sizeof(unsigned), st);
-    if (e == cudaSuccess) {
-        e = launch_gemv(a, grid_x, st);
-    }
+    e = cudaMemsetAsync(a.counters, 0, c.tickets * sizeof(unsigned), st);
     if (e != cudaSuccess) {
-        return d.cuda_fail("launch gemv (static scratch)", e);
+        return d.cuda_fail("clear tickets (static scratch)", e);
     }
-    d.launches++;
-    return 0;
+    return d.gemv_run(a, c, st);
 }

@@ -10,14 +10,19 @@ namespace w4 {
 
 // ---- repack.cu -------------------------------------------------------------------------------
 void launch_repack_q(const uint32_t* q_orig, uint32_t* qt, int n, int k, cudaStream_t st);
-// err_flag (device int, may be null) is set to 1 if a bf16 scale is not exactly an f16 value.
-void launch_repack_s(const uint16_t* s_orig, uint16_t* stl, int n, int k, int group, int scale_bf16,
-                     int* err_flag, cudaStream_t st);
+// Biased-exponent range of the non-zero bf16 scales: range2[0] = min (preset 255), range2[1] = max (preset 0).
+void launch_scale_range(const uint16_t* s_orig, size_t total, int* range2, cudaStream_t st);
+// `group` is the group size of the TILED array; a source group covers `src_div` tiled groups.  bf16 scales are
+// multiplied by 2^shift and stored as f16; err_flag (device int, may be null) is set to 1 if one of them is not
+// exactly representable.
+void launch_repack_s(const uint16_t* s_orig, uint16_t* stl, int n, int k, int group, int src_div, int scale_bf16,
+                     int shift, int* err_flag, cudaStream_t st);
 void launch_unpack_q(const uint32_t* qt, uint32_t* q_orig, int n, int k, cudaStream_t st);
-void launch_unpack_s(const uint16_t* stl, uint16_t* s_orig, int n, int k, int group, cudaStream_t st);
-// out: f32 [n][k] (out_f16 == 0) or f16 [n][k] (out_f16 == 1, round-to-nearest-even of the f32 value)
+void launch_unpack_s(const uint16_t* stl, uint16_t* s_orig, int n, int k, int group, int src_div, cudaStream_t st);
+// out: f32 [n][k] (out_f16 == 0) or f16 [n][k] (out_f16 == 1, round-to-nearest-even of the f32 value);
+// out_mul: the power of two that undoes the shift of bf16 scales (1 otherwise)
 void launch_dequant(const uint32_t* qt, const uint16_t* stl, void* out, int n, int k, int group,
-                    int out_f16, cudaStream_t st);
+                    int out_f16, float out_mul, cudaStream_t st);
 
 // ---- gemv.cu ---------------------------------------------------------------------------------
 constexpr int GEMV_MAX_SEG = 4;
@@ -36,6 +41,7 @@ struct TpComm {
     float* buf[TP_MAX_WORLD];         // rank p's receive areas: [2 parities][world sources][8][max_rows] f32
     unsigned* seq;                    // local: number of fused launches completed
     unsigned* done;                   // local: row blocks that finished the current launch's exchange
+    long long wait_cycles;            // limit of the wait for the peers' words (2^31 cycles, about a second, by default)
 };
 
 constexpr int DBG_LAUNCHES = 64;   // launches kept by the diagnostic timeline (slot = launch number mod 64)
@@ -48,6 +54,7 @@ struct GemvSeg {
     void* out;           // [m][n] f32 or f16
     int n;               // rows of this segment
     int cta0;            // first grid.x index of this segment
+    float out_mul;       // power of two applied to the sums (undoes the shift of bf16 scales; normally 1)
 };
 
 struct GemvArgs {

@@ -7,7 +7,8 @@
 // device copy in a different tiling chosen for B200:
 //
 //   qt : u32 [K/64][N/16][32 lanes][4 words]            (512 B per 16-row x 64-k tile, k-block major)
-//   st : f16 [N/16][K/group][8][2]                      (pair j = scales of rows j and j+8)
+//   st : f16 [N/16][K/group][8][2]                      (pair j = scales of rows j and j+8; group 128 or 32 --
+//                                                        64-channel groups are stored as two groups of 32)
 //
 // Inside a tile, lane = 4*g + t (g = 0..7, t = 0..3) and word w = 2*p + h (p, h in {0,1}) hold
 // rows r0 = 16*rb + g and r1 = r0 + 8 at k = 64*kb + 32*p + 8*t + 4*h + {0,1,2,3}:
@@ -36,7 +37,7 @@ constexpr int TILE_WORDS = 128;  // u32 per tile
 // Shape contract of the tiled layout (the reference's Marlin path requires k%128==0 && n%64==0,
 // crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/marlin.rs:110; this layout is less strict).
 __host__ __device__ inline bool shape_ok(int n, int k, int group) {
-    return n > 0 && k > 0 && (group == 128 || group == 32) && n % TILE_ROWS == 0 &&
+    return n > 0 && k > 0 && (group == 128 || group == 64 || group == 32) && n % TILE_ROWS == 0 &&
            k % TILE_K == 0 && k % group == 0;
 }
 

@@ -21,9 +21,14 @@ namespace {
 
 constexpr int TOPK_WARPS = 8;
 
-// One warp per token. p_e = exp(l_e - max); pick k times the largest remaining p (ties: lower index);
-// weights = p / sum of the picked p. Same selection rule as select_topk
-// (crates/core/src/qwen35/stages/moe.rs:8-31), which divides by the full softmax sum first; that factor cancels.
+// One warp per token, experts dealt to lanes round-robin (expert e lives in lane e % 32, slot e / 32).
+// Same arithmetic as select_topk / moe_topk of the reference (crates/core/src/qwen35/stages/moe.rs:8-31,
+// crates/backend-gpu/src/rawcuda/w4a16_dec/mod.rs:168-185), in the same order: p_e = exp(l_e - max) / sum with the
+// sum taken sequentially over e = 0..n-1, pick k times the largest remaining p (ties: lower index), weights =
+// p / (sum of the picked p, added in pick order).  Ordering on the normalised p, not on the numerators, matters
+// when two different numerators round to the same p.  exp is evaluated in double and rounded once, the closest
+// a device routine gets to the host's expf.  A pick is two warp-wide integer reductions: positive floats order
+// like their bit patterns, so the largest p is a max over u32 and the tie-break a min over the indices that hold it.
 __device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* __restrict__ idx, float* __restrict__ wt,
                                               int n, int k, int lane) {
     float mx = -INFINITY;
@@ -37,36 +42,46 @@ __device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* 
     float pv[32];
     int cnt = 0;
     for (int i = lane; i < n; i += 32) {
-        pv[cnt++] = expf(l[i] - mx);
+        pv[cnt++] = (float)exp((double)(l[i] - mx));
+    }
+    // sum in index order, the same on every lane: element e = 32*j + src comes from lane src, slot j
+    float sum = 0.f;
+    const int slots = (n + 31) >> 5;
+    for (int j = 0; j < slots; ++j) {
+        const float mine_j = j < cnt ? pv[j] : 0.f;
+        const int live = min(32, n - 32 * j);
+        for (int src = 0; src < live; ++src) {
+            sum += __shfl_sync(0xffffffffu, mine_j, src);
+        }
+    }
+    for (int j = 0; j < cnt; ++j) {
+        pv[j] = pv[j] / sum;
     }
     unsigned used = 0u;
     float wsum = 0.f;
-    float mine = 0.f;  // lane r keeps the r-th picked weight
+    float mine = 0.f;  // lane r keeps the r-th picked p
     for (int r = 0; r < k; ++r) {
-        float bv = -INFINITY;
-        int bi = 0x7fffffff;
+        unsigned best = 0u;   // bit pattern of the lane's largest remaining p (p >= 0: patterns order like values)
         for (int j = 0; j < cnt; ++j) {
-            const int e = lane + 32 * j;
-            if (!(used & (1u << j)) && (pv[j] > bv || (pv[j] == bv && e < bi))) {
-                bv = pv[j];
-                bi = e;
+            if (!(used & (1u << j))) {
+                best = max(best, __float_as_uint(pv[j]));
             }
         }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-            if (ov > bv || (ov == bv && oi < bi)) {
-                bv = ov;
-                bi = oi;
+        const unsigned top = __reduce_max_sync(0xffffffffu, best);
+        unsigned cand = 0xffffffffu;   // lowest index on this lane that holds `top`
+        for (int j = cnt - 1; j >= 0; --j) {
+            if (!(used & (1u << j)) && __float_as_uint(pv[j]) == top) {
+                cand = (unsigned)(lane + 32 * j);
             }
         }
+        const int bi = (int)__reduce_min_sync(0xffffffffu, cand);
         if ((bi & 31) == lane) {
             used |= 1u << (bi >> 5);
         }
         if (lane == 0) {
             idx[r] = bi;
         }
+        const float bv = __uint_as_float(top);
         if (lane == (r & 31)) {
             mine = bv;
         }

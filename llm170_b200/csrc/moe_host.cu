@@ -22,12 +22,17 @@ cudaError_t dalloc(T** p, size_t count) {
 }
 }  // namespace
 
-void Dec::free_moe() {
+// `retire`: keep the blocks until the decoder is freed (a captured graph may still name them)
+void Dec::free_moe(bool retire) {
     void* ptrs[] = {mb.idx, mb.wt, mb.cnt, mb.off, mb.cursor, mb.pos_of_slot, mb.slot_of_pos, mb.tile_expert, mb.tile_row0,
                     mb.tile_rows, mb.n_tiles, mb.n_rows, mb.row_w, mb.xs, mb.c13, mb.act, mb.c2};
     for (void* p : ptrs) {
         if (p) {
-            cudaFree(p);
+            if (retire) {
+                retired.push_back(p);
+            } else {
+                cudaFree(p);
+            }
         }
     }
     mb = MoeBufs{};
@@ -42,7 +47,7 @@ int Dec::ensure_moe(int t, cudaStream_t st) {
         return fail("w4a16 moe: scratch too small during graph capture; run the call once before capturing");
     }
     cudaDeviceSynchronize();
-    free_moe();
+    free_moe(true);
     const size_t slots = (size_t)t * moe.top_k;
     const int max_tiles = (int)((slots + 7) / 8) + (moe.e1 - moe.e0);   // worst case: 8-row segments
     cudaError_t e = cudaSuccess;
@@ -163,7 +168,7 @@ int w4a16_set_moe(w4a16_dec* dec, int n_experts, int top_k, int moe_ffn, int hid
     if (n_experts < 1 || n_experts > 1024 || top_k < 1 || top_k > 32 || top_k > n_experts) {
         return d.fail("w4a16 set_moe: n_experts=%d top_k=%d unsupported (experts <= 1024, top_k <= 32)", n_experts, top_k);
     }
-    if ((group != 32 && group != 128) || moe_ffn % 64 != 0 || hidden % 64 != 0 || moe_ffn % group != 0 ||
+    if ((group != 32 && group != 64 && group != 128) || moe_ffn % 64 != 0 || hidden % 64 != 0 || moe_ffn % group != 0 ||
         hidden % group != 0) {
         return d.fail("w4a16 set_moe: ffn=%d hidden=%d group=%d violate the tile contract", moe_ffn, hidden, group);
     }

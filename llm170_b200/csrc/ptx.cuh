@@ -92,6 +92,13 @@ __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t
     return r;
 }
 
+// Routing weight applied to a grouped-matmul output the way the reference's MoE GEMM does it
+// (crates/backend-gpu/src/rawcuda/assets/marlin_moe/marlin_template.h:1515-1524): the f32 sum is rounded to f16,
+// the weight is rounded to f16, and their product is rounded to f16 once more (__hmul2 there).  Returned as f32.
+__device__ __forceinline__ float mul_row_w(float v, float w) {
+    return __half2float(__hmul(__float2half_rn(v), __float2half_rn(w)));
+}
+
 // One packed word of the T64 layout -> a[0]=(r0;k,k+1) a[1]=(r1;k,k+1) a[2]=(r0;k+2,k+3) a[3]=(r1;k+2,k+3)
 // as half2 registers holding (nibble-8) exactly.  0x6400 is f16 1024: (w & 0x000f)|0x6400 = 1024+nibble,
 // minus 1032 = nibble-8;  (w & 0x00f0)|0x6400 = 1024+16*nibble, times 1/16 minus 72 = nibble-8.

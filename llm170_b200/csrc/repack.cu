@@ -71,8 +71,9 @@ __global__ void unpack_q_kernel(const uint32_t* __restrict__ qt, uint32_t* __res
     }
 }
 
-__device__ __forceinline__ uint16_t bf16_to_f16_exact(uint16_t b, int* bad) {
-    const float f = __uint_as_float(((uint32_t)b) << 16);
+// bf16 scale times 2^shift as f16; *bad is set when that value is not exactly representable in f16.
+__device__ __forceinline__ uint16_t bf16_to_f16_exact(uint16_t b, int shift, int* bad) {
+    const float f = ldexpf(__uint_as_float(((uint32_t)b) << 16), shift);
     const __half h = __float2half_rn(f);
     if (__half2float(h) != f && !(f != f)) {
         *bad = 1;
@@ -80,19 +81,41 @@ __device__ __forceinline__ uint16_t bf16_to_f16_exact(uint16_t b, int* bad) {
     return __half_as_ushort(h);
 }
 
-__global__ void repack_s_kernel(const uint16_t* __restrict__ s, uint16_t* __restrict__ stl, int n, int ng,
-                                int scale_bf16, int* __restrict__ err) {
+// Smallest and largest biased exponent among the non-zero bf16 scales (range[0] starts at 255, range[1] at 0).
+__global__ void scale_range_kernel(const uint16_t* __restrict__ s, size_t total, int* __restrict__ range) {
+    int lo = 255, hi = 0;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int v = s[i] & 0x7fff;
+        if (v != 0) {
+            const int e = v >> 7;
+            lo = min(lo, e);
+            hi = max(hi, e);
+        }
+    }
+    lo = __reduce_min_sync(0xffffffffu, lo);
+    hi = __reduce_max_sync(0xffffffffu, hi);
+    if ((threadIdx.x & 31) == 0) {
+        atomicMin(range, lo);
+        atomicMax(range + 1, hi);
+    }
+}
+
+// `ng`: groups per row of the TILED array; a source group covers `src_div` of them (2 when 64-channel groups are
+// stored as two 32-channel groups with the same scale, else 1).
+__global__ void repack_s_kernel(const uint16_t* __restrict__ s, uint16_t* __restrict__ stl, int n, int ng, int src_div,
+                                int scale_bf16, int shift, int* __restrict__ err) {
     const size_t total = (size_t)n * (size_t)ng;
+    const int ng_src = ng / src_div;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
         // i indexes the tiled array: [rb][grp][j][hi]
         const int hi = (int)(i & 1), j = (int)((i >> 1) & 7);
         const size_t rg = i >> 4;
         const int grp = (int)(rg % (size_t)ng), rb = (int)(rg / (size_t)ng);
-        uint16_t v = s[(size_t)(rb * TILE_ROWS + j + 8 * hi) * ng + grp];
+        uint16_t v = s[(size_t)(rb * TILE_ROWS + j + 8 * hi) * ng_src + grp / src_div];
         if (scale_bf16) {
             int bad = 0;
-            v = bf16_to_f16_exact(v, &bad);
+            v = bf16_to_f16_exact(v, shift, &bad);
             if (bad && err) {
                 *err = 1;
             }
@@ -101,14 +124,17 @@ __global__ void repack_s_kernel(const uint16_t* __restrict__ s, uint16_t* __rest
     }
 }
 
-__global__ void unpack_s_kernel(const uint16_t* __restrict__ stl, uint16_t* __restrict__ s, int n, int ng) {
+__global__ void unpack_s_kernel(const uint16_t* __restrict__ stl, uint16_t* __restrict__ s, int n, int ng, int src_div) {
     const size_t total = (size_t)n * (size_t)ng;
+    const int ng_src = ng / src_div;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
         const int hi = (int)(i & 1), j = (int)((i >> 1) & 7);
         const size_t rg = i >> 4;
         const int grp = (int)(rg % (size_t)ng), rb = (int)(rg / (size_t)ng);
-        s[(size_t)(rb * TILE_ROWS + j + 8 * hi) * ng + grp] = stl[i];
+        if (grp % src_div == 0) {
+            s[(size_t)(rb * TILE_ROWS + j + 8 * hi) * ng_src + grp / src_div] = stl[i];
+        }
     }
 }
 
@@ -117,7 +143,7 @@ __global__ void unpack_s_kernel(const uint16_t* __restrict__ stl, uint16_t* __re
 // which is the value the tensor-core GEMM feeds its MMA.
 template <bool OUT_F16>
 __global__ void dequant_kernel(const uint32_t* __restrict__ qt, const uint16_t* __restrict__ stl,
-                               void* __restrict__ out, int n, int k, int group) {
+                               void* __restrict__ out, int n, int k, int group, float out_mul) {
     const size_t total = (size_t)n * (size_t)(k / 8);
     const int nrb = n / TILE_ROWS, ng = k / group;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
@@ -127,8 +153,9 @@ __global__ void dequant_kernel(const uint32_t* __restrict__ qt, const uint16_t* 
         const int rb = c.r0 / TILE_ROWS, g = c.r0 % TILE_ROWS;
         const int grp = c.kbase / group;
         const size_t sbase = (((size_t)rb * ng + grp) * 8 + g) * 2;
-        const float s0 = __half2float(__ushort_as_half(stl[sbase]));
-        const float s1 = __half2float(__ushort_as_half(stl[sbase + 1]));
+        // out_mul is a power of two (1 unless the source scales were bf16 values outside the f16 range)
+        const float s0 = __half2float(__ushort_as_half(stl[sbase])) * out_mul;
+        const float s1 = __half2float(__ushort_as_half(stl[sbase + 1])) * out_mul;
         const int pos[4] = {0, 4, 2, 6};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -160,23 +187,26 @@ inline int grid_for(size_t total) {
 void launch_repack_q(const uint32_t* q, uint32_t* qt, int n, int k, cudaStream_t st) {
     repack_q_kernel<<<grid_for((size_t)n * (k / 8)), 256, 0, st>>>(q, qt, n, k);
 }
-void launch_repack_s(const uint16_t* s, uint16_t* stl, int n, int k, int group, int scale_bf16, int* err,
-                     cudaStream_t st) {
-    repack_s_kernel<<<grid_for((size_t)n * (k / group)), 256, 0, st>>>(s, stl, n, k / group, scale_bf16, err);
+void launch_scale_range(const uint16_t* s, size_t total, int* range2, cudaStream_t st) {
+    scale_range_kernel<<<grid_for(total), 256, 0, st>>>(s, total, range2);
+}
+void launch_repack_s(const uint16_t* s, uint16_t* stl, int n, int k, int group, int src_div, int scale_bf16, int shift,
+                     int* err, cudaStream_t st) {
+    repack_s_kernel<<<grid_for((size_t)n * (k / group)), 256, 0, st>>>(s, stl, n, k / group, src_div, scale_bf16, shift, err);
 }
 void launch_unpack_q(const uint32_t* qt, uint32_t* q, int n, int k, cudaStream_t st) {
     unpack_q_kernel<<<grid_for((size_t)n * (k / 8)), 256, 0, st>>>(qt, q, n, k);
 }
-void launch_unpack_s(const uint16_t* stl, uint16_t* s, int n, int k, int group, cudaStream_t st) {
-    unpack_s_kernel<<<grid_for((size_t)n * (k / group)), 256, 0, st>>>(stl, s, n, k / group);
+void launch_unpack_s(const uint16_t* stl, uint16_t* s, int n, int k, int group, int src_div, cudaStream_t st) {
+    unpack_s_kernel<<<grid_for((size_t)n * (k / group)), 256, 0, st>>>(stl, s, n, k / group, src_div);
 }
 void launch_dequant(const uint32_t* qt, const uint16_t* stl, void* out, int n, int k, int group, int out_f16,
-                    cudaStream_t st) {
+                    float out_mul, cudaStream_t st) {
     const int g = grid_for((size_t)n * (k / 8));
     if (out_f16) {
-        dequant_kernel<true><<<g, 256, 0, st>>>(qt, stl, out, n, k, group);
+        dequant_kernel<true><<<g, 256, 0, st>>>(qt, stl, out, n, k, group, out_mul);
     } else {
-        dequant_kernel<false><<<g, 256, 0, st>>>(qt, stl, out, n, k, group);
+        dequant_kernel<false><<<g, 256, 0, st>>>(qt, stl, out, n, k, group, out_mul);
     }
 }
 

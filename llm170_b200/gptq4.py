@@ -20,13 +20,12 @@ def check_shapes(t: int, qlen: int, slen: int, xlen: int, n: int, k: int, group:
 
 
 def kernel_sym(gemm: bool, group: int, scale_bf16: bool) -> str:
-    """gptq4.rs:60-70: which kernel family serves a (group, scale type) combination.
-
-    This build serves f16 scales for both group sizes and bf16 scales that are exact in f16.
-    """
-    if group not in (128, 32):
+    """gptq4.rs:60-70: which kernel family serves a (group, scale type) combination -- here the template
+    instantiations of csrc/gemm_tc.cu (t > 8) and csrc/gemv_sk.cu (decode), as `W4a16Dec.last_kernel` reports them."""
+    if group not in (128, 64, 32):
         raise W4a16Error(f"gptq4: unsupported combination group={group} scale_bf16={scale_bf16}")
-    return ("w4a16_gemm_tc" if gemm else "w4a16_gemv_sk") + f"_g{group}"
+    g = 32 if group == 64 else group      # group 64 is stored as two groups of 32 with the same scale
+    return f"gemm_w4a16_tc_kernel<{g},1>" if gemm else f"gemv_sk_kernel<{g},true>"
 
 
 class Gptq4:

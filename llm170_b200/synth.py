@@ -12,29 +12,35 @@ from __future__ import annotations
 import numpy as np
 
 
-def quantize_sym_int4(w: np.ndarray, group: int):
-    """w f32 [n,k] -> (q u32 [n,k/8], s u16 (f16 bits) [n,k/group])."""
+def quantize_sym_int4(w: np.ndarray, group: int, scale_bf16: bool = False):
+    """w f32 [n,k] -> (q u32 [n,k/8], s u16 [n,k/group]); s holds f16 bits, or bf16 bits (the f32 value
+    truncated to its upper half, as the reference's generator writes them) when ``scale_bf16``."""
     n, k = w.shape
     assert k % group == 0 and k % 8 == 0
     wg = w.reshape(n, k // group, group).astype(np.float32)
     amax = np.abs(wg).max(axis=2)
     amax = np.where(amax == 0, np.float32(1e-6), amax).astype(np.float32)
-    s16 = (amax / np.float32(7.0)).astype(np.float16)
-    sf = s16.astype(np.float32)
-    # guard: a scale that rounds to zero in f16 would divide by zero
+    s32 = (amax / np.float32(7.0)).astype(np.float32)
+    if scale_bf16:
+        sbits = (s32.view(np.uint32) >> 16).astype(np.uint16)
+        sf = (sbits.astype(np.uint32) << 16).view(np.float32)
+    else:
+        sbits = s32.astype(np.float16).view(np.uint16)
+        sf = sbits.view(np.float16).astype(np.float32)
+    # guard: a scale that rounds to zero would divide by zero
     sf = np.where(sf == 0, np.float32(2.0 ** -24), sf)
     qv = np.clip(np.rint(wg / sf[:, :, None]), -8, 7).astype(np.int32) + 8
     nib = qv.reshape(n, k // 8, 8).astype(np.uint32)
     shifts = (4 * np.arange(8, dtype=np.uint32))[None, None, :]
     q = np.bitwise_or.reduce(nib << shifts, axis=2).astype(np.uint32)
-    return q, s16.view(np.uint16).reshape(n, k // group)
+    return q, np.ascontiguousarray(sbits.reshape(n, k // group))
 
 
-def make_linear(n: int, k: int, group: int, seed: int, sigma: float = 0.02):
+def make_linear(n: int, k: int, group: int, seed: int, sigma: float = 0.02, scale_bf16: bool = False):
     """Deterministic int4 linear: returns (q u32 [n,k/8], s u16 [n,k/group])."""
     rng = np.random.Generator(np.random.PCG64(seed))
     w = rng.standard_normal((n, k), dtype=np.float32) * np.float32(sigma)
-    return quantize_sym_int4(w, group)
+    return quantize_sym_int4(w, group, scale_bf16)
 
 
 def make_acts(m: int, k: int, seed: int, scale: float = 1.0) -> np.ndarray:

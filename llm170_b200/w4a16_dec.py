@@ -68,6 +68,10 @@ class W4a16Dec:
     def launch_count(self) -> int:
         return int(self._L.w4a16_launch_count(self._h))
 
+    def last_kernel(self) -> str:
+        """Kernel instantiation launched by the last forward call."""
+        return self._L.w4a16_last_kernel(self._h).decode()
+
     def weights_bytes(self) -> int:
         return int(self._L.w4a16_weights_bytes(self._h))
 
@@ -189,9 +193,14 @@ class W4a16Dec:
         self._ck(self._L.w4a16_tp_connect(self._h, blob))
         dist.barrier(group=group)
 
+    def tp_rearm(self):
+        """Resets this rank's exchange block after an abandoned fused all-reduce; every rank calls it between
+        two host barriers."""
+        self._ck(self._L.w4a16_tp_rearm(self._h))
+
     def sk_single_allreduce(self, name: str, x16: torch.Tensor, out: torch.Tensor | None = None, t: int = 1,
                             out_f16: bool = False) -> torch.Tensor:
-        """Row-parallel GEMV whose kernel also sums the partial outputs over the ranks (peer loads)."""
+        """Row-parallel GEMV whose kernel also sums the partial outputs over the ranks (peer stores)."""
         n, k, _ = self.lin_spec(name)
         self._tensor_ok(x16, torch.float16, "x16")
         if x16.numel() != t * k:

@@ -198,8 +198,9 @@ def moe_ffn(x_u16, logits, w13_q, w13_s, w2_q, w2_s, top_k: int, group: int, exp
     """CPU restatement of the resident MoE FFN: routing by select_topk
     (crates/core/src/qwen35/stages/moe.rs:8-31); per expert the two linears are lane dots; the rounding
     points follow the reference's GPU path (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/marlin_moe.rs:290-422):
-    c13 -> f16, silu(g)*u -> f16 (crates/backend-gpu/src/rawcuda/assets/moe.cu:1649-1660), w*c2 -> f16, then the
-    f32 sum over k in rank order (crates/backend-gpu/src/rawcuda/assets/moe.cu:1662-1674).
+    c13 -> f16, silu(g)*u -> f16 (crates/backend-gpu/src/rawcuda/assets/moe.cu:1649-1660), f16(c2) * f16(w) -> f16
+    (the epilogue of the grouped GEMM, crates/backend-gpu/src/rawcuda/assets/marlin_moe/marlin_template.h:1515-1524),
+    then the f32 sum over k in rank order (crates/backend-gpu/src/rawcuda/assets/moe.cu:1662-1674).
     `experts=(e0,e1)` keeps only that range (one rank's share under expert parallelism)."""
     x = _c(x_u16, np.uint16)
     t, h = x.shape
@@ -218,8 +219,9 @@ def moe_ffn(x_u16, logits, w13_q, w13_s, w2_q, w2_s, top_k: int, group: int, exp
         g, u = c13[:, :f], c13[:, f:]
         act = ((g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))) * u).astype(np.float16)
         c2 = linear_lane(w2_q[e], w2_s[e], act.view(np.uint16), len(rows), h, f, group)
-        wv = np.array([w for _, _, w in rows], np.float32)[:, None]
-        c2 = (c2 * wv).astype(np.float16).astype(np.float32)
+        # marlin_moe/marlin_template.h:1515-1524: the f16 result times the f16-rounded routing weight, rounded to f16
+        wv = np.array([w for _, _, w in rows], np.float32)[:, None].astype(np.float16).astype(np.float32)
+        c2 = (c2.astype(np.float16).astype(np.float32) * wv).astype(np.float16).astype(np.float32)
         for j, (i, r, _) in enumerate(rows):
             contrib[i, r] = c2[j]
     out = np.zeros((t, h), np.float32)

@@ -81,12 +81,14 @@ def test_shapes_reject_bad_rank_and_misalignment(L):
 
 
 def test_kernel_sym_selects_variants():
-    # gptq4.rs:228-233, adapted: both group sizes exist for f16 scales; other groups are rejected
-    assert kernel_sym(False, 128, False) == "w4a16_gemv_sk_g128"
-    assert kernel_sym(True, 128, False) == "w4a16_gemm_tc_g128"
-    assert kernel_sym(False, 32, True) == "w4a16_gemv_sk_g32"
+    # gptq4.rs:228-233, adapted: the names are the kernel instantiations this library launches; group 64 is
+    # served by the group-32 kernels (its scales are stored twice), other groups are rejected
+    assert kernel_sym(False, 128, False) == "gemv_sk_kernel<128,true>"
+    assert kernel_sym(True, 128, False) == "gemm_w4a16_tc_kernel<128,1>"
+    assert kernel_sym(False, 32, True) == "gemv_sk_kernel<32,true>"
+    assert kernel_sym(True, 64, False) == "gemm_w4a16_tc_kernel<32,1>"
     with pytest.raises(W4a16Error):
-        kernel_sym(True, 64, False)
+        kernel_sym(True, 16, False)
 
 
 def test_layout_word_index_is_a_bijection():

@@ -111,3 +111,41 @@ def test_gemm_and_gemv_agree_on_the_same_weights(dec):
                         dec.sk_single_dev("both", x[8:].contiguous(), t=8)])
     dec.sync()
     assert (y_gemm - y_gemv).abs().max().item() <= 2e-4
+
+
+# BASELINE config 3 at its own sizes: the four 27B-class layer shapes at M = 4096, and M = 1024 on the two largest.
+# Every output is checked against the specified operation as a plain torch fp32 matmul (x times the weight rounded
+# once to f16), and a spread of rows and tokens -- first, middle and last n-tile, first and last m-tile -- against
+# the f32-accumulated CPU lane oracle with the 2e-3 gate (crates/server/src/probes/w4a16/gates.rs:108-138,
+# crates/server/src/probes/w4a16/gpu/bench.rs:191-259 are the reference's checks of the same kernels).
+@pytest.mark.parametrize("name,m", [("qkv", 4096), ("o_proj", 4096), ("gate_up", 4096), ("down", 4096),
+                                    ("gate_up", 1024), ("down", 1024)])
+def test_config3_prefill_shapes_full_size(dec, orc, name, m):
+    k, n = synth.DENSE_27B[name]
+    q, s = synth.make_linear_cuda(n, k, 128, seed=2000 + len(name), device=torch.device("cuda", 0))
+    dec.upload_lin_g_dev("c3", q, s, n, k, 128)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2)
+    xd = (torch.randn((m, k), generator=gen, device="cuda") / (k ** 0.5)).to(torch.float16)
+    y = dec.lin_forward("c3", xd, m)
+    dec.sync()
+    w16 = dec.dequant_lin("c3", f16=True)
+    worst, scale = 0.0, 0.0
+    for r0 in range(0, n, 8192):                      # row slabs keep the fp32 reference within a few GB
+        ref = xd.float() @ w16[r0:r0 + 8192].float().T
+        worst = max(worst, (y[:, r0:r0 + 8192] - ref).abs().max().item())
+        scale = max(scale, ref.abs().max().item())
+        del ref
+    assert worst <= 1e-4 * scale + 1e-6, (worst, scale)
+    # lane oracle on 3 x 32 rows and 64 tokens
+    qh, sh = q.cpu().numpy().view(np.uint32), s.cpu().numpy().view(np.uint16)
+    toks = np.r_[0:16, m // 2:m // 2 + 16, m - 32:m]
+    xs = np.ascontiguousarray(xd[torch.from_numpy(toks).cuda()].cpu().numpy().view(np.uint16))
+    got = y[torch.from_numpy(toks).cuda()].cpu().numpy()
+    for r0 in (0, (n // 2) // 16 * 16, n - 32):
+        want = orc.linear_lane(qh, sh, xs, len(toks), n, k, 128, rows=(r0, r0 + 32))
+        assert np.abs(got[:, r0:r0 + 32] - want[:, r0:r0 + 32]).max() <= TOL
+    y16 = dec.lin_forward("c3", xd, m, out_f16=True)
+    dec.sync()
+    assert torch.equal(y16, y.to(torch.float16))
+    dec.drop_lin("c3")

@@ -204,6 +204,24 @@ def test_config1_reference_cpu_case(dec, orc):
     dec.drop_lin("c1")
 
 
+def test_config1_single_call_all_rows(dec, orc):
+    # BASELINE config 1 through ONE lin_forward(t=16) call (the small-batch band above the decode GEMV),
+    # every one of the 16 x 4096 outputs against the lane oracle; f16 output = RN_f16 of the f32 one
+    n = k = 4096
+    q, s = synth.make_linear(n, k, 128, seed=0)
+    x = synth.make_acts(16, k, seed=0)
+    want = orc.linear_lane(q, s, x, 16, n, k, 128)
+    dec.upload_lin_g("c1b", q, s, n, k, 128)
+    xd = x_dev(x)
+    got = dec.lin_forward("c1b", xd, 16)
+    dec.sync()
+    assert np.abs(got.cpu().numpy() - want).max() <= TOL
+    got16 = dec.lin_forward("c1b", xd, 16, out_f16=True)
+    dec.sync()
+    assert torch.equal(got16, got.to(torch.float16))
+    dec.drop_lin("c1b")
+
+
 def test_multi_segment_matches_single(dec):
     k = 1024
     segs = [("q_", 512), ("k_", 128), ("v_", 144)]
@@ -212,8 +230,13 @@ def test_multi_segment_matches_single(dec):
         q, s = synth.make_linear(n, k, 128, seed=40 + i)
         dec.upload_lin_g(nm, q, s, n, k, 128)
     outs = dec.sk_multi_dev([nm for nm, _ in segs], x, t=4)
-    for (nm, _), o in zip(segs, outs):
-        assert torch.equal(o, dec.sk_single_dev(nm, x, t=4))
+    outs2 = dec.sk_multi_dev([nm for nm, _ in segs], x, t=4)
+    for (nm, _), o, o2 in zip(segs, outs, outs2):
+        assert torch.equal(o, o2)                      # the same launch twice: the same bits
+        # the leftover row blocks of a launch are cut along K by the launch's geometry, so the multi-segment
+        # launch and the single one may add the same f32 terms in another order
+        single = dec.sk_single_dev(nm, x, t=4)
+        assert (o - single).abs().max().item() <= 1e-5 * max(1.0, single.abs().max().item())
 
 
 def test_split_k_is_deterministic_and_scratch_is_clean(dec):
@@ -296,3 +319,87 @@ def test_debug_timeline_stamps_are_ordered(dec):
         dec.set_tuning("debug_timeline", 0)
     with pytest.raises(Exception):
         dec.debug_timeline()                  # off again: the call says so
+
+
+def test_captured_graph_survives_scratch_growth(dec):
+    # a graph captured with a small shape keeps the scratch addresses of that time; a later eager call that needs
+    # more scratch must not free them under the graph
+    n, k = 512, 2048
+    q, s = synth.make_linear(n, k, 128, seed=5)
+    dec.upload_lin_g("gsmall", q, s, n, k, 128)
+    x = x_dev(synth.make_acts(1, k, seed=5))
+    ref = dec.sk_single_dev("gsmall", x, t=1).clone()
+    out = torch.zeros_like(ref)
+    st = torch.cuda.ExternalStream(dec.stream_ptr(), device=torch.device("cuda", 0))
+    torch.cuda.synchronize()
+    with torch.cuda.stream(st):
+        dec.capture_begin()
+        dec.sk_single_dev("gsmall", x, out=out, t=1)
+        gx = dec.capture_end()
+    dec.graph_launch(gx)
+    dec.sync()
+    assert torch.equal(out, ref)
+    # grow: forced K splits of a wide linear need far more partial-sum scratch than anything above
+    nb, kb = 34816, 5120
+    qb, sb = synth.make_linear_cuda(nb, kb, 128, seed=6, device=torch.device("cuda", 0))
+    dec.upload_lin_g_dev("gbig", qb, sb, nb, kb, 128)
+    dec.set_tuning("gemv_persistent", 0)
+    dec.set_tuning("gemv_cluster", 0)
+    dec.set_tuning("gemv_ksplit", 40)
+    try:
+        dec.sk_single_dev("gbig", torch.randn((8, kb), device="cuda").half(), t=8)
+        dec.sync()
+    finally:
+        dec.set_tuning("gemv_ksplit", 0)
+        dec.set_tuning("gemv_cluster", 1)
+        dec.set_tuning("gemv_persistent", 1)
+    out.zero_()
+    dec.graph_launch(gx)
+    dec.sync()
+    assert torch.equal(out, ref)
+    dec.graph_destroy(gx)
+    dec.drop_lin("gbig")
+
+
+def test_misaligned_buffers_are_refused_before_launch(dec):
+    from llm170_b200.w4a16_dec import W4a16Error
+    n, k = 256, 512
+    q, s = synth.make_linear(n, k, 128, seed=8)
+    dec.upload_lin_g("al", q, s, n, k, 128)
+    x = x_dev(synth.make_acts(1, k, seed=8))
+    buf = torch.zeros(n + 8, device="cuda")
+    with pytest.raises(W4a16Error, match="aligned"):
+        dec.sk_single_dev("al", x, out=buf[1:n + 1], t=1)          # 4-byte aligned f32 view
+    with pytest.raises(W4a16Error, match="aligned"):
+        dec.sk_single_static("al", x, out=buf[1:n + 1], t=1)
+    xbuf = torch.zeros(k + 8, dtype=torch.float16, device="cuda")
+    with pytest.raises(W4a16Error, match="aligned"):
+        dec.sk_single_dev("al", xbuf[1:k + 1], t=1)
+    assert torch.isfinite(dec.sk_single_dev("al", x, out=buf[4:n + 4], t=1)).all()   # 16-byte aligned view is fine
+
+
+# Scale / group variants the reference's loader accepts (crates/core/src/w4a16.rs:141-146,225-234): groups of 64
+# channels, and bf16 scales -- ordinary ones, and ones far outside the f16 range, which are shifted by a power of
+# two at upload and shifted back by the kernels.
+@pytest.mark.parametrize("group,bf16,sigma", [(64, False, 0.02), (64, True, 0.02), (32, True, 0.02), (128, True, 0.02),
+                                              (32, True, 2e-7), (128, True, 3e5)])
+def test_group64_and_bf16_scales(dec, orc, group, bf16, sigma):
+    n, k = 512, 1024
+    q, s = synth.make_linear(n, k, group, seed=90 + group, sigma=sigma, scale_bf16=bf16)
+    dec.upload_lin_g("var", q, s, n, k, group, scale_bf16=bf16)
+    assert dec.lin_spec("var") == (n, k, group)
+    want = orc.dequant_w4a16(q, s, n, k, group, scale_bf16=bf16)
+    got = dec.dequant_lin("var").cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))        # (nibble-8)*scale, bit for bit
+    scale = float(np.abs(want).max()) * np.sqrt(k)
+    for t in (1, 8, 40):                                                    # decode GEMV and tensor-core GEMM
+        x = synth.make_acts(t, k, seed=t)
+        y = dec.lin_forward("var", x_dev(x), t).cpu().numpy()
+        ref = orc.linear_lane(q, s, x, t, n, k, group, scale_bf16=bf16)
+        assert np.abs(y - ref).max() <= max(TOL, 1e-3 * scale) * (1.0 if sigma == 0.02 else np.abs(ref).max() + 1e-30), (t,)
+    if sigma == 0.02:
+        q2, s2 = dec.unpack_lin("var")                                      # scales come back as f16 values
+        assert np.array_equal(q2.cpu().numpy().view(np.uint32), q)
+        sf = (s.astype(np.uint32) << 16).view(np.float32) if bf16 else s.view(np.float16).astype(np.float32)
+        assert np.array_equal(s2.cpu().numpy().astype(np.float32), sf)
+    dec.drop_lin("var")

@@ -110,7 +110,71 @@ def test_moe_contract_errors(dec):
     with pytest.raises(W4a16Error):
         dec.set_moe(2000, 8, 64, 64, 32)
     with pytest.raises(W4a16Error):
-        dec.set_moe(8, 2, 64, 64, 64)
+        dec.set_moe(8, 2, 64, 64, 16)
     dec.set_moe(8, 2, 64, 128, 32)
     with pytest.raises(W4a16Error):
         dec.moe_ffn_dev_t(5, torch.zeros((1, 8), device="cuda"), torch.zeros((1, 128), dtype=torch.float16, device="cuda"), 1)
+
+
+# BASELINE config 4 at its own dimensions: 128 experts, hidden 2048, expert FFN 768, top-8, group 32, for
+# T = 1, 64 and 4096 tokens.  T = 4096 is compared on a stated token subset (the oracle runs one token at a
+# time through every selected expert); the reference's own check of this chain is the tiny-model token
+# equivalence of crates/server/src/probes/w4a16/tiny_equiv_tests.rs:56-136.
+@pytest.fixture(scope="module")
+def moe35(dec):
+    mo = synth.MOE_35B
+    w = synth.make_experts(mo["n_experts"], mo["moe_ffn"], mo["hidden"], mo["group"], seed=3)
+    return mo, w
+
+
+@pytest.mark.parametrize("t", [1, 64, 4096])
+def test_config4_moe_layer_full_size(dec, orc, moe35, t):
+    mo, (w13_q, w13_s, w2_q, w2_s) = moe35
+    ne, h, f, kk, grp = mo["n_experts"], mo["hidden"], mo["moe_ffn"], mo["top_k"], mo["group"]
+    dec.set_moe(ne, kk, f, h, grp)
+    dec.upload_experts(0, w13_q, w13_s, w2_q, w2_s)
+    x = synth.make_acts(t, h, seed=30 + t)
+    lg = synth.make_router_logits(t, ne, seed=31 + t)
+    xd = torch.from_numpy(x.view(np.float16).copy()).cuda()
+    lgd = torch.from_numpy(lg).cuda()
+    y = dec.moe_ffn_dev_t(0, lgd, xd, t)
+    dec.sync()
+    y2 = dec.moe_ffn_dev_t(0, lgd, xd, t)
+    dec.sync()
+    assert torch.equal(y, y2)                                        # bit-repeatable
+    sub = np.arange(t) if t <= 64 else np.r_[0:8, t // 2:t // 2 + 8, t - 8:t]
+    want = orc.moe_ffn(np.ascontiguousarray(x[sub]), np.ascontiguousarray(lg[sub]), w13_q, w13_s, w2_q, w2_s, kk, grp)
+    got = y.cpu().numpy()[sub]
+    err = np.abs(got - want).max()
+    assert err <= TOL, err
+    # routing of every token, not only the subset
+    idx, wt = dec.moe_topk(lgd)
+    idx = idx.cpu().numpy()
+    for i in list(range(0, t, max(1, t // 97))):
+        assert [e for e, _ in orc.select_topk(lg[i], kk)] == idx[i].tolist(), i
+
+
+def test_topk_near_ties_order_on_normalised_probabilities(dec, orc):
+    # Logits one or two float steps apart: their exponentials differ, but after the division by the softmax sum
+    # they may round to the same probability, and then the lower index must win -- as in the reference, which
+    # orders on p = exp / sum (crates/core/src/qwen35/stages/moe.rs:8-31), not on the numerators.
+    n_exp, k, t = 128, 8, 256
+    dec.set_moe(n_exp, k, 64, 64, 32)
+    rng = np.random.Generator(np.random.PCG64(77))
+    lg = rng.standard_normal((t, n_exp)).astype(np.float32)
+    for i in range(t):
+        # clusters of almost-equal logits around the top of the distribution
+        base = np.float32(1.5 + 0.01 * i)
+        cols = rng.permutation(n_exp)[:12]
+        steps = rng.integers(0, 3, size=12)
+        vals = np.array([base] * 12, np.float32)
+        for j in range(12):
+            for _ in range(int(steps[j])):
+                vals[j] = np.nextafter(vals[j], np.float32(0))
+        lg[i, cols] = vals
+    idx, wt = dec.moe_topk(torch.from_numpy(lg).cuda())
+    idx, wt = idx.cpu().numpy(), wt.cpu().numpy()
+    for i in range(t):
+        want = orc.select_topk(lg[i], k)
+        assert [e for e, _ in want] == idx[i].tolist(), i
+        assert np.allclose([w for _, w in want], wt[i], rtol=0, atol=2e-7)

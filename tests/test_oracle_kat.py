@@ -301,3 +301,66 @@ def test_linear_rows_subset_and_threads(orc):
     assert np.array_equal(a, b)
     c = orc.linear_lane(q, s, x, 3, n, k, 128, rows=(10, 50))
     assert np.array_equal(c[:, 10:50], a[:, 10:50]) and not c[:, :10].any() and not c[:, 50:].any()
+
+
+def _f16_round(orc, v):
+    """f32 array -> f16 values (as f32), element by element through the pinned orc.f32_to_f16."""
+    flat = np.asarray(v, np.float32).ravel()
+    bits = np.array([orc.f32_to_f16(float(e)) for e in flat], np.uint16)
+    return np.array([orc.half_to_f32(int(b)) for b in bits], np.float32).reshape(np.shape(v)), bits.reshape(np.shape(v))
+
+
+def test_moe_ffn_equals_stepwise_chain_of_pinned_primitives(orc):
+    """The resident MoE chain of crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/marlin_moe.rs:290-422, restated
+    a second time, token by token and row by row, from primitives that the known-answer tests above pin
+    (select_topk, dot_row_w4a16_lane_group, half_to_f32, f32_to_f16): grouped matmul 1 -> f16, silu(gate)*up in
+    f32 -> f16 (assets/moe.cu:1649-1660), grouped matmul 2 -> f16, times the f16 routing weight -> f16
+    (assets/marlin_moe/marlin_template.h:1515-1524), f32 sum over k in slot order (assets/moe.cu:1662-1674).
+    Weights, scales and activations are powers of two (the recipe of probes/w4a16/gpu/bench.rs:123-166), so
+    matmul 1 is exact whatever the summation order.  oracle.moe_ffn must agree bit for bit.  The reference holds
+    no known answer for the whole chain; this composition is the strongest pin available for it."""
+    n_exp, top_k, f, h, group, t = 4, 2, 64, 64, 32, 5
+    def pow2_linear(n, k, salt):
+        kk, nn = np.meshgrid(np.arange(k), np.arange(n))
+        nib = ((kk * 7 + nn * 3 + salt) % 16).astype(np.uint32)
+        q = np.bitwise_or.reduce(nib.reshape(n, k // 8, 8) << (4 * np.arange(8, dtype=np.uint32)), axis=2).astype(np.uint32)
+        s = np.array([[(12 - ((r + g + salt) % 4)) << 10 for g in range(k // group)] for r in range(n)], np.uint16)
+        return q, s
+    w13 = [pow2_linear(2 * f, h, e) for e in range(n_exp)]
+    w2 = [pow2_linear(h, f, 5 + e) for e in range(n_exp)]
+    w13_q, w13_s = np.stack([a for a, _ in w13]), np.stack([b for _, b in w13])
+    w2_q, w2_s = np.stack([a for a, _ in w2]), np.stack([b for _, b in w2])
+    i = np.arange(t * h)
+    x = ((13 - ((i // h + (i % h) // 8) % 3)) << 10).astype(np.uint16).reshape(t, h)
+    x[:, ::5] ^= 0x8000                                    # some negative activations
+    rng = np.random.Generator(np.random.PCG64(11))
+    logits = rng.standard_normal((t, n_exp)).astype(np.float32)
+
+    def lin_row(q_row, s_row, xv, k):
+        z = np.full(k // group, 8, np.uint32)
+        sf = np.array([orc.half_to_f32(int(b)) for b in s_row], np.float32)
+        return orc.dot_row_w4a16_lane_group(q_row, z, sf, xv, group)
+
+    want = np.zeros((t, h), np.float32)
+    for ti in range(t):
+        acc = np.zeros(h, np.float32)
+        for e, wgt in orc.select_topk(logits[ti], top_k):
+            c13 = np.array([lin_row(w13_q[e][r], w13_s[e][r], x[ti], h) for r in range(2 * f)], np.float32)
+            c13, _ = _f16_round(orc, c13)
+            g, u = c13[:f], c13[f:]
+            act32 = (g / (np.float32(1.0) + np.exp(-g, dtype=np.float32))) * u
+            _, act_bits = _f16_round(orc, act32)
+            c2 = np.array([lin_row(w2_q[e][r], w2_s[e][r], act_bits, f) for r in range(h)], np.float32)
+            c2h, _ = _f16_round(orc, c2)
+            wh, _ = _f16_round(orc, np.float32(wgt))
+            contrib, _ = _f16_round(orc, c2h * wh)           # product of two f16 values: exact in f32, one rounding
+            acc = acc + contrib
+        want[ti] = acc
+    got = orc.moe_ffn(x, logits, w13_q, w13_s, w2_q, w2_s, top_k, group)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # matmul 1 is exact for these inputs: check one expert against plain f64 arithmetic as well
+    e = 1
+    nib = ((w13_q[e][:, :, None] >> (4 * np.arange(8, dtype=np.uint32))) & 0xF).astype(np.float64).reshape(2 * f, h) - 8
+    wd = nib * np.repeat(w13_s[e].view(np.float16).astype(np.float64), group, axis=1)
+    exact = (x.view(np.float16).astype(np.float64) @ wd.T).astype(np.float32)
+    assert np.array_equal(orc.linear_lane(w13_q[e], w13_s[e], x, t, 2 * f, h, group), exact)
