@@ -1,6 +1,7 @@
 """Builds ``libw4a16_b200.so`` in-tree with nvcc for sm_100a (cross-compiles without a GPU)."""
 from __future__ import annotations
 
+import hashlib
 import os
 import subprocess
 import sys
@@ -8,6 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "libw4a16_b200.so")
+HASH = SO + ".srchash"
 SOURCES = ["dec.cu", "repack.cu", "gemv.cu", "gemv_sk.cu", "gemm_tc.cu", "moe.cu", "moe_host.cu", "gemv_static.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -15,13 +17,26 @@ NVCC_FLAGS = [
 ]
 
 
+def source_hash() -> str:
+    """sha256 over the CUDA sources, the public header and the compiler flags: what the binary is made from."""
+    h = hashlib.sha256()
+    files = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC))
+    files.append(os.path.join(os.path.dirname(HERE), "include", "w4a16_b200.h"))
+    for f in files:
+        h.update(os.path.basename(f).encode())
+        with open(f, "rb") as fh:
+            h.update(fh.read())
+    h.update(" ".join(NVCC_FLAGS + SOURCES).encode())
+    return h.hexdigest()
+
+
 def _stale() -> bool:
-    if not os.path.exists(SO):
+    """The binary is current when the hash recorded beside it equals the hash of the sources (file times do not
+    survive a copy of the tree to another machine; contents do)."""
+    if not os.path.exists(SO) or not os.path.exists(HASH):
         return True
-    t = os.path.getmtime(SO)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
-    deps.append(os.path.join(os.path.dirname(HERE), "include", "w4a16_b200.h"))
-    return any(os.path.getmtime(d) > t for d in deps)
+    with open(HASH) as fh:
+        return fh.read().strip() != source_hash()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -35,6 +50,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         sys.stderr.write(r.stdout + r.stderr)
     if r.returncode != 0:
         raise RuntimeError("nvcc failed building libw4a16_b200.so")
+    with open(HASH, "w") as fh:
+        fh.write(source_hash() + "\n")
     return SO
 
 

@@ -21,6 +21,8 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <string>
+
 #include "../../include/w4a16_b200.h"
 #include "dec.h"
 #include "ptx.cuh"
@@ -491,6 +493,7 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     if (e != cudaSuccess) {
         return cuda_fail("launch gemm", e);
     }
+    last_kernel = "gemm_w4a16_tc_kernel<" + std::to_string(l->group) + "," + std::to_string(mt) + ">";
     launches++;
     return 0;
 }
@@ -553,6 +556,7 @@ int Dec::gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int 
     if (e != cudaSuccess) {
         return cuda_fail("launch grouped gemm", e);
     }
+    last_kernel = "gemm_w4a16_tc_kernel<" + std::to_string(l->group) + "," + std::to_string(mt) + "> (grouped)";
     launches++;
     return 0;
 }

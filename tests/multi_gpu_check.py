@@ -70,25 +70,78 @@ def main():
                     worst = max(worst, err)
                     assert err <= 2e-3, (t, rep, i, err)
     st = torch.cuda.ExternalStream(dec.stream_ptr(), device=dev)
-    q2, s2, n2, k2, g2 = lins[0]
-    x = synth.make_acts(1, k2, seed=999)
-    xs = torch.from_numpy(shard.shard_acts(x, k2, "row", rank, world).view(np.float16).copy()).to(dev)
-    outs = [torch.zeros((1, n2), device=dev) for _ in range(4)]
+    # A long replay: the same 4-launch graph (all three row-parallel linears, one of them twice) 2000 times with
+    # the inputs rewritten between replays (8 rotating input sets); every 100th replay is compared with the oracle.
+    # Every wait is bounded, so a lost word would end as a status code, not as a hang.
+    nsets = 8
+    xsets, wants = [], []
+    for si in range(nsets):
+        row = []
+        for i, (q2, s2, n2, k2, g2) in enumerate(lins):
+            x = synth.make_acts(1, k2, seed=5000 + 10 * si + i)
+            row.append(torch.from_numpy(shard.shard_acts(x, k2, "row", rank, world).view(np.float16).copy()).to(dev))
+            if rank == 0:
+                wants.append(oracle.linear_lane(q2, s2, x, 1, n2, k2, g2))
+        xsets.append(row)
+    xin = [torch.empty_like(t) for t in xsets[0]]
+    outs = [torch.zeros((1, lins[i][2]), device=dev) for i in (0, 1, 2, 0)]
     torch.cuda.synchronize()
     dist.barrier()
     with torch.cuda.stream(st):
+        for j, i in enumerate((0, 1, 2, 0)):
+            dec.sk_single_allreduce(f"ar{i}", xin[i], out=outs[j], t=1)       # warm
+        st.synchronize()
+        dist.barrier()
         dec.capture_begin()
-        for o in outs:
-            dec.sk_single_allreduce("ar0", xs, out=o, t=1)
+        for j, i in enumerate((0, 1, 2, 0)):
+            dec.sk_single_allreduce(f"ar{i}", xin[i], out=outs[j], t=1)
         gx = dec.capture_end()
-    for _ in range(5):
-        dec.graph_launch(gx)
-    dec.sync()
+        replays, checked = 2000, 0
+        for rep in range(replays):
+            si = rep % nsets
+            for i in range(3):
+                xin[i].copy_(xsets[si][i], non_blocking=True)
+            dec.graph_launch(gx)
+            if rep % 100 == 99 or rep == replays - 1:
+                dec.sync()
+                if rank == 0:
+                    for j, i in enumerate((0, 1, 2, 0)):
+                        err = float(np.abs(outs[j].cpu().numpy() - wants[si * 3 + i]).max())
+                        worst = max(worst, err)
+                        assert err <= 2e-3, (rep, j, err)
+                checked += 1
+        dec.sync()
+        dec.graph_destroy(gx)
     if rank == 0:
-        want = oracle.linear_lane(q2, s2, x, 1, n2, k2, g2)
-        for o in outs:
-            assert float(np.abs(o.cpu().numpy() - want).max()) <= 2e-3
-        print(f"fused all-reduce GEMV over {world} ranks (eager + graph replay): worst max err {worst:.2e}")
+        print(f"fused all-reduce GEMV over {world} ranks (eager + {replays} graph replays, {checked} checked): worst max err {worst:.2e}")
+    dist.barrier()
+    # A wait that runs out: with the limit shortened to 2^20 cycles (half a millisecond), rank 0 makes one fused
+    # launch that no peer joins.  Its wait gives up and the status call reports it; the kernel returns, the context
+    # stays usable.  Then every rank re-arms between two barriers and the next launches are correct again.
+    dec.set_tuning("tp_wait_log2", 20)
+    q2, s2, n2, k2, g2 = lins[0]
+    x = synth.make_acts(1, k2, seed=777)
+    xs = torch.from_numpy(shard.shard_acts(x, k2, "row", rank, world).view(np.float16).copy()).to(dev)
+    if rank == 0:
+        dec.sk_single_allreduce("ar0", xs, t=1)
+        gave_up = False
+        try:
+            dec.sync()
+        except Exception as e:   # W4a16Error: a bounded pipeline wait expired
+            gave_up = "wait expired" in str(e)
+        assert gave_up, "the lone launch should have reported an expired wait"
+    dist.barrier()
+    dec.tp_rearm()
+    dist.barrier()
+    dec.set_tuning("tp_wait_log2", 31)
+    for rep in range(3):
+        y = dec.sk_single_allreduce("ar0", xs, t=1)
+        dec.sync()
+        if rank == 0:
+            err = float(np.abs(y.cpu().numpy() - oracle.linear_lane(q2, s2, x, 1, n2, k2, g2)).max())
+            assert err <= 2e-3, ("after re-arm", rep, err)
+    if rank == 0:
+        print("expired wait reported, collective re-arm, next launches correct")
     dist.barrier()
     # expert-parallel MoE
     ne, kk, f, h, t = 16, 4, 128, 256, 40
