@@ -570,6 +570,13 @@ int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
         d.tune_gemm_mt = value;
         return 0;
     }
+    if (!strcmp(key, "gemm_ksplit")) {
+        if (value < 0 || value > 32) {
+            return d.fail("w4a16 tuning: gemm_ksplit must be 0..32");
+        }
+        d.tune_gemm_ksplit = value;
+        return 0;
+    }
     if (!strcmp(key, "gemv_cluster")) {
         d.tune_gemv_cluster = value != 0;
         return 0;

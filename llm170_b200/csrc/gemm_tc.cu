@@ -71,6 +71,12 @@ struct GemmArgs {
     int expert0;          // first expert held by this decoder
     const float* row_w;   // optional per-row factor applied in the epilogue (routing weight)
     float out_mul;        // power of two applied to every sum (undoes the shift of bf16 scales; normally 1)
+    // split-K (few tiles: small token counts): grid = tiles x ksplit, a CTA multiplies k-blocks
+    // [nkb*s/ksplit, nkb*(s+1)/ksplit); f32 partial tiles go to `part` and the last split to arrive (ticket per
+    // tile, left at zero) adds them in split order, converts and stores
+    int ksplit;
+    float* part;          // [tiles][ksplit][BM*MT][BN] f32
+    unsigned* counters;   // [tiles]
     int* status;  // 0 = ok; otherwise code<<16 | detail of the first wait that expired
     long long* dbg;  // optional timeline buffer (diagnostic), CTA 0 only
 };
@@ -125,6 +131,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
     extern __shared__ unsigned char smem_dyn[];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
+    __shared__ int s_last;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
@@ -142,9 +149,10 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
 
     // tile of this CTA (groups of GROUP_M m-tiles walk the n-tiles together)
     int m0, n0, rb0, rows_valid;
+    const int ks = a.ksplit, split = (int)blockIdx.x % ks, tile_id = (int)blockIdx.x / ks;
     if (a.grouped) {
         // consecutive CTAs walk the m-tiles of one n-tile: neighbours share an expert's weight tile in L2
-        const int mt = blockIdx.x % a.m_tiles, n_tile = blockIdx.x / a.m_tiles;
+        const int mt = tile_id % a.m_tiles, n_tile = tile_id / a.m_tiles;
         if (mt >= *a.num_tiles) {
             return;  // the table is sized for the worst case
         }
@@ -154,7 +162,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
         rb0 = ((a.tile_expert[mt] - a.expert0) * a.n + n0) / TILE_ROWS;
     } else {
         // groups of GROUP_M m-tiles walk the n-tiles together
-        const int tile = blockIdx.x;
+        const int tile = tile_id;
         const int per_group = GROUP_M * a.n_tiles;
         const int grp = tile / per_group;
         const int first_m = grp * GROUP_M;
@@ -165,7 +173,9 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
         rb0 = n0 / TILE_ROWS;
         rows_valid = min(BMT, a.m - m0);
     }
-    const int nkb = a.k / BK;
+    const int nkb_all = a.k / BK;
+    const int kb0 = (int)((long long)nkb_all * split / ks);                 // this split's k-blocks: [kb0, kb0 + nkb)
+    const int nkb = (int)((long long)nkb_all * (split + 1) / ks) - kb0;
     const int nrbv = min(BN, a.n - n0) / TILE_ROWS;  // valid 16-row blocks in this tile
     // 128-token blocks of this tile that hold rows: an empty second block is neither fetched nor multiplied
     const int mt_live = (MT == 2 && rows_valid <= BM) ? 1 : MT;
@@ -214,11 +224,11 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
 #pragma unroll
                 for (int mt = 0; mt < MT; ++mt) {
                     if (mt < mt_live) {
-                        tma_load_2d(a_addr(s) + mt * A_BYTES, &tmap_x, it * BK, m0 + mt * BM, full_bar(s));
+                        tma_load_2d(a_addr(s) + mt * A_BYTES, &tmap_x, (kb0 + it) * BK, m0 + mt * BM, full_bar(s));
                     }
                 }
                 // the tile's row blocks are contiguous at one k-block (k-block-major layout): one copy
-                bulk_load(raw_addr(s), a.qt + ((size_t)it * a.nrb_w + rb0) * TILE_WORDS,
+                bulk_load(raw_addr(s), a.qt + ((size_t)(kb0 + it) * a.nrb_w + rb0) * TILE_WORDS,
                           nrbv * (TILE_WORDS * 4), full_bar(s));
             }
         }
@@ -270,12 +280,13 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
         auto load_scales = [&](int it, uint32_t (&sc)[2]) {
             sc[0] = sc[1] = 0;
             if (dw < nrbv && it < nkb) {
+                const int kbi = kb0 + it;
                 const uint32_t* sp = a.st + ((size_t)(rb0 + dw) * ng) * 8 + g;
                 if (GROUP >= BK) {
-                    sc[0] = sc[1] = __ldg(sp + (size_t)(it * BK / GROUP) * 8);
+                    sc[0] = sc[1] = __ldg(sp + (size_t)(kbi * BK / GROUP) * 8);
                 } else {
-                    sc[0] = __ldg(sp + (size_t)(it * 2) * 8);
-                    sc[1] = __ldg(sp + (size_t)(it * 2 + 1) * 8);
+                    sc[0] = __ldg(sp + (size_t)(kbi * 2) * 8);
+                    sc[1] = __ldg(sp + (size_t)(kbi * 2 + 1) * 8);
                 }
             }
         };
@@ -350,7 +361,20 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                     const float rw = (a.row_w != nullptr && row_l < rows_valid) ? a.row_w[row] : 1.0f;
                     uint32_t v[32];
                     tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * 256 + c0), v);
-                    if (row_l < rows_valid) {
+                    if (ks > 1) {
+                        // split-K: the f32 sums of this split go to scratch as they are
+                        if (row_l < rows_valid) {
+                            float4* pp = reinterpret_cast<float4*>(
+                                a.part + ((size_t)tile_id * ks + split) * (size_t)(BMT * BN) + (size_t)row_l * BN + c0);
+#pragma unroll
+                            for (int i = 0; i < 32; i += 4) {
+                                if (c0 + i < ncols) {
+                                    pp[i / 4] = make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]),
+                                                            __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                                }
+                            }
+                        }
+                    } else if (row_l < rows_valid) {
                         if (a.out_mul != 1.0f) {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
@@ -399,10 +423,64 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
     if (stamp && threadIdx.x == 64) {
         a.dbg[4002] = clock64();
     }
+    if (ks > 1) {
+        __threadfence();   // this thread's partial sums, before the ticket below
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+    if (ks > 1) {
+        // the last split of this tile to arrive adds all partial tiles in split order (the same bits whatever the
+        // arrival order), converts and stores; its ticket goes back to zero for the next launch
+        if (threadIdx.x == 0) {
+            int last = 0;
+            if (!*abort_flag) {
+                last = atomicAdd(a.counters + tile_id, 1u) == (unsigned)ks - 1u;
+                __threadfence();
+            }
+            s_last = last;
+        }
+        __syncthreads();
+        if (s_last) {
+            const int ncols = min(BN, a.n - n0), c4n = ncols / 4;
+            const float* base_p = a.part + (size_t)tile_id * ks * (size_t)(BMT * BN);
+            for (int idx = threadIdx.x; idx < rows_valid * c4n; idx += NUM_THREADS) {
+                const int row_l = idx / c4n, c = (idx - row_l * c4n) * 4;
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sp = 0; sp < ks; ++sp) {
+                    const float4 pv = __ldcg(reinterpret_cast<const float4*>(base_p + (size_t)sp * (BMT * BN) +
+                                                                             (size_t)row_l * BN + c));
+                    sum.x += pv.x;
+                    sum.y += pv.y;
+                    sum.z += pv.z;
+                    sum.w += pv.w;
+                }
+                const int row = m0 + row_l;
+                float o4[4] = {sum.x * a.out_mul, sum.y * a.out_mul, sum.z * a.out_mul, sum.w * a.out_mul};
+                if (a.row_w != nullptr) {
+                    const float rw = a.row_w[row];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        o4[i] = mul_row_w(o4[i], rw);
+                    }
+                }
+                if (a.out_f16) {
+                    const __half2 h0 = __floats2half2_rn(o4[0], o4[1]), h1 = __floats2half2_rn(o4[2], o4[3]);
+                    uint2 pk;
+                    pk.x = *reinterpret_cast<const uint32_t*>(&h0);
+                    pk.y = *reinterpret_cast<const uint32_t*>(&h1);
+                    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(a.out) + (size_t)row * a.n + n0 + c) = pk;
+                } else {
+                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(a.out) + (size_t)row * a.n + n0 + c) =
+                        make_float4(o4[0], o4[1], o4[2], o4[3]);
+                }
+            }
+            if (threadIdx.x == 0) {
+                a.counters[tile_id] = 0;
+            }
+        }
     }
 }
 
@@ -475,7 +553,40 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.out_mul = l->out_mul;
     a.status = gemm_status;
     a.dbg = dbg_buf;
-    const int grid = a.m_tiles * a.n_tiles;
+    // Few tiles (a handful of tokens, or a narrow linear): split K so that about one CTA per SM streams weights.
+    // At least four k-blocks per split; the f32 partial tiles must fit 64 MB of scratch.
+    const int tiles = a.m_tiles * a.n_tiles;
+    int ks = 1;
+    if (tune_gemm_ksplit > 0) {
+        ks = tune_gemm_ksplit;
+    } else if (tiles * 4 < sm_count * 3) {
+        ks = sm_count / tiles;
+    }
+    const int nkb_all = l->k / BK;
+    if (ks > nkb_all / 4) {
+        ks = nkb_all / 4;
+    }
+    if (ks > 32) {
+        ks = 32;
+    }
+    const size_t tile_floats = (size_t)BM * mt * BN;
+    while (ks > 1 && (size_t)tiles * ks * tile_floats * sizeof(float) > (64u << 20)) {
+        --ks;
+    }
+    if (ks < 1 || tiles > 4096) {
+        ks = 1;
+    }
+    a.ksplit = ks;
+    a.part = nullptr;
+    a.counters = nullptr;
+    if (ks > 1) {
+        if (int rc = ensure_scratch((size_t)tiles * ks * tile_floats, tiles, st)) {
+            return rc;
+        }
+        a.part = part;
+        a.counters = counters;
+    }
+    const int grid = tiles * ks;
     if (l->group == 128) {
         if (mt == 2) {
             gemm_w4a16_tc_kernel<128, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, a);
@@ -493,7 +604,8 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     if (e != cudaSuccess) {
         return cuda_fail("launch gemm", e);
     }
-    last_kernel = "gemm_w4a16_tc_kernel<" + std::to_string(l->group) + "," + std::to_string(mt) + ">";
+    last_kernel = "gemm_w4a16_tc_kernel<" + std::to_string(l->group) + "," + std::to_string(mt) + ">" +
+                  (ks > 1 ? " split-K " + std::to_string(ks) : std::string());
     launches++;
     return 0;
 }
@@ -536,6 +648,9 @@ int Dec::gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int 
     a.expert0 = moe.e0;
     a.row_w = row_w;
     a.out_mul = l->out_mul;
+    a.ksplit = 1;
+    a.part = nullptr;
+    a.counters = nullptr;
     a.status = gemm_status;
     a.dbg = nullptr;
     const int grid = a.m_tiles * a.n_tiles;

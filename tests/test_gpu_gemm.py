@@ -92,10 +92,12 @@ def test_tile_variants_agree_bitwise(dec):
     dec.upload_lin_g("mtv", q, s, n, k, 128)
     x = x_dev(synth.make_acts(t, k, seed=62, scale=1 / np.sqrt(k)))
     outs = []
+    dec.set_tuning("gemm_ksplit", 1)          # one K range per tile: the tile variants then add in the same order
     for mt in (1, 2):
         dec.set_tuning("gemm_mt", mt)
         outs.append(dec.lin_forward("mtv", x, t).clone())
     dec.set_tuning("gemm_mt", 0)
+    dec.set_tuning("gemm_ksplit", 0)
     dec.sync()
     assert torch.equal(outs[0], outs[1])      # same k order per output element -> same bits
 
@@ -149,3 +151,46 @@ def test_config3_prefill_shapes_full_size(dec, orc, name, m):
     dec.sync()
     assert torch.equal(y16, y.to(torch.float16))
     dec.drop_lin("c3")
+
+
+# Split-K form of the GEMM (few tiles: the small-batch band above the decode GEMV, narrow linears): the partial
+# tiles are added in split order by the last split to arrive, so forced splits reproduce the exact-arithmetic
+# known answers bit for bit, twice in a row.
+@pytest.mark.parametrize("t,k,n,group,ks", [(9, 1024, 128, 128, 4), (16, 2048, 272, 128, 8), (33, 1024, 512, 32, 3),
+                                            (300, 1024, 272, 128, 2), (64, 4096, 256, 128, 16)])
+def test_split_k_gemm_pow2_exact_and_repeatable(dec, t, k, n, group, ks):
+    q, s, x, expect = pow2_case(t, k, n, group)
+    dec.upload_lin_g("p2k", q, s, n, k, group)
+    dec.set_tuning("gemm_ksplit", ks)
+    try:
+        y = dec.lin_forward("p2k", x_dev(x), t).clone()
+        y2 = dec.lin_forward("p2k", x_dev(x), t)
+        dec.sync()
+        assert "split-K" in dec.last_kernel()
+    finally:
+        dec.set_tuning("gemm_ksplit", 0)
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), expect.view(np.uint32))
+    assert torch.equal(y, y2)
+
+
+# The small-batch band of the reference's FFMA family (crates/backend-gpu/src/rawcuda/assets/gptq4.cu:458-951,
+# T <= 32, and the MTP verify width 9 of crates/backend-gpu/src/rawcuda/w4a16_dec/chains.rs:315-507) on the
+# baseline's layer shapes: one call each, all tokens, rows spread over the output, against the lane oracle.
+@pytest.mark.parametrize("name", ["qkv", "o_proj", "gate_up", "down"])
+@pytest.mark.parametrize("t", [9, 16, 32])
+def test_small_batch_band_on_layer_shapes(dec, orc, name, t):
+    k, n = synth.DENSE_27B[name]
+    q, s = synth.make_linear_cuda(n, k, 128, seed=77, device=torch.device("cuda", 0))
+    dec.upload_lin_g_dev("sb", q, s, n, k, 128)
+    x = synth.make_acts(t, k, seed=t)
+    y = dec.lin_forward("sb", x_dev(x), t)
+    dec.sync()
+    qh, sh = q.cpu().numpy().view(np.uint32), s.cpu().numpy().view(np.uint16)
+    got = y.cpu().numpy()
+    scale = 0.0
+    for r0 in (0, (n // 2) // 16 * 16, n - 64):
+        want = orc.linear_lane(qh, sh, x, t, n, k, 128, rows=(r0, r0 + 64))
+        scale = max(scale, float(np.abs(want).max()))
+        # N(0,1) activations: |y| reaches ~10, and the GEMM multiplies weights rounded once to f16 (relative 2^-11)
+        assert np.abs(got[:, r0:r0 + 64] - want[:, r0:r0 + 64]).max() <= TOL * max(1.0, scale)
+    dec.drop_lin("sb")
