@@ -131,12 +131,27 @@ W4A16_API int w4a16_dequant_lin(w4a16_dec* dec, const char* name, void* out_dev,
  * crates/backend-gpu/src/rawcuda/w4a16_dec/prefill.rs:81-345). */
 W4A16_API int w4a16_lin_forward(w4a16_dec* dec, const char* name, const void* x16_dev, void* dst_dev, int t,
                       int out_kind, void* stream);
+/* lin_forward for callers that hold f32 activations, as the reference's FFMA paths do (x f32 holding f16 values,
+ * crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/gemv.rs:4-38; cast kernel w4a16_cast_f16,
+ * crates/backend-gpu/src/rawcuda/assets/moepp.cu:36-51): rounds x32[t][k] to f16 into a staging buffer of the
+ * decoder (grown outside graph capture only), then runs w4a16_lin_forward on it. */
+W4A16_API int w4a16_lin_forward_x32(w4a16_dec* dec, const char* name, const float* x32_dev, void* dst_dev, int t,
+                                    int out_kind, void* stream);
+/* The parity-gate kernel: dst[t][n] f32 computed in the lane order of crates/core/src/quant/lane.rs:2-70 (64 f32
+ * lane accumulators, un-fused multiply and add, f64 tree), bit-identical to the CPU lane dot for every t. Takes the
+ * place of the reference's FFMA mirror w4a16_gemm_g128 / w4a16_gemm_g32_bf16
+ * (crates/backend-gpu/src/rawcuda/assets/gptq4.cu:825-951), which the gate
+ * crates/server/src/probes/w4a16/gates.rs:108-138 compares bit for bit. A checking tool, not a fast path. */
+W4A16_API int w4a16_lin_forward_lane(w4a16_dec* dec, const char* name, const void* x16_dev, float* dst_dev, int t,
+                                     void* stream);
 /* W4a16Dec::sk_single_dev (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:89-127):
  * the decode GEMV on one linear, t in 1..8. */
 W4A16_API int w4a16_sk_single_dev(w4a16_dec* dec, const char* name, const void* x16_dev, void* out_dev, int t,
                         int out_kind, void* stream);
 /* W4a16Dec::sk_multi_dev (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:23-57): up to
- * four linears that share x and k (q|k|v, gate|up) in ONE launch; outs[i] is [t][n_i]. */
+ * four linears that share x and k (q|k|v, gate|up) in ONE launch for t <= 8; outs[i] is [t][n_i]. Above 8 rows
+ * (gemv_multi_t_dev of the batch-decode chain, crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/gemv.rs:272-300)
+ * each segment runs through the tensor-core GEMM. */
 W4A16_API int w4a16_sk_multi_dev(w4a16_dec* dec, const char* const* names, int n_seg, const void* x16_dev,
                        void* const* outs_dev, int t, int out_kind, void* stream);
 /* The decode GEMV of w4a16_sk_single_dev for hosts that must not allocate device memory (an engine that

@@ -36,6 +36,8 @@ _SIGS = {
     "w4a16_unpack_lin": (_i, [_vp, C.c_char_p, _vp, _vp, _vp]),
     "w4a16_dequant_lin": (_i, [_vp, C.c_char_p, _vp, _i, _vp]),
     "w4a16_lin_forward": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
+    "w4a16_lin_forward_x32": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
+    "w4a16_lin_forward_lane": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _vp]),
     "w4a16_sk_single_dev": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
     "w4a16_sk_single_static": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
     "w4a16_tp_create": (_i, [_vp, _i, _i, _i, _vp]),

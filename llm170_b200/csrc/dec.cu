@@ -492,6 +492,9 @@ void w4a16_dec_free(w4a16_dec* dec) {
     if (d.xh) {
         cudaFree(d.xh);
     }
+    if (d.x16) {
+        cudaFree(d.x16);
+    }
     if (d.yh) {
         cudaFree(d.yh);
     }
@@ -909,6 +912,16 @@ int w4a16_sk_multi_dev(w4a16_dec* dec, const char* const* names, int n_seg, cons
             return 1;
         }
     }
+    if (t > w4::GEMV_MAX_M) {
+        // the small-batch band above the decode GEMV (batch decode and speculative verify run q|k|v and gate|up at up
+        // to 32 rows: crates/backend-gpu/src/rawcuda/w4a16_dec/chains.rs:315-507): one GEMM per segment
+        for (int i = 0; i < n_seg; ++i) {
+            if (int rc = d.gemm(ls[i], x16_dev, outs_dev[i], t, out_kind, pick_stream(dec, stream))) {
+                return rc;
+            }
+        }
+        return 0;
+    }
     return d.gemv(ls, n_seg, x16_dev, outs_dev, t, out_kind, pick_stream(dec, stream));
 }
 
@@ -929,6 +942,58 @@ int w4a16_lin_forward(w4a16_dec* dec, const char* name, const void* x16_dev, voi
         return d.gemv(ls, 1, x16_dev, outs, t, out_kind, st);
     }
     return d.gemm(l, x16_dev, dst_dev, t, out_kind, st);
+}
+
+int w4a16_lin_forward_lane(w4a16_dec* dec, const char* name, const void* x16_dev, float* dst_dev, int t, void* stream) {
+    Dec& d = dec->d;
+    Lin* l = find_lin(d, name);
+    if (!l) {
+        return 1;
+    }
+    if (t < 1 || t > 65535) {
+        return d.fail("w4a16 lin_forward_lane %s: t=%d", name, t);
+    }
+    w4::launch_lane_mirror(l->qt, l->st, x16_dev, dst_dev, l->n, l->k, l->group, t, l->out_mul, pick_stream(dec, stream));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        return d.cuda_fail("launch lane mirror", e);
+    }
+    d.last_kernel = "lane_mirror_kernel";
+    d.launches++;
+    return 0;
+}
+
+int w4a16_lin_forward_x32(w4a16_dec* dec, const char* name, const float* x32_dev, void* dst_dev, int t, int out_kind,
+                          void* stream) {
+    Dec& d = dec->d;
+    Lin* l = find_lin(d, name);
+    if (!l) {
+        return 1;
+    }
+    if (t < 1) {
+        return d.fail("w4a16 lin_forward_x32 %s: t=%d", name, t);
+    }
+    cudaStream_t st = pick_stream(dec, stream);
+    const size_t xb = (size_t)t * l->k * 2;
+    if (xb > d.x16_cap) {
+        if (Dec::capturing(st)) {
+            return d.fail("w4a16 lin_forward_x32: staging too small during graph capture; run the call once before capturing");
+        }
+        cudaDeviceSynchronize();
+        if (d.x16) {
+            d.retired.push_back(d.x16);   // a captured graph may still name it
+        }
+        d.x16 = nullptr;
+        d.x16_cap = 0;
+        cudaError_t e = cudaMalloc(&d.x16, xb);
+        if (e != cudaSuccess) {
+            return d.cuda_fail("alloc f16 staging", e);
+        }
+        d.x16_cap = xb;
+    }
+    w4::launch_cast_f16(x32_dev, d.x16, (size_t)t * l->k, st);
+    d.launches++;
+    return w4a16_lin_forward(dec, name, d.x16, dst_dev, t, out_kind, stream);
 }
 
 int w4a16_lin_forward_host(w4a16_dec* dec, const char* name, const void* x16_host, void* dst_host, int t,

@@ -68,6 +68,8 @@ struct Dec {
     size_t xh_cap = 0;
     void* yh = nullptr;
     size_t yh_cap = 0;
+    void* x16 = nullptr;         // f16 copy of f32 activations (w4a16_lin_forward_x32)
+    size_t x16_cap = 0;
     // knobs
     int tune_gemv_stages = 4;
     int tune_gemv_warps = 8;

@@ -24,6 +24,11 @@ void launch_unpack_s(const uint16_t* stl, uint16_t* s_orig, int n, int k, int gr
 void launch_dequant(const uint32_t* qt, const uint16_t* stl, void* out, int n, int k, int group,
                     int out_f16, float out_mul, cudaStream_t st);
 
+// lane-order mirror of the CPU dot (parity gates): out f32 [t][n], x16 f16 [t][k]
+void launch_lane_mirror(const uint32_t* qt, const uint16_t* stl, const void* x16, float* out, int n, int k, int group,
+                        int t, float out_mul, cudaStream_t st);
+void launch_cast_f16(const float* x, void* y16, size_t total, cudaStream_t st);
+
 // ---- gemv.cu ---------------------------------------------------------------------------------
 constexpr int GEMV_MAX_SEG = 4;
 constexpr int GEMV_MAX_M = 8;

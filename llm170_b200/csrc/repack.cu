@@ -174,6 +174,55 @@ __global__ void dequant_kernel(const uint32_t* __restrict__ qt, const uint16_t* 
     }
 }
 
+// Lane-order mirror of the CPU dot product, for parity gates: one warp per output element keeps the 64 f32 lane
+// accumulators of crates/core/src/quant/lane.rs:42-70 (lane l owns elements i = l mod 64, in increasing i, with the
+// multiply and the add rounded separately), two per thread, and combines them in f64 with the fixed tree of
+// lane.rs:2-13 (i += i+32, then offsets 16, 8, 4, 2, 1).  Bit-identical to the reference's lane dot for any
+// token count; it plays the role of the reference's FFMA mirror kernel w4a16_gemm_g128
+// (crates/backend-gpu/src/rawcuda/assets/gptq4.cu:825-951), which its gate compares bit for bit with lane.rs.
+__global__ void lane_mirror_kernel(const uint32_t* __restrict__ qt, const uint16_t* __restrict__ stl,
+                                   const __half* __restrict__ x, float* __restrict__ out, int n, int k, int group,
+                                   float out_mul) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + warp, tok = blockIdx.y;
+    if (row >= n) {
+        return;
+    }
+    const int ng = k / group;
+    const int rb = row / TILE_ROWS, rr = row % TILE_ROWS;
+    const uint16_t* srow = stl + ((size_t)rb * ng * 8 + (rr & 7)) * 2 + (rr >> 3);   // + grp * 16
+    const __half* xr = x + (size_t)tok * k;
+    float acc[2] = {0.f, 0.f};
+    for (int i0 = 0; i0 < k; i0 += 64) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int i = i0 + lane + 32 * h;
+            int pos;
+            const size_t wi = word_index(row, i, n, &pos);
+            const int nib = (int)((qt[wi] >> (4 * pos)) & 0xFu);
+            const float sc = __half2float(__ushort_as_half(srow[(size_t)(i / group) * 16])) * out_mul;
+            const float w = __fmul_rn((float)(nib - 8), sc);
+            acc[h] = __fadd_rn(acc[h], __fmul_rn(w, __half2float(xr[i])));
+        }
+    }
+    double a = (double)acc[0] + (double)acc[1];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        a += __shfl_down_sync(0xffffffffu, a, off);
+    }
+    if (lane == 0) {
+        out[(size_t)tok * n + row] = (float)a;
+    }
+}
+
+// f32 activations -> f16 (round to nearest even; exact for the f16-valued f32 the reference's norm kernels emit),
+// the role of w4a16_cast_f16 (crates/backend-gpu/src/rawcuda/assets/moepp.cu:36-51)
+__global__ void cast_f16_kernel(const float* __restrict__ x, __half* __restrict__ y, size_t total) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        y[i] = __float2half_rn(x[i]);
+    }
+}
+
 inline int grid_for(size_t total) {
     size_t b = (total + 255) / 256;
     if (b > 148 * 32) {
@@ -186,6 +235,13 @@ inline int grid_for(size_t total) {
 
 void launch_repack_q(const uint32_t* q, uint32_t* qt, int n, int k, cudaStream_t st) {
     repack_q_kernel<<<grid_for((size_t)n * (k / 8)), 256, 0, st>>>(q, qt, n, k);
+}
+void launch_lane_mirror(const uint32_t* qt, const uint16_t* stl, const void* x16, float* out, int n, int k, int group,
+                        int t, float out_mul, cudaStream_t st) {
+    lane_mirror_kernel<<<dim3((n + 7) / 8, t), 256, 0, st>>>(qt, stl, (const __half*)x16, out, n, k, group, out_mul);
+}
+void launch_cast_f16(const float* x, void* y16, size_t total, cudaStream_t st) {
+    cast_f16_kernel<<<grid_for(total), 256, 0, st>>>(x, (__half*)y16, total);
 }
 void launch_scale_range(const uint16_t* s, size_t total, int* range2, cudaStream_t st) {
     scale_range_kernel<<<grid_for(total), 256, 0, st>>>(s, total, range2);

@@ -154,6 +154,28 @@ class W4a16Dec:
                                            OUT_F16 if out_f16 else OUT_F32, _cur_stream()))
         return dst
 
+    def lin_forward_x32(self, name: str, x32: torch.Tensor, t: int, dst: torch.Tensor | None = None,
+                        out_f16: bool = False) -> torch.Tensor:
+        """lin_forward on f32 activations (kernels/gemv.rs:4-38 takes x as f32 holding f16 values)."""
+        n, k, _ = self.lin_spec(name)
+        self._tensor_ok(x32, torch.float32, "x32")
+        if x32.numel() != t * k:
+            raise W4a16Error(f"lin_forward_x32 {name}: x has {x32.numel()} elements, need {t}x{k}")
+        dst = self._out(t, n, out_f16, dst)
+        self._ck(self._L.w4a16_lin_forward_x32(self._h, name.encode(), x32.data_ptr(), dst.data_ptr(), t,
+                                               OUT_F16 if out_f16 else OUT_F32, _cur_stream()))
+        return dst
+
+    def lin_forward_lane(self, name: str, x16: torch.Tensor, t: int) -> torch.Tensor:
+        """The parity-gate kernel (gptq4.cu:825-951): f32 [t,n] in the CPU lane order, bit-identical to lane.rs."""
+        n, k, _ = self.lin_spec(name)
+        self._tensor_ok(x16, torch.float16, "x16")
+        if x16.numel() != t * k:
+            raise W4a16Error(f"lin_forward_lane {name}: x has {x16.numel()} elements, need {t}x{k}")
+        dst = self._out(t, n, False, None)
+        self._ck(self._L.w4a16_lin_forward_lane(self._h, name.encode(), x16.data_ptr(), dst.data_ptr(), t, _cur_stream()))
+        return dst
+
     def sk_single_dev(self, name: str, x16: torch.Tensor, out: torch.Tensor | None = None, t: int = 1,
                       out_f16: bool = False) -> torch.Tensor:
         """kernels/decode.rs:89-127: split-K decode GEMV on one linear."""

@@ -403,3 +403,43 @@ def test_group64_and_bf16_scales(dec, orc, group, bf16, sigma):
         sf = (s.astype(np.uint32) << 16).view(np.float32) if bf16 else s.view(np.float16).astype(np.float32)
         assert np.array_equal(s2.cpu().numpy().astype(np.float32), sf)
     dec.drop_lin("var")
+
+
+@pytest.mark.parametrize("n,k,group,bf16,t", [(64, 5120, 128, False, 8), (64, 6144, 128, False, 1), (48, 2048, 32, True, 8),
+                                              (32, 768, 64, False, 3), (64, 17408, 128, False, 32)])
+def test_lane_mirror_is_bit_identical_to_the_cpu_lane(dec, orc, n, k, group, bf16, t):
+    # the reference's gate (crates/server/src/probes/w4a16/gates.rs:108-138): first rows of a linear, x uniform in
+    # [-1,1) rounded to f16, every output of the mirror kernel BIT-IDENTICAL to dot_row_w4a16_lane_group
+    q, s = synth.make_linear(n, k, group, seed=600 + t, scale_bf16=bf16)
+    rng = np.random.default_rng(t)
+    x = (rng.random((t, k), dtype=np.float32) * 2 - 1).astype(np.float16).view(np.uint16)
+    dec.upload_lin_g("lm", q, s, n, k, group, scale_bf16=bf16)
+    got = dec.lin_forward_lane("lm", x_dev(x), t)
+    dec.sync()
+    want = orc.linear_lane(q, s, x, t, n, k, group, scale_bf16=bf16)
+    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    # and the fast kernels agree with it within the gate
+    fast = dec.lin_forward("lm", x_dev(x), t)
+    dec.sync()
+    assert (fast - got).abs().max().item() <= TOL
+    dec.drop_lin("lm")
+
+
+def test_f32_activation_entry_and_multi_segment_above_eight_rows(dec, orc):
+    k = 1024
+    segs = [("q16", 512), ("k16", 128), ("v16", 144)]
+    xs = synth.make_acts(16, k, seed=21)
+    x = x_dev(xs)
+    for i, (nm, n) in enumerate(segs):
+        q, s = synth.make_linear(n, k, 128, seed=70 + i)
+        dec.upload_lin_g(nm, q, s, n, k, 128)
+    outs = dec.sk_multi_dev([nm for nm, _ in segs], x, t=16)               # batch decode: q|k|v at 16 rows
+    for (nm, n), o in zip(segs, outs):
+        assert torch.equal(o, dec.lin_forward(nm, x, 16))
+    # f32 activations holding f16 values: the same bits as the f16 entry, for the GEMV and the GEMM band
+    x32 = x.float()
+    for t in (1, 8, 16):
+        a = dec.lin_forward_x32("q16", x32[:t].contiguous(), t)
+        b = dec.lin_forward("q16", x[:t].contiguous(), t)
+        dec.sync()
+        assert torch.equal(a, b)
