@@ -16,7 +16,7 @@
  *     CUDA graph (crates/backend-gpu/src/rawcuda/ctx/graph.rs:4-65).
  * Weight format at the boundary (compressed-tensors pack-quantized, crates/core/src/w4a16.rs:124-175):
  *   q: little-endian u32 [n][k/8], element i of a row = nibble at bits 4*(i&7) of word i>>3, value q+8
- *   s: f16 (or bf16) [n][k/group], group in {128, 32};  dequantised weight = (nibble-8)*scale.
+ *   s: f16 (or bf16) [n][k/group], group in {128, 64, 32};  dequantised weight = (nibble-8)*scale.
  */
 #ifndef W4A16_B200_H
 #define W4A16_B200_H
@@ -35,6 +35,10 @@ extern "C" {
 #endif
 
 typedef struct w4a16_dec w4a16_dec;
+/* a mapped safetensors archive (w4a16_st_open) */
+typedef struct w4a16_st w4a16_st;
+/* chunk callback of w4a16_upload_lin_g_stream */
+typedef void (*w4a16_fill_fn)(void* user, int which, size_t off, void* dst, size_t len);
 
 /* Output element type of a forward call. The reference writes f32 (dst of lin_forward). */
 #define W4A16_OUT_F32 0
@@ -105,6 +109,14 @@ W4A16_API int w4a16_upload_lin_g(w4a16_dec* dec, const char* name, const void* q
  * produced on the device; the reference has no such variant). */
 W4A16_API int w4a16_upload_lin_g_dev(w4a16_dec* dec, const char* name, const void* q_dev, const void* s_dev, int n,
                            int k, int group, int scale_bf16);
+/* W4a16Dec::upload_lin_g_stream (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:1643; experts
+ * upload_experts_resident_streamed, :1021-1082): the caller does not hold the linear as one host slice but fills
+ * chunks on request. `fill(user, which, off, dst, len)` must write bytes [off, off+len) of q (which == 0) or of s
+ * (which == 1) to dst, a pinned buffer of the decoder; it is called for whole rows, in 8 MiB chunks, and twice over
+ * the scales when they are bf16. Every chunk is re-tiled into place as it arrives, so the load needs neither the
+ * whole host slice nor a second copy of the linear on the device (w4a16_upload_lin_g is built on this call). */
+W4A16_API int w4a16_upload_lin_g_stream(w4a16_dec* dec, const char* name, int n, int k, int group, int scale_bf16,
+                                        w4a16_fill_fn fill, void* user);
 /* W4a16Dec::lin_spec (crates/backend-gpu/src/rawcuda/w4a16_dec/mod.rs:1193): n and k, plus the
  * group size; non-zero if `name` is unknown. */
 W4A16_API int w4a16_lin_spec(w4a16_dec* dec, const char* name, int* n, int* k, int* group);
@@ -122,6 +134,34 @@ W4A16_API int w4a16_unpack_lin(w4a16_dec* dec, const char* name, void* q_dev, vo
  * out_kind W4A16_OUT_F32 -> (nibble-8)*scale exactly as crates/core/src/matmul/cpu.rs:167-194;
  * W4A16_OUT_F16 -> that value rounded once to f16, the operand the tensor-core GEMM multiplies. */
 W4A16_API int w4a16_dequant_lin(w4a16_dec* dec, const char* name, void* out_dev, int out_kind, void* stream);
+
+/* ---- checkpoints and the tile cache -------------------------------------------------------- */
+
+/* StArchive::open (crates/core/src/st.rs:115-290) + the triple scan of W4a16Model::open
+ * (crates/core/src/w4a16.rs:108-191): maps a .safetensors file, or every model*.safetensors of a directory,
+ * checks each header entry (dtype, shape x element size == data_offsets, inside the file) and collects the
+ * linears: every `<base>.weight_packed` (I32 [n, k/8]) with `<base>.weight_scale` (F16 / BF16 [n, k/group],
+ * group 32, 64 or 128) and `<base>.weight_shape` (I64 [2] = n, k). Needs no device. Errors: w4a16_st_error(). */
+W4A16_API int w4a16_st_open(const char* path, w4a16_st** out);
+W4A16_API void w4a16_st_close(w4a16_st* st);
+W4A16_API const char* w4a16_st_error(void);
+/* W4a16Model::lins (crates/core/src/w4a16.rs:170-175): number of linears, and the i-th one in name order. */
+W4A16_API int w4a16_st_lin_count(const w4a16_st* st);
+W4A16_API int w4a16_st_lin_at(const w4a16_st* st, int i, char* base_out, size_t cap, int* n, int* k, int* group,
+                              int* scale_bf16);
+/* 64-bit FNV-1a over a linear's shape, packed weights and scales: names what a cache file was made from. It has
+ * no counterpart in the reference, which keeps no weight cache (its prebuilt kernel binaries are guarded by a
+ * hash manifest in the same spirit, scripts/preflight.sh). */
+W4A16_API int w4a16_st_lin_tag(const w4a16_st* st, const char* base, uint64_t* tag);
+/* upload_model's per-linear step (crates/server/src/gpu_engine/upload.rs:264-305): streams linear `base` of the
+ * archive to the device under `name`, straight from the mapped file. */
+W4A16_API int w4a16_upload_lin_st(w4a16_dec* dec, const char* name, const w4a16_st* st, const char* base);
+/* Tile cache (no counterpart in the reference, which re-runs its host repack at every load:
+ * crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:99-179). save writes the resident tiles of `name` with a
+ * header (shape, groups, layout version, source_tag); load puts a linear back with plain host-to-device copies --
+ * no staging copy, no repack -- and refuses a file of another layout version or another source_tag. */
+W4A16_API int w4a16_save_lin_cache(w4a16_dec* dec, const char* name, const char* path, uint64_t source_tag);
+W4A16_API int w4a16_load_lin_cache(w4a16_dec* dec, const char* name, const char* path, uint64_t source_tag);
 
 /* ---- linear forward ---------------------------------------------------------------------- */
 

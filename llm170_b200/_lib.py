@@ -30,6 +30,16 @@ _SIGS = {
     "w4a16_check_shapes": (_i, [_sz] * 7),
     "w4a16_upload_lin_g": (_i, [_vp, C.c_char_p, _vp, _sz, _vp, _sz, _i, _i, _i, _i]),
     "w4a16_upload_lin_g_dev": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _i, _i]),
+    "w4a16_upload_lin_g_stream": (_i, [_vp, C.c_char_p, _i, _i, _i, _i, _vp, _vp]),
+    "w4a16_st_open": (_i, [C.c_char_p, C.POINTER(_vp)]),
+    "w4a16_st_close": (None, [_vp]),
+    "w4a16_st_error": (C.c_char_p, []),
+    "w4a16_st_lin_count": (_i, [_vp]),
+    "w4a16_st_lin_at": (_i, [_vp, _i, C.c_char_p, _sz, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
+    "w4a16_st_lin_tag": (_i, [_vp, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "w4a16_upload_lin_st": (_i, [_vp, C.c_char_p, _vp, C.c_char_p]),
+    "w4a16_save_lin_cache": (_i, [_vp, C.c_char_p, C.c_char_p, C.c_uint64]),
+    "w4a16_load_lin_cache": (_i, [_vp, C.c_char_p, C.c_char_p, C.c_uint64]),
     "w4a16_lin_spec": (_i, [_vp, C.c_char_p, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     "w4a16_drop_lin": (_i, [_vp, C.c_char_p]),
     "w4a16_weights_bytes": (_sz, [_vp]),
@@ -64,6 +74,9 @@ def declared_symbols() -> list[str]:
     """Every entry point the public header declares."""
     text = open(HEADER).read()
     return sorted(set(re.findall(r"W4A16_API\s+[\w\s\*]+?\b(w4a16_\w+)\s*\(", text)))
+
+
+FILL_FN = C.CFUNCTYPE(None, _vp, _i, _sz, _vp, _sz)   # w4a16_fill_fn
 
 
 def lib() -> C.CDLL:

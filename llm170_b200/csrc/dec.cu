@@ -495,6 +495,12 @@ void w4a16_dec_free(w4a16_dec* dec) {
     if (d.x16) {
         cudaFree(d.x16);
     }
+    if (d.pin) {
+        cudaFreeHost(d.pin);
+    }
+    if (d.stage_dev) {
+        cudaFree(d.stage_dev);
+    }
     if (d.yh) {
         cudaFree(d.yh);
     }
@@ -679,6 +685,17 @@ static int validate_upload(Dec& d, const char* name, size_t q_bytes, size_t s_by
     return 0;
 }
 
+namespace {
+struct SliceFill {
+    const unsigned char* q;
+    const unsigned char* s;
+};
+void slice_fill(void* user, int which, size_t off, void* dst, size_t len) {
+    const SliceFill* f = (const SliceFill*)user;
+    memcpy(dst, (which == 0 ? f->q : f->s) + off, len);
+}
+}  // namespace
+
 int w4a16_upload_lin_g(w4a16_dec* dec, const char* name, const void* q, size_t q_bytes, const void* s,
                        size_t s_bytes, int n, int k, int group, int scale_bf16) {
     Dec& d = dec->d;
@@ -686,30 +703,9 @@ int w4a16_upload_lin_g(w4a16_dec* dec, const char* name, const void* q, size_t q
     if (int rc = validate_upload(d, name, q_bytes, s_bytes, n, k, group)) {
         return rc;
     }
-    void *dq = nullptr, *ds = nullptr;
-    cudaError_t e = cudaMalloc(&dq, q_bytes);
-    if (e != cudaSuccess) {
-        return d.cuda_fail("alloc upload staging", e);
-    }
-    e = cudaMalloc(&ds, s_bytes);
-    if (e != cudaSuccess) {
-        cudaFree(dq);
-        return d.cuda_fail("alloc upload staging", e);
-    }
-    e = cudaMemcpyAsync(dq, q, q_bytes, cudaMemcpyHostToDevice, d.stream);
-    if (e == cudaSuccess) {
-        e = cudaMemcpyAsync(ds, s, s_bytes, cudaMemcpyHostToDevice, d.stream);
-    }
-    int rc = 0;
-    if (e != cudaSuccess) {
-        rc = d.cuda_fail("copy weights to device", e);
-    } else {
-        rc = d.upload_common(name, dq, ds, n, k, group, scale_bf16);
-    }
-    cudaStreamSynchronize(d.stream);
-    cudaFree(dq);
-    cudaFree(ds);
-    return rc;
+    // streamed in 8 MiB row chunks: no second full copy of the linear on the device
+    SliceFill f{(const unsigned char*)q, (const unsigned char*)s};
+    return d.upload_stream(name, n, k, group, scale_bf16, slice_fill, &f);
 }
 
 int w4a16_upload_lin_g_dev(w4a16_dec* dec, const char* name, const void* q_dev, const void* s_dev, int n,

@@ -4,6 +4,7 @@
 #include <string>
 #include <vector>
 
+#include "../../include/w4a16_b200.h"
 #include "internal.h"
 
 namespace w4 {
@@ -68,6 +69,9 @@ struct Dec {
     size_t xh_cap = 0;
     void* yh = nullptr;
     size_t yh_cap = 0;
+    void* pin = nullptr;         // pinned host ring (two slots) and its device twin for streamed uploads / cache reads
+    void* stage_dev = nullptr;
+    size_t pin_cap = 0;
     void* x16 = nullptr;         // f16 copy of f32 activations (w4a16_lin_forward_x32)
     size_t x16_cap = 0;
     // knobs
@@ -93,6 +97,7 @@ struct Dec {
     static bool capturing(cudaStream_t st);
     int ensure_scratch(size_t part_floats, int grid_x, cudaStream_t st);
     void free_lin(Lin& l);
+    int upload_stream(const char* name, int n, int k, int group, int scale_bf16, w4a16_fill_fn fill, void* user);
     int upload_common(const char* name, const void* q_dev, const void* s_dev, int n, int k, int group,
                       int scale_bf16);
     std::string last_kernel;   // instantiation launched by the last forward call

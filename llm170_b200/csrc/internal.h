@@ -17,6 +17,10 @@ void launch_scale_range(const uint16_t* s_orig, size_t total, int* range2, cudaS
 // exactly representable.
 void launch_repack_s(const uint16_t* s_orig, uint16_t* stl, int n, int k, int group, int src_div, int scale_bf16,
                      int shift, int* err_flag, cudaStream_t st);
+// the same for a chunk of source rows [16*rb0, 16*(rb0+nrbc)) (streamed uploads)
+void launch_repack_q_rows(const uint32_t* q_chunk, uint32_t* qt, int n, int k, int rb0, int nrbc, cudaStream_t st);
+void launch_repack_s_rows(const uint16_t* s_chunk, uint16_t* stl, int n, int k, int group, int src_div, int scale_bf16,
+                          int shift, int* err_flag, int rb0, int nrbc, cudaStream_t st);
 void launch_unpack_q(const uint32_t* qt, uint32_t* q_orig, int n, int k, cudaStream_t st);
 void launch_unpack_s(const uint16_t* stl, uint16_t* s_orig, int n, int k, int group, int src_div, cudaStream_t st);
 // out: f32 [n][k] (out_f16 == 0) or f16 [n][k] (out_f16 == 1, round-to-nearest-even of the f32 value);

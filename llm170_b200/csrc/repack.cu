@@ -55,6 +55,24 @@ __global__ void repack_q_kernel(const uint32_t* __restrict__ q, uint32_t* __rest
     }
 }
 
+// The same re-tiling for a CHUNK of source rows: q holds rows [16*rb0, 16*(rb0+nrbc)) of the boundary format; their
+// tiles (one per k-block and row block, scattered over qt) are written in place.  Streamed uploads re-tile chunk by chunk.
+__global__ void repack_q_rows_kernel(const uint32_t* __restrict__ q, uint32_t* __restrict__ qt, int n, int k, int rb0,
+                                     int nrbc) {
+    const size_t total = (size_t)nrbc * TILE_ROWS * (size_t)(k / 8);
+    const int nrb = n / TILE_ROWS, k8 = k / 8;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const WordCoord c = coord_of(i, nrbc);          // coordinates inside the chunk (row blocks 0..nrbc-1)
+        const int sh = 4 * (c.kbase & 7);
+        const uint32_t a = (q[(size_t)c.r0 * k8 + (c.kbase >> 3)] >> sh) & 0xFFFFu;
+        const uint32_t b = (q[(size_t)(c.r0 + 8) * k8 + (c.kbase >> 3)] >> sh) & 0xFFFFu;
+        const size_t tile = i >> 7;
+        const int rb = (int)(tile % (size_t)nrbc), kb = (int)(tile / (size_t)nrbc);
+        qt[((size_t)kb * nrb + rb0 + rb) * TILE_WORDS + (i & 127)] = spread4(a) | (spread4(b) << 4);
+    }
+}
+
 __global__ void unpack_q_kernel(const uint32_t* __restrict__ qt, uint32_t* __restrict__ q, int n, int k) {
     // one thread per ORIGINAL word (8 consecutive k of one row) = two packed words (h = 0, 1)
     const size_t total = (size_t)n * (size_t)(k / 8);
@@ -121,6 +139,29 @@ __global__ void repack_s_kernel(const uint16_t* __restrict__ s, uint16_t* __rest
             }
         }
         stl[i] = v;
+    }
+}
+
+// Scales of a chunk of source rows: the tiled array keeps a row block's groups together, so the chunk's tiles are the
+// contiguous range starting at row block rb0.
+__global__ void repack_s_rows_kernel(const uint16_t* __restrict__ s, uint16_t* __restrict__ stl, int ng, int src_div,
+                                     int scale_bf16, int shift, int* __restrict__ err, int rb0, int nrbc) {
+    const size_t total = (size_t)nrbc * TILE_ROWS * (size_t)ng;
+    const int ng_src = ng / src_div;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const int hi = (int)(i & 1), j = (int)((i >> 1) & 7);
+        const size_t rg = i >> 4;
+        const int grp = (int)(rg % (size_t)ng), rb = (int)(rg / (size_t)ng);
+        uint16_t v = s[(size_t)(rb * TILE_ROWS + j + 8 * hi) * ng_src + grp / src_div];
+        if (scale_bf16) {
+            int bad = 0;
+            v = bf16_to_f16_exact(v, shift, &bad);
+            if (bad && err) {
+                *err = 1;
+            }
+        }
+        stl[(size_t)rb0 * ng * 16 + i] = v;
     }
 }
 
@@ -249,6 +290,15 @@ void launch_scale_range(const uint16_t* s, size_t total, int* range2, cudaStream
 void launch_repack_s(const uint16_t* s, uint16_t* stl, int n, int k, int group, int src_div, int scale_bf16, int shift,
                      int* err, cudaStream_t st) {
     repack_s_kernel<<<grid_for((size_t)n * (k / group)), 256, 0, st>>>(s, stl, n, k / group, src_div, scale_bf16, shift, err);
+}
+void launch_repack_q_rows(const uint32_t* q_chunk, uint32_t* qt, int n, int k, int rb0, int nrbc, cudaStream_t st) {
+    repack_q_rows_kernel<<<grid_for((size_t)nrbc * TILE_ROWS * (k / 8)), 256, 0, st>>>(q_chunk, qt, n, k, rb0, nrbc);
+}
+void launch_repack_s_rows(const uint16_t* s_chunk, uint16_t* stl, int n, int k, int group, int src_div, int scale_bf16,
+                          int shift, int* err, int rb0, int nrbc, cudaStream_t st) {
+    (void)n;
+    repack_s_rows_kernel<<<grid_for((size_t)nrbc * TILE_ROWS * (k / group)), 256, 0, st>>>(s_chunk, stl, k / group, src_div,
+                                                                                           scale_bf16, shift, err, rb0, nrbc);
 }
 void launch_unpack_q(const uint32_t* qt, uint32_t* q, int n, int k, cudaStream_t st) {
     unpack_q_kernel<<<grid_for((size_t)n * (k / 8)), 256, 0, st>>>(qt, q, n, k);

@@ -99,6 +99,26 @@ class W4a16Dec:
         self._ck(self._L.w4a16_upload_lin_g(self._h, name.encode(), qb.ctypes.data, qb.size, sb.ctypes.data,
                                             sb.size, n, k, group, int(scale_bf16)))
 
+    def upload_lin_g_stream(self, name: str, n: int, k: int, group: int, scale_bf16: bool, fill):
+        """upload.rs:1643 -- `fill(which, off, buf)` writes bytes [off, off+len(buf)) of q (which 0) or s (which 1)
+        into the writable buffer it is given (a view of the decoder's pinned chunk)."""
+        def tramp(_user, which, off, dst, length):
+            buf = (C.c_ubyte * length).from_address(dst)
+            fill(int(which), int(off), memoryview(buf).cast("B"))
+        cb = _lib.FILL_FN(tramp)
+        self._ck(self._L.w4a16_upload_lin_g_stream(self._h, name.encode(), n, k, group, int(scale_bf16), cb, None))
+
+    def upload_lin_st(self, name: str, st: "SafeTensors", base: str):
+        """gpu_engine/upload.rs:264-305: one linear of a mapped checkpoint, streamed to the device."""
+        self._ck(self._L.w4a16_upload_lin_st(self._h, name.encode(), st._h, base.encode()))
+
+    def save_lin_cache(self, name: str, path: str, source_tag: int):
+        self._ck(self._L.w4a16_save_lin_cache(self._h, name.encode(), path.encode(), C.c_uint64(source_tag)))
+
+    def load_lin_cache(self, name: str, path: str, source_tag: int):
+        """Puts a linear back from its tile cache file with plain copies (no repack); raises on a stale file."""
+        self._ck(self._L.w4a16_load_lin_cache(self._h, name.encode(), path.encode(), C.c_uint64(source_tag)))
+
     def upload_lin_g_dev(self, name: str, q: torch.Tensor, s: torch.Tensor, n: int, k: int, group: int,
                          scale_bf16: bool = False):
         """Device-source upload: q int32 [n,k/8], s int16/float16 [n,k/group] CUDA tensors."""
@@ -328,3 +348,43 @@ class W4a16Dec:
         self._ck(self._L.w4a16_moe_ffn(self._h, il, logits.data_ptr(), x16.data_ptr(), out.data_ptr(), t,
                                        OUT_F16 if out_f16 else OUT_F32, _cur_stream()))
         return out
+
+
+class SafeTensors:
+    """crates/core/src/st.rs StArchive + the linear scan of crates/core/src/w4a16.rs:108-191, over the C ABI
+    (host only: needs no device)."""
+
+    def __init__(self, path: str):
+        self._L = _lib.lib()
+        h = C.c_void_p()
+        if self._L.w4a16_st_open(str(path).encode(), C.byref(h)) != 0:
+            raise W4a16Error(self._L.w4a16_st_error().decode())
+        self._h = h
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.w4a16_st_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def linears(self):
+        """[(base, n, k, group, scale_bf16)] in name order."""
+        out = []
+        buf = C.create_string_buffer(512)
+        n, k, g, b = C.c_int(), C.c_int(), C.c_int(), C.c_int()
+        for i in range(self._L.w4a16_st_lin_count(self._h)):
+            if self._L.w4a16_st_lin_at(self._h, i, buf, 512, C.byref(n), C.byref(k), C.byref(g), C.byref(b)) != 0:
+                raise W4a16Error(self._L.w4a16_st_error().decode())
+            out.append((buf.value.decode(), n.value, k.value, g.value, bool(b.value)))
+        return out
+
+    def tag(self, base: str) -> int:
+        t = C.c_uint64()
+        if self._L.w4a16_st_lin_tag(self._h, base.encode(), C.byref(t)) != 0:
+            raise W4a16Error(self._L.w4a16_st_error().decode())
+        return int(t.value)
