@@ -684,14 +684,28 @@ def moe_layer(dec, dist, device, st, rank, world, g):
             st.synchronize()
             if world > 1:
                 dist.barrier()
+            # one GPU: the nlay calls replayed as a CUDA graph, the way the reference replays its decode chain;
+            # expert-parallel: eager calls (the NCCL all-reduce of torch is not captured)
+            gxm = None
+            if world == 1:
+                dec.capture_begin()
+                for li in range(nlay):
+                    call(li)
+                gxm = dec.capture_end()
+                dec.graph_launch(gxm)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             reps = 5
             e0.record(st)
             for _ in range(reps):
-                for li in range(nlay):
-                    call(li)
+                if gxm is not None:
+                    dec.graph_launch(gxm)
+                else:
+                    for li in range(nlay):
+                        call(li)
             e1.record(st)
             e1.synchronize()
+            if gxm is not None:
+                dec.graph_destroy(gxm)
             us = e0.elapsed_time(e1) * 1e3 / (reps * nlay)
             if world > 1:
                 tus = torch.tensor([us], device=device)

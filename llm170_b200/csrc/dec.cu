@@ -99,7 +99,7 @@ void Dec::free_lin(Lin& l) {
 }
 
 int Dec::upload_common(const char* name, const void* q_dev, const void* s_dev, int n, int k, int group,
-                       int scale_bf16) {
+                       int scale_bf16, int glu_f) {
     // q_dev/s_dev: boundary format already on the device.  Groups of 64 channels (accepted by the reference's loader,
     // crates/core/src/w4a16.rs:225-234) are kept as two groups of 32 with the same scale: the dequantised weight
     // (nibble-8)*scale is the same number, and the kernels need no third group size.
@@ -108,6 +108,7 @@ int Dec::upload_common(const char* name, const void* q_dev, const void* s_dev, i
     l.k = k;
     l.group_src = group;
     l.group = group == 64 ? 32 : group;
+    l.glu_f = glu_f;
     const int src_div = group == 64 ? 2 : 1;
     const size_t qb = (size_t)n * (size_t)(k / 2), sb = (size_t)n * (size_t)(k / l.group) * 2;
     cudaError_t e = cudaMalloc(&l.qt, qb);
@@ -150,8 +151,8 @@ int Dec::upload_common(const char* name, const void* q_dev, const void* s_dev, i
     }
     l.out_mul = ldexpf(1.0f, -shift);
     cudaMemsetAsync(err_flag, 0, sizeof(int), stream);
-    launch_repack_q((const uint32_t*)q_dev, l.qt, n, k, stream);
-    launch_repack_s((const uint16_t*)s_dev, l.st, n, k, l.group, src_div, scale_bf16, shift, err_flag, stream);
+    launch_repack_q((const uint32_t*)q_dev, l.qt, n, k, glu_f, stream);
+    launch_repack_s((const uint16_t*)s_dev, l.st, n, k, l.group, src_div, scale_bf16, shift, err_flag, glu_f, stream);
     int bad = 0;
     e = cudaMemcpyAsync(&bad, err_flag, sizeof(int), cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) {
@@ -308,6 +309,9 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
 int Dec::gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert, const MoeBufs& b, int max_tiles,
                       int est_tiles, const float* row_w, cudaStream_t st, const int* x_slot_of_pos,
                       int x_slots_per_token) {
+    if (l->glu_f > 0 && tune_gemv_warps != 8) {
+        return fail("w4a16 grouped gemv: the fused gate|up form needs gemv_warps = 8");
+    }
     // eight staged token rows leave little room: with a two-stage ring the scales still fit in shared memory
     // and three CTAs share an SM (measured: 177 -> 147 us for 64 tokens of the 128-expert layer)
     const int grouped_stages = 2;
@@ -339,7 +343,8 @@ int Dec::gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert,
     }
     a.ksplit = ks;
     a.subnormal = tune_gemv_subnormal;
-    a.pdl = 0;
+    a.pdl = tune_pdl;
+    a.glu = l->glu_f > 0 ? 1 : 0;
     a.ring_stages = grouped_stages;
     a.cons_warps = tune_gemv_warps;
     a.cluster = ks >= 2 ? 1 : 0;
@@ -363,6 +368,8 @@ int Dec::gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert,
     if (e != cudaSuccess) {
         return cuda_fail("launch grouped gemv", e);
     }
+    last_kernel = "gemv_w4a16_kernel<" + std::to_string(a.group) + "," + (a.subnormal ? "true" : "false") + "," +
+                  std::to_string(a.cons_warps) + "> (grouped)";
     launches++;
     return 0;
 }

@@ -17,6 +17,7 @@ struct Lin {
     int n = 0, k = 0, group = 0;   // group: of the resident scale tiles (128 or 32)
     int group_src = 0;             // group of the uploaded scales (64 is stored as two groups of 32)
     float out_mul = 1.0f;          // 2^-shift when bf16 scales had to be shifted into the f16 range (else 1)
+    int glu_f = 0;                 // > 0: gate / up row blocks of every expert interleaved (layout.cuh), = ffn / 16
     size_t bytes = 0;
 };
 
@@ -97,9 +98,10 @@ struct Dec {
     static bool capturing(cudaStream_t st);
     int ensure_scratch(size_t part_floats, int grid_x, cudaStream_t st);
     void free_lin(Lin& l);
-    int upload_stream(const char* name, int n, int k, int group, int scale_bf16, w4a16_fill_fn fill, void* user);
+    int upload_stream(const char* name, int n, int k, int group, int scale_bf16, w4a16_fill_fn fill, void* user,
+                      int glu_f = 0);
     int upload_common(const char* name, const void* q_dev, const void* s_dev, int n, int k, int group,
-                      int scale_bf16);
+                      int scale_bf16, int glu_f = 0);
     std::string last_kernel;   // instantiation launched by the last forward call
     int gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& c);
     int gemv_run(GemvArgs& a, const GemvChoice& c, cudaStream_t st);

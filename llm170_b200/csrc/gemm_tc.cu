@@ -71,6 +71,8 @@ struct GemmArgs {
     int expert0;          // first expert held by this decoder
     const float* row_w;   // optional per-row factor applied in the epilogue (routing weight)
     float out_mul;        // power of two applied to every sum (undoes the shift of bf16 scales; normally 1)
+    int glu;              // 1: weight rows are interleaved gate / up 16-row blocks; the epilogue stores
+                          // f16(silu(f16 gate) * f16 up), n/2 values per row
     // split-K (few tiles: small token counts): grid = tiles x ksplit, a CTA multiplies k-blocks
     // [nkb*s/ksplit, nkb*(s+1)/ksplit); f32 partial tiles go to `part` and the last split to arrive (ticket per
     // tile, left at zero) adds them in split order, converts and stores
@@ -374,6 +376,21 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                                 }
                             }
                         }
+                    } else if (a.glu) {
+                        // a 32-column chunk = the gate sums and the up sums of the same 16 outputs
+                        if (row_l < rows_valid && c0 < ncols) {
+                            uint32_t pk[8];
+#pragma unroll
+                            for (int i = 0; i < 16; i += 2) {
+                                const __half h0 = silu_mul_f16(__uint_as_float(v[i]) * a.out_mul, __uint_as_float(v[16 + i]) * a.out_mul);
+                                const __half h1 = silu_mul_f16(__uint_as_float(v[i + 1]) * a.out_mul, __uint_as_float(v[17 + i]) * a.out_mul);
+                                pk[i / 2] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+                            }
+                            uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.out) + (size_t)row * (a.n / 2) +
+                                                                (n0 + c0) / 2);
+                            o[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            o[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+                        }
                     } else if (row_l < rows_valid) {
                         if (a.out_mul != 1.0f) {
 #pragma unroll
@@ -551,6 +568,7 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.expert0 = 0;
     a.row_w = nullptr;
     a.out_mul = l->out_mul;
+    a.glu = 0;
     a.status = gemm_status;
     a.dbg = dbg_buf;
     // Few tiles (a handful of tokens, or a narrow linear): split K so that about one CTA per SM streams weights.
@@ -648,6 +666,7 @@ int Dec::gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int 
     a.expert0 = moe.e0;
     a.row_w = row_w;
     a.out_mul = l->out_mul;
+    a.glu = l->glu_f > 0 ? 1 : 0;
     a.ksplit = 1;
     a.part = nullptr;
     a.counters = nullptr;

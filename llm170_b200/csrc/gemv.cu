@@ -509,6 +509,27 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     }
 
     // tot[r][0],[1]: row g, tokens 2t, 2t+1 ; tot[r][2],[3]: row g+8, tokens 2t, 2t+1
+    if (a.ksplit == 1 && a.glu) {
+        // interleaved gate / up row blocks: this warp's two row blocks are the gate and the up rows of the same 16
+        // outputs, so the activation is applied here and [rows][n/2] f16 is stored
+        if (RB_PER_WARP == 2 && nvalid == 2) {
+            const int orow0 = ((rb_cta0 + rbw0) / 2) * TILE_ROWS + g, orow1 = orow0 + 8;
+            const int nh = sg.n / 2;
+            __half* ob = reinterpret_cast<__half*>(a.seg[0].out) + (size_t)row_base * nh;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int tok = 2 * t + j;
+                if (tok < m_loc) {
+                    ob[(size_t)tok * nh + orow0] = silu_mul_f16(tot[0][j], tot[RB_PER_WARP - 1][j]);
+                    ob[(size_t)tok * nh + orow1] = silu_mul_f16(tot[0][2 + j], tot[RB_PER_WARP - 1][2 + j]);
+                }
+            }
+        }
+        if (stamp && threadIdx.x == 0) {
+            stamp_now(5);
+        }
+        return;
+    }
     if (a.ksplit == 1) {
 #pragma unroll
         for (int r = 0; r < RB_PER_WARP; ++r) {
@@ -565,9 +586,42 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         }
         cluster_sync_all();
         const int nrows_c = nrbv * TILE_ROWS;
+        const uint32_t pbase = sbase + p.off_ring;
+        if (a.glu) {
+            // every CTA of the cluster sums and activates a slice of the outputs: output o of this 256-row block
+            // has its gate sum in local row 32*(o/16) + o%16 and its up sum 16 rows further
+            const int nout = nrows_c / 2;
+            const int per_o = (nout + a.ksplit - 1) / a.ksplit;
+            const int o_begin = split * per_o, o_end = min(nout, o_begin + per_o);
+            const int nh = sg.n / 2;
+            __half* ob = reinterpret_cast<__half*>(a.seg[0].out) + (size_t)row_base * nh;
+            for (int i = threadIdx.x; i < (o_end - o_begin) * m_loc; i += blockDim.x) {
+                const int o = o_begin + i / m_loc, tok = i % m_loc;
+                const int lg = (o / TILE_ROWS) * 2 * TILE_ROWS + (o % TILE_ROWS), lu = lg + TILE_ROWS;
+                float vg[8], vu[8];
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    vg[s] = s < a.ksplit ? ld_dsmem_f32(pbase + (uint32_t)(lg * GEMV_MAX_M + tok) * 4u, (unsigned)s) : 0.f;
+                    vu[s] = s < a.ksplit ? ld_dsmem_f32(pbase + (uint32_t)(lu * GEMV_MAX_M + tok) * 4u, (unsigned)s) : 0.f;
+                }
+                float sg_ = 0.f, su = 0.f;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    if (s < a.ksplit) {
+                        sg_ += vg[s];
+                        su += vu[s];
+                    }
+                }
+                ob[(size_t)tok * nh + (rb_cta0 / 2) * TILE_ROWS + o] = silu_mul_f16(sg_, su);
+            }
+            cluster_sync_all();  // peers may still be reading this CTA's buffer
+            if (stamp && threadIdx.x == 0) {
+                stamp_now(5);
+            }
+            return;
+        }
         const int per = (nrows_c + a.ksplit - 1) / a.ksplit;
         const int lr_begin = split * per, lr_end = min(nrows_c, lr_begin + per);
-        const uint32_t pbase = sbase + p.off_ring;
         for (int i = threadIdx.x; i < (lr_end - lr_begin) * m_loc; i += blockDim.x) {
             const int lr = lr_begin + i / m_loc, tok = i % m_loc;
             // all splits' loads first (a cluster has at most 8 CTAs), then the sum in split order

@@ -9,18 +9,20 @@
 namespace w4 {
 
 // ---- repack.cu -------------------------------------------------------------------------------
-void launch_repack_q(const uint32_t* q_orig, uint32_t* qt, int n, int k, cudaStream_t st);
+// glu_f > 0: the tiles interleave the gate and up row blocks of every expert (layout.cuh), glu_f = ffn / 16
+void launch_repack_q(const uint32_t* q_orig, uint32_t* qt, int n, int k, int glu_f, cudaStream_t st);
 // Biased-exponent range of the non-zero bf16 scales: range2[0] = min (preset 255), range2[1] = max (preset 0).
 void launch_scale_range(const uint16_t* s_orig, size_t total, int* range2, cudaStream_t st);
 // `group` is the group size of the TILED array; a source group covers `src_div` tiled groups.  bf16 scales are
 // multiplied by 2^shift and stored as f16; err_flag (device int, may be null) is set to 1 if one of them is not
 // exactly representable.
 void launch_repack_s(const uint16_t* s_orig, uint16_t* stl, int n, int k, int group, int src_div, int scale_bf16,
-                     int shift, int* err_flag, cudaStream_t st);
+                     int shift, int* err_flag, int glu_f, cudaStream_t st);
 // the same for a chunk of source rows [16*rb0, 16*(rb0+nrbc)) (streamed uploads)
-void launch_repack_q_rows(const uint32_t* q_chunk, uint32_t* qt, int n, int k, int rb0, int nrbc, cudaStream_t st);
+void launch_repack_q_rows(const uint32_t* q_chunk, uint32_t* qt, int n, int k, int rb0, int nrbc, int glu_f,
+                          cudaStream_t st);
 void launch_repack_s_rows(const uint16_t* s_chunk, uint16_t* stl, int n, int k, int group, int src_div, int scale_bf16,
-                          int shift, int* err_flag, int rb0, int nrbc, cudaStream_t st);
+                          int shift, int* err_flag, int rb0, int nrbc, int glu_f, cudaStream_t st);
 void launch_unpack_q(const uint32_t* qt, uint32_t* q_orig, int n, int k, cudaStream_t st);
 void launch_unpack_s(const uint16_t* stl, uint16_t* s_orig, int n, int k, int group, int src_div, cudaStream_t st);
 // out: f32 [n][k] (out_f16 == 0) or f16 [n][k] (out_f16 == 1, round-to-nearest-even of the f32 value);
@@ -94,6 +96,8 @@ struct GemvArgs {
     const int* tile_rows;
     const int* num_tiles;
     const float* row_w;   // optional factor per sorted row, applied at the final store
+    int glu;              // 1: the rows are interleaved gate / up 16-row blocks (layout.cuh) and the kernel stores
+                          // f16(silu(f16 gate) * f16 up), n/2 values per token, instead of the n sums
     const int* x_slot_of_pos;   // optional gather: sorted row r reads x row x_slot_of_pos[r] / x_slots_per_token
     int x_slots_per_token;
     int nrb_w;            // 16-row blocks of the whole resident matrix (tile pitch); 0 = seg n / 16

@@ -41,6 +41,25 @@ __host__ __device__ inline bool shape_ok(int n, int k, int group) {
            k % TILE_K == 0 && k % group == 0;
 }
 
+// Gate|up interleaving of MoE expert matrices.  The boundary format stacks, per expert, `f` gate rows then `f` up
+// rows.  With F = f/16 > 0 the resident layout alternates their 16-row blocks -- block 2j = gate rows 16j..16j+15,
+// block 2j+1 = the up rows of the same outputs -- so that the CTA (and the warp, and the epilogue thread) that ends
+// up with a gate value also holds its up value and can apply silu(gate)*up itself.  F = 0: no interleaving.
+__host__ __device__ inline int glu_dest_rb(int src_rb, int F) {
+    if (F <= 0) {
+        return src_rb;
+    }
+    const int e = src_rb / (2 * F), b = src_rb - e * 2 * F;
+    return e * 2 * F + (b < F ? 2 * b : 2 * (b - F) + 1);
+}
+__host__ __device__ inline int glu_src_rb(int dest_rb, int F) {
+    if (F <= 0) {
+        return dest_rb;
+    }
+    const int e = dest_rb / (2 * F), d = dest_rb - e * 2 * F;
+    return e * 2 * F + ((d & 1) ? F + (d >> 1) : (d >> 1));
+}
+
 // Index of the packed word that holds element (row, kk), and the nibble position inside it.
 __host__ __device__ inline size_t word_index(int row, int kk, int n_total, int* nib_pos) {
     const int rb = row / TILE_ROWS, rr = row % TILE_ROWS;

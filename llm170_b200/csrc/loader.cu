@@ -439,12 +439,14 @@ namespace w4 {
 
 // Streamed upload: the source arrives through `fill` in row chunks of at most 8 MiB, each copied to the device and
 // re-tiled into its place, so neither a whole host slice nor a second full device copy is ever needed.
-int Dec::upload_stream(const char* name, int n, int k, int group, int scale_bf16, w4a16_fill_fn fill, void* user) {
+int Dec::upload_stream(const char* name, int n, int k, int group, int scale_bf16, w4a16_fill_fn fill, void* user,
+                       int glu_f) {
     Lin l;
     l.n = n;
     l.k = k;
     l.group_src = group;
     l.group = group == 64 ? 32 : group;
+    l.glu_f = glu_f;
     const int src_div = group == 64 ? 2 : 1;
     const int ng_src = k / group;
     const size_t row_q = (size_t)k / 2, row_s = (size_t)ng_src * 2;
@@ -539,9 +541,9 @@ int Dec::upload_stream(const char* name, int n, int k, int group, int scale_bf16
         fill(user, 0, (size_t)r0 * row_q, hp, (size_t)rows * row_q);
         fill(user, 1, (size_t)r0 * row_s, hp + chunk_q, (size_t)rows * row_s);
         cudaMemcpyAsync(dp, hp, chunk_q + (size_t)rows * row_s, cudaMemcpyHostToDevice, stream);
-        launch_repack_q_rows((const uint32_t*)dp, l.qt, n, k, r0 / TILE_ROWS, rows / TILE_ROWS, stream);
+        launch_repack_q_rows((const uint32_t*)dp, l.qt, n, k, r0 / TILE_ROWS, rows / TILE_ROWS, glu_f, stream);
         launch_repack_s_rows((const uint16_t*)(dp + chunk_q), l.st, n, k, l.group, src_div, scale_bf16, shift, err_flag,
-                             r0 / TILE_ROWS, rows / TILE_ROWS, stream);
+                             r0 / TILE_ROWS, rows / TILE_ROWS, glu_f, stream);
         cudaEventRecord(done[i & 1], stream);
     }
     int bad = 0;
@@ -714,6 +716,9 @@ int w4a16_save_lin_cache(w4a16_dec* dec, const char* name, const char* path, uin
     }
     const Lin& l = it->second;
     cudaSetDevice(d.device);
+    if (l.glu_f > 0) {
+        return d.fail("w4a16 save_lin_cache: %s is an interleaved expert matrix, which the cache format does not describe", name);
+    }
     CacheHeader h{};
     memcpy(h.magic, "W4T64LIN", 8);
     h.version = CACHE_VERSION;

@@ -3,6 +3,7 @@
 // (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:795-812,1021-1235) and moe_ffn_dev_t
 // (crates/backend-gpu/src/rawcuda/w4a16_dec/moe/mod.rs:263-447).
 #include <cstdio>
+#include <cstring>
 #include <string>
 
 #include "../../include/w4a16_b200.h"
@@ -115,7 +116,7 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
             // routing and all dispatch tables in one launch; the first grouped GEMV fetches each row's token itself
             launch_moe_route_small(logits, mb, t, moe.n_experts, moe.top_k, moe.e0, moe.e1, 8, st);
             launches += 1;
-            if (int rc = gemv_grouped(&i13->second, x16, mb.c13, 2 * moe.ffn, mb, max_tiles, est_tiles, nullptr, st,
+            if (int rc = gemv_grouped(&i13->second, x16, mb.act, 2 * moe.ffn, mb, max_tiles, est_tiles, nullptr, st,
                                       mb.slot_of_pos, moe.top_k)) {
                 return rc;
             }
@@ -124,11 +125,11 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
             launch_moe_align(mb, ns, moe.n_experts, moe.e0, moe.e1, 8, st);
             launch_moe_gather(x16, mb, ns, moe.top_k, moe.hidden, st);
             launches += 5;
-            if (int rc = gemv_grouped(&i13->second, mb.xs, mb.c13, 2 * moe.ffn, mb, max_tiles, est_tiles, nullptr, st)) {
+            if (int rc = gemv_grouped(&i13->second, mb.xs, mb.act, 2 * moe.ffn, mb, max_tiles, est_tiles, nullptr, st)) {
                 return rc;
             }
         }
-        launch_moe_act(mb, ns, moe.ffn, st);
+        // silu(gate)*up is applied by the first grouped matmul (interleaved gate / up rows): no activation pass
         if (int rc = gemv_grouped(&i2->second, mb.act, mb.c2, moe.hidden, mb, max_tiles, est_tiles, mb.row_w, st)) {
             return rc;
         }
@@ -140,16 +141,15 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
         launches += 5;
         launch_moe_align(mb, ns, moe.n_experts, moe.e0, moe.e1, bm, st);
         launch_moe_gather(x16, mb, ns, moe.top_k, moe.hidden, st);
-        if (int rc = gemm_grouped(&i13->second, mb.xs, ns, mb.c13, 2 * moe.ffn, mb, max_tiles, bm / 128, nullptr, st)) {
+        if (int rc = gemm_grouped(&i13->second, mb.xs, ns, mb.act, 2 * moe.ffn, mb, max_tiles, bm / 128, nullptr, st)) {
             return rc;
         }
-        launch_moe_act(mb, ns, moe.ffn, st);
         if (int rc = gemm_grouped(&i2->second, mb.act, ns, mb.c2, moe.hidden, mb, max_tiles, bm / 128, mb.row_w, st)) {
             return rc;
         }
     }
     launch_moe_combine(mb, y, t, moe.hidden, moe.top_k, out_kind == W4A16_OUT_F16, st);
-    launches += 2;
+    launches += 1;
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : cuda_fail("moe_ffn launch", e);
 }
@@ -198,18 +198,32 @@ static int upload_experts_impl(w4a16_dec* dec, int layer, const void* w13_q, con
     const int ne = d.moe.e1 - d.moe.e0, f = d.moe.ffn, h = d.moe.hidden, g = d.moe.group;
     const int n13 = ne * 2 * f, n2 = ne * h;
     const std::string a = w4::w13_name(layer), b = w4::w2_name(layer);
+    if (!w4::shape_ok(n13, h, g) || !w4::shape_ok(n2, f, g)) {
+        return d.fail("w4a16 upload_experts: ffn=%d hidden=%d group=%d violate the tile contract", f, h, g);
+    }
+    cudaSetDevice(d.device);
+    // w13 is stored with the gate and up row blocks of every expert interleaved, so that the first grouped matmul
+    // applies silu(gate)*up itself (no activation pass, no [slots][2*ffn] round trip)
+    const int glu_f = f / w4::TILE_ROWS;
     if (on_device) {
-        if (int rc = w4a16_upload_lin_g_dev(dec, a.c_str(), w13_q, w13_s, n13, h, g, scale_bf16)) {
+        cudaDeviceSynchronize();   // order after whatever produced the arrays on the legacy default stream
+        if (int rc = d.upload_common(a.c_str(), w13_q, w13_s, n13, h, g, scale_bf16, glu_f)) {
             return rc;
         }
-        return w4a16_upload_lin_g_dev(dec, b.c_str(), w2_q, w2_s, n2, f, g, scale_bf16);
+        return d.upload_common(b.c_str(), w2_q, w2_s, n2, f, g, scale_bf16, 0);
     }
-    if (int rc = w4a16_upload_lin_g(dec, a.c_str(), w13_q, (size_t)n13 * (h / 2), w13_s, (size_t)n13 * (h / g) * 2, n13,
-                                    h, g, scale_bf16)) {
+    struct Fill {
+        const unsigned char *q, *s;
+        static void fn(void* user, int which, size_t off, void* dst, size_t len) {
+            const Fill* me = (const Fill*)user;
+            memcpy(dst, (which == 0 ? me->q : me->s) + off, len);
+        }
+    };
+    Fill f13{(const unsigned char*)w13_q, (const unsigned char*)w13_s}, f2{(const unsigned char*)w2_q, (const unsigned char*)w2_s};
+    if (int rc = d.upload_stream(a.c_str(), n13, h, g, scale_bf16, Fill::fn, &f13, glu_f)) {
         return rc;
     }
-    return w4a16_upload_lin_g(dec, b.c_str(), w2_q, (size_t)n2 * (f / 2), w2_s, (size_t)n2 * (f / g) * 2, n2, f, g,
-                              scale_bf16);
+    return d.upload_stream(b.c_str(), n2, f, g, scale_bf16, Fill::fn, &f2, 0);
 }
 
 int w4a16_upload_experts(w4a16_dec* dec, int layer, const void* w13_q, const void* w13_s, const void* w2_q,

@@ -99,6 +99,14 @@ __device__ __forceinline__ float mul_row_w(float v, float w) {
     return __half2float(__hmul(__float2half_rn(v), __float2half_rn(w)));
 }
 
+// silu(gate) * up the way the reference's activation kernel computes it (crates/backend-gpu/src/rawcuda/assets/moe.cu:
+// 1649-1660) on the f16-rounded outputs of the first grouped matmul: both sums are rounded to f16, the product is
+// formed in f32 and rounded to f16 once.
+__device__ __forceinline__ __half silu_mul_f16(float gate_sum, float up_sum) {
+    const float g = __half2float(__float2half_rn(gate_sum)), u = __half2float(__float2half_rn(up_sum));
+    return __float2half_rn((g / (1.0f + expf(-g))) * u);
+}
+
 // One packed word of the T64 layout -> a[0]=(r0;k,k+1) a[1]=(r1;k,k+1) a[2]=(r0;k+2,k+3) a[3]=(r1;k+2,k+3)
 // as half2 registers holding (nibble-8) exactly.  0x6400 is f16 1024: (w & 0x000f)|0x6400 = 1024+nibble,
 // minus 1032 = nibble-8;  (w & 0x00f0)|0x6400 = 1024+16*nibble, times 1/16 minus 72 = nibble-8.

@@ -42,15 +42,17 @@ __device__ __forceinline__ WordCoord coord_of(size_t widx, int nrb) {
     return c;
 }
 
-__global__ void repack_q_kernel(const uint32_t* __restrict__ q, uint32_t* __restrict__ qt, int n, int k) {
+// glu_f: 16-row blocks per gate (and per up) half of an expert when the tiles interleave them (layout.cuh), else 0
+__global__ void repack_q_kernel(const uint32_t* __restrict__ q, uint32_t* __restrict__ qt, int n, int k, int glu_f) {
     const size_t total = (size_t)n * (size_t)(k / 8);
     const int nrb = n / TILE_ROWS, k8 = k / 8;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
         const WordCoord c = coord_of(i, nrb);
+        const int r0 = glu_src_rb(c.r0 / TILE_ROWS, glu_f) * TILE_ROWS + c.r0 % TILE_ROWS;   // source row of this tile row
         const int sh = 4 * (c.kbase & 7);
-        const uint32_t a = (q[(size_t)c.r0 * k8 + (c.kbase >> 3)] >> sh) & 0xFFFFu;
-        const uint32_t b = (q[(size_t)(c.r0 + 8) * k8 + (c.kbase >> 3)] >> sh) & 0xFFFFu;
+        const uint32_t a = (q[(size_t)r0 * k8 + (c.kbase >> 3)] >> sh) & 0xFFFFu;
+        const uint32_t b = (q[(size_t)(r0 + 8) * k8 + (c.kbase >> 3)] >> sh) & 0xFFFFu;
         qt[i] = spread4(a) | (spread4(b) << 4);
     }
 }
@@ -58,7 +60,7 @@ __global__ void repack_q_kernel(const uint32_t* __restrict__ q, uint32_t* __rest
 // The same re-tiling for a CHUNK of source rows: q holds rows [16*rb0, 16*(rb0+nrbc)) of the boundary format; their
 // tiles (one per k-block and row block, scattered over qt) are written in place.  Streamed uploads re-tile chunk by chunk.
 __global__ void repack_q_rows_kernel(const uint32_t* __restrict__ q, uint32_t* __restrict__ qt, int n, int k, int rb0,
-                                     int nrbc) {
+                                     int nrbc, int glu_f) {
     const size_t total = (size_t)nrbc * TILE_ROWS * (size_t)(k / 8);
     const int nrb = n / TILE_ROWS, k8 = k / 8;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
@@ -69,7 +71,7 @@ __global__ void repack_q_rows_kernel(const uint32_t* __restrict__ q, uint32_t* _
         const uint32_t b = (q[(size_t)(c.r0 + 8) * k8 + (c.kbase >> 3)] >> sh) & 0xFFFFu;
         const size_t tile = i >> 7;
         const int rb = (int)(tile % (size_t)nrbc), kb = (int)(tile / (size_t)nrbc);
-        qt[((size_t)kb * nrb + rb0 + rb) * TILE_WORDS + (i & 127)] = spread4(a) | (spread4(b) << 4);
+        qt[((size_t)kb * nrb + glu_dest_rb(rb0 + rb, glu_f)) * TILE_WORDS + (i & 127)] = spread4(a) | (spread4(b) << 4);
     }
 }
 
@@ -121,7 +123,7 @@ __global__ void scale_range_kernel(const uint16_t* __restrict__ s, size_t total,
 // `ng`: groups per row of the TILED array; a source group covers `src_div` of them (2 when 64-channel groups are
 // stored as two 32-channel groups with the same scale, else 1).
 __global__ void repack_s_kernel(const uint16_t* __restrict__ s, uint16_t* __restrict__ stl, int n, int ng, int src_div,
-                                int scale_bf16, int shift, int* __restrict__ err) {
+                                int scale_bf16, int shift, int* __restrict__ err, int glu_f) {
     const size_t total = (size_t)n * (size_t)ng;
     const int ng_src = ng / src_div;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
@@ -129,7 +131,7 @@ __global__ void repack_s_kernel(const uint16_t* __restrict__ s, uint16_t* __rest
         // i indexes the tiled array: [rb][grp][j][hi]
         const int hi = (int)(i & 1), j = (int)((i >> 1) & 7);
         const size_t rg = i >> 4;
-        const int grp = (int)(rg % (size_t)ng), rb = (int)(rg / (size_t)ng);
+        const int grp = (int)(rg % (size_t)ng), rb = glu_src_rb((int)(rg / (size_t)ng), glu_f);
         uint16_t v = s[(size_t)(rb * TILE_ROWS + j + 8 * hi) * ng_src + grp / src_div];
         if (scale_bf16) {
             int bad = 0;
@@ -145,7 +147,7 @@ __global__ void repack_s_kernel(const uint16_t* __restrict__ s, uint16_t* __rest
 // Scales of a chunk of source rows: the tiled array keeps a row block's groups together, so the chunk's tiles are the
 // contiguous range starting at row block rb0.
 __global__ void repack_s_rows_kernel(const uint16_t* __restrict__ s, uint16_t* __restrict__ stl, int ng, int src_div,
-                                     int scale_bf16, int shift, int* __restrict__ err, int rb0, int nrbc) {
+                                     int scale_bf16, int shift, int* __restrict__ err, int rb0, int nrbc, int glu_f) {
     const size_t total = (size_t)nrbc * TILE_ROWS * (size_t)ng;
     const int ng_src = ng / src_div;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
@@ -161,7 +163,7 @@ __global__ void repack_s_rows_kernel(const uint16_t* __restrict__ s, uint16_t* _
                 *err = 1;
             }
         }
-        stl[(size_t)rb0 * ng * 16 + i] = v;
+        stl[(size_t)glu_dest_rb(rb0 + rb, glu_f) * ng * 16 + (i - (size_t)rb * ng * 16)] = v;
     }
 }
 
@@ -274,8 +276,8 @@ inline int grid_for(size_t total) {
 
 }  // namespace
 
-void launch_repack_q(const uint32_t* q, uint32_t* qt, int n, int k, cudaStream_t st) {
-    repack_q_kernel<<<grid_for((size_t)n * (k / 8)), 256, 0, st>>>(q, qt, n, k);
+void launch_repack_q(const uint32_t* q, uint32_t* qt, int n, int k, int glu_f, cudaStream_t st) {
+    repack_q_kernel<<<grid_for((size_t)n * (k / 8)), 256, 0, st>>>(q, qt, n, k, glu_f);
 }
 void launch_lane_mirror(const uint32_t* qt, const uint16_t* stl, const void* x16, float* out, int n, int k, int group,
                         int t, float out_mul, cudaStream_t st) {
@@ -288,17 +290,19 @@ void launch_scale_range(const uint16_t* s, size_t total, int* range2, cudaStream
     scale_range_kernel<<<grid_for(total), 256, 0, st>>>(s, total, range2);
 }
 void launch_repack_s(const uint16_t* s, uint16_t* stl, int n, int k, int group, int src_div, int scale_bf16, int shift,
-                     int* err, cudaStream_t st) {
-    repack_s_kernel<<<grid_for((size_t)n * (k / group)), 256, 0, st>>>(s, stl, n, k / group, src_div, scale_bf16, shift, err);
+                     int* err, int glu_f, cudaStream_t st) {
+    repack_s_kernel<<<grid_for((size_t)n * (k / group)), 256, 0, st>>>(s, stl, n, k / group, src_div, scale_bf16, shift, err,
+                                                                       glu_f);
 }
-void launch_repack_q_rows(const uint32_t* q_chunk, uint32_t* qt, int n, int k, int rb0, int nrbc, cudaStream_t st) {
-    repack_q_rows_kernel<<<grid_for((size_t)nrbc * TILE_ROWS * (k / 8)), 256, 0, st>>>(q_chunk, qt, n, k, rb0, nrbc);
+void launch_repack_q_rows(const uint32_t* q_chunk, uint32_t* qt, int n, int k, int rb0, int nrbc, int glu_f,
+                          cudaStream_t st) {
+    repack_q_rows_kernel<<<grid_for((size_t)nrbc * TILE_ROWS * (k / 8)), 256, 0, st>>>(q_chunk, qt, n, k, rb0, nrbc, glu_f);
 }
 void launch_repack_s_rows(const uint16_t* s_chunk, uint16_t* stl, int n, int k, int group, int src_div, int scale_bf16,
-                          int shift, int* err, int rb0, int nrbc, cudaStream_t st) {
+                          int shift, int* err, int rb0, int nrbc, int glu_f, cudaStream_t st) {
     (void)n;
-    repack_s_rows_kernel<<<grid_for((size_t)nrbc * TILE_ROWS * (k / group)), 256, 0, st>>>(s_chunk, stl, k / group, src_div,
-                                                                                           scale_bf16, shift, err, rb0, nrbc);
+    repack_s_rows_kernel<<<grid_for((size_t)nrbc * TILE_ROWS * (k / group)), 256, 0, st>>>(
+        s_chunk, stl, k / group, src_div, scale_bf16, shift, err, rb0, nrbc, glu_f);
 }
 void launch_unpack_q(const uint32_t* qt, uint32_t* q, int n, int k, cudaStream_t st) {
     unpack_q_kernel<<<grid_for((size_t)n * (k / 8)), 256, 0, st>>>(qt, q, n, k);
