@@ -587,8 +587,8 @@ int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
         return 0;
     }
     if (!strcmp(key, "gemm_ksplit")) {
-        if (value < 0 || value > 32) {
-            return d.fail("w4a16 tuning: gemm_ksplit must be 0..32");
+        if (value < -1 || value > 16) {
+            return d.fail("w4a16 tuning: gemm_ksplit must be -1..16");
         }
         d.tune_gemm_ksplit = value;
         return 0;

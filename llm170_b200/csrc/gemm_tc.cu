@@ -21,6 +21,7 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <string>
 
 #include "../../include/w4a16_b200.h"
@@ -73,12 +74,14 @@ struct GemmArgs {
     float out_mul;        // power of two applied to every sum (undoes the shift of bf16 scales; normally 1)
     int glu;              // 1: weight rows are interleaved gate / up 16-row blocks; the epilogue stores
                           // f16(silu(f16 gate) * f16 up), n/2 values per row
-    // split-K (few tiles: small token counts): grid = tiles x ksplit, a CTA multiplies k-blocks
-    // [nkb*s/ksplit, nkb*(s+1)/ksplit); f32 partial tiles go to `part` and the last split to arrive (ticket per
-    // tile, left at zero) adds them in split order, converts and stores
+    // split-K: the first `n_whole` tiles (in launch order) are one CTA each; every later tile is `ksplit` CTAs, each
+    // multiplying k-blocks [nkb*s/ksplit, nkb*(s+1)/ksplit).  Their f32 partial tiles go to `part`, and the last
+    // split to arrive (ticket per tile, left at zero) adds them in split order, converts and stores.  Used for all
+    // tiles when they are few (small token counts), and for the tiles of an incomplete last wave otherwise.
+    int n_whole;
     int ksplit;
-    float* part;          // [tiles][ksplit][BM*MT][BN] f32
-    unsigned* counters;   // [tiles]
+    float* part;          // [split tiles][ksplit][BM*MT][BN] f32
+    unsigned* counters;   // [split tiles]
     int* status;  // 0 = ok; otherwise code<<16 | detail of the first wait that expired
     long long* dbg;  // optional timeline buffer (diagnostic), CTA 0 only
 };
@@ -151,7 +154,12 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
 
     // tile of this CTA (groups of GROUP_M m-tiles walk the n-tiles together)
     int m0, n0, rb0, rows_valid;
-    const int ks = a.ksplit, split = (int)blockIdx.x % ks, tile_id = (int)blockIdx.x / ks;
+    // whole tiles first, then the split ones: their CTAs run last and fill the wave the whole tiles leave incomplete
+    const bool is_split = (int)blockIdx.x >= a.n_whole && a.ksplit > 1;
+    const int ks = is_split ? a.ksplit : 1;
+    const int sidx = is_split ? ((int)blockIdx.x - a.n_whole) / ks : 0;     // index among the split tiles
+    const int split = is_split ? ((int)blockIdx.x - a.n_whole) % ks : 0;
+    const int tile_id = is_split ? a.n_whole + sidx : (int)blockIdx.x;
     if (a.grouped) {
         // consecutive CTAs walk the m-tiles of one n-tile: neighbours share an expert's weight tile in L2
         const int mt = tile_id % a.m_tiles, n_tile = tile_id / a.m_tiles;
@@ -367,7 +375,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                         // split-K: the f32 sums of this split go to scratch as they are
                         if (row_l < rows_valid) {
                             float4* pp = reinterpret_cast<float4*>(
-                                a.part + ((size_t)tile_id * ks + split) * (size_t)(BMT * BN) + (size_t)row_l * BN + c0);
+                                a.part + ((size_t)sidx * ks + split) * (size_t)(BMT * BN) + (size_t)row_l * BN + c0);
 #pragma unroll
                             for (int i = 0; i < 32; i += 4) {
                                 if (c0 + i < ncols) {
@@ -449,30 +457,53 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
     if (ks > 1) {
-        // the last split of this tile to arrive adds all partial tiles in split order (the same bits whatever the
-        // arrival order), converts and stores; its ticket goes back to zero for the next launch
+        // Every split of the tile adds a slice of its rows over all partial tiles, in split order (the same bits whatever
+        // the arrival order), converts and stores.  One CTA adding all of them would read ksplit x 256 KB alone and take
+        // longer than the wave it saves.  The splits of a tile are consecutive CTAs of the launch's last wave (their
+        // number never exceeds the SM count), so they run at the same time; the wait for the siblings is bounded all
+        // the same.  The ticket counts arrivals up to ksplit and departures up to 2 x ksplit, then returns to zero.
         if (threadIdx.x == 0) {
-            int last = 0;
+            int ready = 0;
             if (!*abort_flag) {
-                last = atomicAdd(a.counters + tile_id, 1u) == (unsigned)ks - 1u;
+                atomicAdd(a.counters + sidx, 1u);
+                const long long t0 = clock64();
+                ready = 1;
+                while (*reinterpret_cast<volatile unsigned*>(a.counters + sidx) < (unsigned)ks) {
+                    if (clock64() - t0 > (1ll << 31)) {
+                        atomicCAS(a.status, 0, (7 << 16) | (sidx & 0xffff));   // a sibling split never arrived
+                        ready = 0;
+                        break;
+                    }
+                }
                 __threadfence();
             }
-            s_last = last;
+            s_last = ready;
         }
         __syncthreads();
         if (s_last) {
             const int ncols = min(BN, a.n - n0), c4n = ncols / 4;
-            const float* base_p = a.part + (size_t)tile_id * ks * (size_t)(BMT * BN);
-            for (int idx = threadIdx.x; idx < rows_valid * c4n; idx += NUM_THREADS) {
-                const int row_l = idx / c4n, c = (idx - row_l * c4n) * 4;
+            const float* base_p = a.part + (size_t)sidx * ks * (size_t)(BMT * BN);
+            const int r_begin = (int)((long long)rows_valid * split / ks), r_end = (int)((long long)rows_valid * (split + 1) / ks);
+            for (int idx = threadIdx.x; idx < (r_end - r_begin) * c4n; idx += NUM_THREADS) {
+                const int row_l = r_begin + idx / c4n, c = (idx % c4n) * 4;
                 float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int sp = 0; sp < ks; ++sp) {
-                    const float4 pv = __ldcg(reinterpret_cast<const float4*>(base_p + (size_t)sp * (BMT * BN) +
-                                                                             (size_t)row_l * BN + c));
-                    sum.x += pv.x;
-                    sum.y += pv.y;
-                    sum.z += pv.z;
-                    sum.w += pv.w;
+                const float* src = base_p + (size_t)row_l * BN + c;
+                for (int sp0 = 0; sp0 < ks; sp0 += 8) {
+                    float4 pv[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {      // loads of up to eight splits in flight, then added in order
+                        pv[q] = sp0 + q < ks ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp0 + q) * (BMT * BN)))
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        if (sp0 + q < ks) {
+                            sum.x += pv[q].x;
+                            sum.y += pv[q].y;
+                            sum.z += pv[q].z;
+                            sum.w += pv[q].w;
+                        }
+                    }
                 }
                 const int row = m0 + row_l;
                 float o4[4] = {sum.x * a.out_mul, sum.y * a.out_mul, sum.z * a.out_mul, sum.w * a.out_mul};
@@ -494,8 +525,11 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                         make_float4(o4[0], o4[1], o4[2], o4[3]);
                 }
             }
+            __syncthreads();
             if (threadIdx.x == 0) {
-                a.counters[tile_id] = 0;
+                if (atomicAdd(a.counters + sidx, 1u) == 2u * (unsigned)ks - 1u) {
+                    a.counters[sidx] = 0;   // every split has read what it needed: ready for the next launch
+                }
             }
         }
     }
@@ -557,10 +591,61 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.k = l->k;
     a.out_f16 = out_kind == W4A16_OUT_F16;
     a.n_tiles = (l->n + BN - 1) / BN;
-    // two 128-token blocks per CTA unless that leaves fewer CTAs than half the SMs (measured crossover)
-    const int mt = (tune_gemm_mt == 1 || tune_gemm_mt == 2)
-                       ? tune_gemm_mt
-                       : ((((t + 2 * BM - 1) / (2 * BM)) * a.n_tiles * 2 >= sm_count) ? 2 : 1);
+    // Tile shape and K split are chosen together by a small cost model (times in microseconds, fitted to measurements
+    // on B200): a CTA takes 0.75 us per k-block with one 128-token block and 0.95 us with two (twice the tokens), 5 us
+    // around its loop, and a split CTA another 4 + 6 us per token block for writing, awaiting and adding f32 partial
+    // tiles.  Candidates per tile shape: whole tiles only; whole tiles plus a split last wave; every tile split
+    // 2..16 ways (at least four k-blocks per split, partial tiles within 128 MB of scratch).
+    const int nkb_all = l->k / BK;
+    struct Choice {
+        int mt, n_whole, ks;
+        double cost;
+    };
+    Choice best{1, 0, 1, 1e30};
+    for (int mtc = 1; mtc <= 2; ++mtc) {
+        if ((tune_gemm_mt == 1 || tune_gemm_mt == 2) && mtc != tune_gemm_mt) {
+            continue;
+        }
+        const int m_tiles = (t + BM * mtc - 1) / (BM * mtc);
+        // a second, empty token block is neither fetched nor multiplied: its k-blocks cost what one block costs
+        const bool half_empty = mtc == 2 && t <= BM;
+        const double per_kb = (mtc == 2 && !half_empty) ? 0.95 : 0.75;
+        const long long tiles = (long long)m_tiles * a.n_tiles;
+        const double tile_bytes = (double)BM * mtc * BN * 4.0;
+        auto cta_cost = [&](int nk, bool split) { return nk * per_kb + 5.0 + (split ? 4.0 + 6.0 * mtc : 0.0); };
+        auto consider = [&](long long n_whole, int ks) {
+            const long long split_tiles = tiles - n_whole;
+            if (ks > 1 && (split_tiles > 4096 || split_tiles * ks * tile_bytes > 128.0 * (1 << 20))) {
+                return;
+            }
+            const int nk_split = (nkb_all + ks - 1) / ks;
+            double c = (double)((n_whole + sm_count - 1) / sm_count) * cta_cost(nkb_all, false);
+            if (split_tiles > 0) {
+                c += (double)((split_tiles * ks + sm_count - 1) / sm_count) * cta_cost(nk_split, ks > 1);
+            }
+            if (c < best.cost) {
+                best = Choice{mtc, (int)n_whole, ks, c};
+            }
+        };
+        if (tune_gemm_ksplit > 0) {
+            consider(0, std::min(tune_gemm_ksplit, std::max(1, nkb_all)));
+            continue;
+        }
+        consider(tiles, 1);
+        if (tune_gemm_ksplit < 0) {
+            continue;
+        }
+        const long long rem = tiles % sm_count;
+        if (rem > 0 && tiles > sm_count) {
+            for (int ks = 2; ks <= 16 && nkb_all / ks >= 4; ++ks) {
+                consider(tiles - rem, ks);
+            }
+        }
+        for (int ks = 2; ks <= 16 && nkb_all / ks >= 4; ++ks) {
+            consider(0, ks);
+        }
+    }
+    const int mt = best.mt;
     a.m_tiles = (t + BM * mt - 1) / (BM * mt);
     a.nrb_w = l->n / TILE_ROWS;
     a.grouped = 0;
@@ -571,40 +656,25 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.glu = 0;
     a.status = gemm_status;
     a.dbg = dbg_buf;
-    // Few tiles (a handful of tokens, or a narrow linear): split K so that about one CTA per SM streams weights.
-    // At least four k-blocks per split; the f32 partial tiles must fit 64 MB of scratch.
     const int tiles = a.m_tiles * a.n_tiles;
-    int ks = 1;
-    if (tune_gemm_ksplit > 0) {
-        ks = tune_gemm_ksplit;
-    } else if (tiles * 4 < sm_count * 3) {
-        ks = sm_count / tiles;
-    }
-    const int nkb_all = l->k / BK;
-    if (ks > nkb_all / 4) {
-        ks = nkb_all / 4;
-    }
-    if (ks > 32) {
-        ks = 32;
+    int n_whole = best.n_whole, ks = best.ks;
+    if (ks <= 1) {
+        ks = 1;
+        n_whole = tiles;
     }
     const size_t tile_floats = (size_t)BM * mt * BN;
-    while (ks > 1 && (size_t)tiles * ks * tile_floats * sizeof(float) > (64u << 20)) {
-        --ks;
-    }
-    if (ks < 1 || tiles > 4096) {
-        ks = 1;
-    }
+    a.n_whole = n_whole;
     a.ksplit = ks;
     a.part = nullptr;
     a.counters = nullptr;
     if (ks > 1) {
-        if (int rc = ensure_scratch((size_t)tiles * ks * tile_floats, tiles, st)) {
+        if (int rc = ensure_scratch((size_t)(tiles - n_whole) * ks * tile_floats, tiles - n_whole, st)) {
             return rc;
         }
         a.part = part;
         a.counters = counters;
     }
-    const int grid = tiles * ks;
+    const int grid = n_whole + (tiles - n_whole) * ks;
     if (l->group == 128) {
         if (mt == 2) {
             gemm_w4a16_tc_kernel<128, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, a);
@@ -623,7 +693,7 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
         return cuda_fail("launch gemm", e);
     }
     last_kernel = "gemm_w4a16_tc_kernel<" + std::to_string(l->group) + "," + std::to_string(mt) + ">" +
-                  (ks > 1 ? " split-K " + std::to_string(ks) : std::string());
+                  (ks > 1 ? " split-K " + std::to_string(ks) + (n_whole > 0 ? " on the last wave" : "") : std::string());
     launches++;
     return 0;
 }
@@ -667,6 +737,7 @@ int Dec::gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int 
     a.row_w = row_w;
     a.out_mul = l->out_mul;
     a.glu = l->glu_f > 0 ? 1 : 0;
+    a.n_whole = a.m_tiles * ((n_per_expert + BN - 1) / BN);
     a.ksplit = 1;
     a.part = nullptr;
     a.counters = nullptr;

@@ -92,7 +92,7 @@ def test_tile_variants_agree_bitwise(dec):
     dec.upload_lin_g("mtv", q, s, n, k, 128)
     x = x_dev(synth.make_acts(t, k, seed=62, scale=1 / np.sqrt(k)))
     outs = []
-    dec.set_tuning("gemm_ksplit", 1)          # one K range per tile: the tile variants then add in the same order
+    dec.set_tuning("gemm_ksplit", -1)         # one K range per tile: the tile variants then add in the same order
     for mt in (1, 2):
         dec.set_tuning("gemm_mt", mt)
         outs.append(dec.lin_forward("mtv", x, t).clone())
@@ -166,7 +166,7 @@ def test_split_k_gemm_pow2_exact_and_repeatable(dec, t, k, n, group, ks):
         y = dec.lin_forward("p2k", x_dev(x), t).clone()
         y2 = dec.lin_forward("p2k", x_dev(x), t)
         dec.sync()
-        assert "split-K" in dec.last_kernel()
+        assert "split-K" in dec.last_kernel(), dec.last_kernel()
     finally:
         dec.set_tuning("gemm_ksplit", 0)
     assert np.array_equal(y.cpu().numpy().view(np.uint32), expect.view(np.uint32))
@@ -194,3 +194,28 @@ def test_small_batch_band_on_layer_shapes(dec, orc, name, t):
         # N(0,1) activations: |y| reaches ~10, and the GEMM multiplies weights rounded once to f16 (relative 2^-11)
         assert np.abs(got[:, r0:r0 + 64] - want[:, r0:r0 + 64]).max() <= TOL * max(1.0, scale)
     dec.drop_lin("sb")
+
+
+def test_last_wave_split_agrees_with_whole_tiles(dec):
+    # 19 x 8 = 152 tiles of 256 tokens on 148 SMs: the automatic choice runs 148 whole tiles and splits the last 4 along K;
+    # same products, partial sums added in another order -> agreement to f32 rounding, and bit-repeatable
+    n, k, t = 2048, 4096, 4864
+    q, s = synth.make_linear_cuda(n, k, 128, seed=5, device=torch.device("cuda", 0))
+    dec.upload_lin_g_dev("lw", q, s, n, k, 128)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(9)
+    x = (torch.randn((t, k), generator=gen, device="cuda") / (k ** 0.5)).to(torch.float16)
+    y = dec.lin_forward("lw", x, t).clone()
+    name = dec.last_kernel()
+    y2 = dec.lin_forward("lw", x, t).clone()
+    dec.set_tuning("gemm_ksplit", -1)
+    try:
+        y_whole = dec.lin_forward("lw", x, t)
+        dec.sync()
+    finally:
+        dec.set_tuning("gemm_ksplit", 0)
+    if torch.cuda.get_device_properties(0).multi_processor_count == 148:
+        assert "last wave" in name, name
+    assert torch.equal(y, y2)
+    assert (y - y_whole).abs().max().item() <= 1e-5 * y_whole.abs().max().item() + 1e-7
+    dec.drop_lin("lw")
