@@ -29,8 +29,10 @@ constexpr int TOPK_WARPS = 8;
 // when two different numerators round to the same p.  exp is evaluated in double and rounded once, the closest
 // a device routine gets to the host's expf.  A pick is two warp-wide integer reductions: positive floats order
 // like their bit patterns, so the largest p is a max over u32 and the tie-break a min over the indices that hold it.
+// `stage`: optional shared-memory row of n floats owned by this warp; with it the sequential sum is read back by one
+// lane (independent loads, one dependent add each) instead of travelling through n dependent shuffles.
 __device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* __restrict__ idx, float* __restrict__ wt,
-                                              int n, int k, int lane) {
+                                              int n, int k, int lane, float* stage = nullptr) {
     float mx = -INFINITY;
     for (int i = lane; i < n; i += 32) {
         mx = fmaxf(mx, l[i]);
@@ -46,12 +48,26 @@ __device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* 
     }
     // sum in index order, the same on every lane: element e = 32*j + src comes from lane src, slot j
     float sum = 0.f;
-    const int slots = (n + 31) >> 5;
-    for (int j = 0; j < slots; ++j) {
-        const float mine_j = j < cnt ? pv[j] : 0.f;
-        const int live = min(32, n - 32 * j);
-        for (int src = 0; src < live; ++src) {
-            sum += __shfl_sync(0xffffffffu, mine_j, src);
+    if (stage != nullptr) {
+        for (int j = 0; j < cnt; ++j) {
+            stage[lane + 32 * j] = pv[j];
+        }
+        __syncwarp();
+        if (lane == 0) {
+            for (int e = 0; e < n; ++e) {
+                sum += stage[e];
+            }
+        }
+        sum = __shfl_sync(0xffffffffu, sum, 0);
+        __syncwarp();   // the row may be reused for the warp's next token
+    } else {
+        const int slots = (n + 31) >> 5;
+        for (int j = 0; j < slots; ++j) {
+            const float mine_j = j < cnt ? pv[j] : 0.f;
+            const int live = min(32, n - 32 * j);
+            for (int src = 0; src < live; ++src) {
+                sum += __shfl_sync(0xffffffffu, mine_j, src);
+            }
         }
     }
     for (int j = 0; j < cnt; ++j) {
@@ -93,13 +109,15 @@ __device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* 
 }
 
 __global__ void moe_topk_kernel(const float* __restrict__ lg, int* __restrict__ idx, float* __restrict__ wt, int t,
-                                int n, int k) {
+                                int n, int k, int stage_rows) {
+    extern __shared__ float s_stage[];   // [warps][n] when the launch provides it
     const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ti = blockIdx.x * TOPK_WARPS + w;
     if (ti >= t) {
         return;
     }
-    topk_of_token(lg + (size_t)ti * n, idx + (size_t)ti * k, wt + (size_t)ti * k, n, k, lane);
+    topk_of_token(lg + (size_t)ti * n, idx + (size_t)ti * k, wt + (size_t)ti * k, n, k, lane,
+                  stage_rows ? s_stage + (size_t)w * n : nullptr);
 }
 
 // Decode-sized batches (at most 1024 (token, expert) slots): routing, histogram, offsets, tile table, placement
@@ -110,13 +128,15 @@ moe_route_small_kernel(const float* __restrict__ lg, int* __restrict__ idx, floa
                        int* __restrict__ off, int* __restrict__ pos_of_slot, int* __restrict__ slot_of_pos,
                        int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ tile_rows,
                        int* __restrict__ n_tiles, int* __restrict__ n_rows, float* __restrict__ row_w, int t, int n_exp,
-                       int k, int e0, int e1, int bm) {
+                       int k, int e0, int e1, int bm, int stage_rows) {
     __shared__ int s_rows[1024], s_tiles[1024], s_off[1024], s_cursor[1024];
+    extern __shared__ float s_stage[];   // [32 warps][n_exp] when the launch provides it
     const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
     s_rows[tid] = 0;
     s_cursor[tid] = 0;
     for (int ti = w; ti < t; ti += 32) {
-        topk_of_token(lg + (size_t)ti * n_exp, idx + (size_t)ti * k, wt + (size_t)ti * k, n_exp, k, lane);
+        topk_of_token(lg + (size_t)ti * n_exp, idx + (size_t)ti * k, wt + (size_t)ti * k, n_exp, k, lane,
+                      stage_rows ? s_stage + (size_t)w * n_exp : nullptr);
     }
     __syncthreads();   // idx / wt of every token are visible to the block
     const int ns = t * k;
@@ -337,14 +357,17 @@ inline int blocks_for(size_t total, int threads) {
 }  // namespace
 
 void launch_moe_topk(const float* logits, int* idx, float* wt, int t, int n_exp, int k, cudaStream_t st) {
-    moe_topk_kernel<<<(t + TOPK_WARPS - 1) / TOPK_WARPS, TOPK_WARPS * 32, 0, st>>>(logits, idx, wt, t, n_exp, k);
+    const int stage = n_exp <= 512;   // 8 warps x 512 floats = 16 KB of shared memory at most
+    moe_topk_kernel<<<(t + TOPK_WARPS - 1) / TOPK_WARPS, TOPK_WARPS * 32, stage ? TOPK_WARPS * n_exp * sizeof(float) : 0, st>>>(
+        logits, idx, wt, t, n_exp, k, stage);
 }
 
 void launch_moe_route_small(const float* logits, const MoeBufs& b, int t, int n_exp, int k, int e0, int e1, int bm,
                             cudaStream_t st) {
-    moe_route_small_kernel<<<1, 1024, 0, st>>>(logits, b.idx, b.wt, b.off, b.pos_of_slot, b.slot_of_pos, b.tile_expert,
-                                               b.tile_row0, b.tile_rows, b.n_tiles, b.n_rows, b.row_w, t, n_exp, k, e0,
-                                               e1, bm);
+    const int stage = n_exp <= 256;   // 32 warps x 256 floats = 32 KB beside the 16 KB of tables
+    moe_route_small_kernel<<<1, 1024, stage ? 32 * n_exp * sizeof(float) : 0, st>>>(
+        logits, b.idx, b.wt, b.off, b.pos_of_slot, b.slot_of_pos, b.tile_expert, b.tile_row0, b.tile_rows, b.n_tiles, b.n_rows,
+        b.row_w, t, n_exp, k, e0, e1, bm, stage);
 }
 
 void launch_moe_align(const MoeBufs& b, int ns, int n_exp, int e0, int e1, int bm, cudaStream_t st) {
