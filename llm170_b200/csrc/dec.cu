@@ -593,6 +593,10 @@ int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
         d.tune_gemm_ksplit = value;
         return 0;
     }
+    if (!strcmp(key, "gemm_tma_store")) {
+        d.tune_gemm_tma_store = value != 0;
+        return 0;
+    }
     if (!strcmp(key, "gemv_cluster")) {
         d.tune_gemv_cluster = value != 0;
         return 0;

@@ -87,6 +87,7 @@ struct Dec {
     int tune_tp_wait_log2 = 31;  // the fused all-reduce gives up on its peers after 2^this cycles
     int tune_gemm_mt = 0;        // 128-token blocks per GEMM tile: 0 = automatic, 1 or 2
     int tune_gemm_ksplit = 0;    // K splits of the GEMM: 0 = automatic (only when the tiles do not fill the SMs)
+    int tune_gemm_tma_store = 1; // dense whole tiles leave through shared memory and TMA stores (0: per-lane stores)
     long long* dbg_buf = nullptr;  // device timeline buffer (DBG_SLOTS entries) when the knob is on
     int tune_gemv_ksplit = 0;
     // kernels launched by forward calls since creation

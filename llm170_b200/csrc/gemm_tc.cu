@@ -84,6 +84,7 @@ struct GemmArgs {
     unsigned* counters;   // [split tiles]
     int* status;  // 0 = ok; otherwise code<<16 | detail of the first wait that expired
     long long* dbg;  // optional timeline buffer (diagnostic), CTA 0 only
+    int tma_store;   // 1: whole dense tiles leave through shared memory and TMA stores (tmap_y)
 };
 
 // K-major, 128B-swizzled operand: 8-row groups are 1024 B apart (SBO), LBO unused, descriptor version 1.
@@ -127,7 +128,8 @@ __device__ __forceinline__ uint32_t hmul2u(uint32_t a, uint32_t b) {
 }
 template <int GROUP, int MT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs a) {
+gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
+                     const GemmArgs a) {
     constexpr int NT = Cfg<MT>::NT;
     constexpr int NB = Cfg<MT>::NB;
     constexpr int A_STAGE = Cfg<MT>::A_STAGE;
@@ -361,6 +363,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const int quad = warp & 3;
                 const int ncols = min(BN, a.n - n0);
+                int n_staged = 0;
                 for (int mc = 0; mc < mt_live * (BN / 32); ++mc) {
                     const int mt = mc / (BN / 32), c0 = (mc % (BN / 32)) * 32;
                     if (c0 >= ncols || (mc & 3) != (dw >> 2)) {
@@ -399,6 +402,57 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                             o[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                             o[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
                         }
+                    } else if (a.tma_store) {
+                        // The warp's 32 rows x 32 columns go to a staging tile in the (now idle) operand rings, laid out
+                        // with the tensor map's swizzle so that the 16-byte writes of a quarter-warp hit distinct banks,
+                        // and leave as one TMA store: whole 128-byte lines instead of 32 scattered half-sectors per
+                        // instruction.  Rows past the batch and columns past n are clipped by the tensor map.  Two
+                        // staging tiles per warp: the store of one is read out while the next is filled.
+                        if (a.out_mul != 1.0f) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                v[i] = __float_as_uint(__uint_as_float(v[i]) * a.out_mul);
+                            }
+                        }
+                        if (n_staged >= 2) {
+                            if (lane == 0) {
+                                bulk_wait_group_read<1>();
+                            }
+                            __syncwarp();
+                        }
+                        const uint32_t sbuf = base + (uint32_t)dw * 8192u + (uint32_t)(n_staged & 1) * 4096u;
+                        if (a.out_f16) {
+                            const uint32_t rowp = sbuf + (uint32_t)lane * 64u, sw = (uint32_t)(lane >> 1) & 3u;
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                uint4 pk;
+                                __half2 h;
+                                h = __floats2half2_rn(__uint_as_float(v[8 * c]), __uint_as_float(v[8 * c + 1]));
+                                pk.x = *reinterpret_cast<uint32_t*>(&h);
+                                h = __floats2half2_rn(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3]));
+                                pk.y = *reinterpret_cast<uint32_t*>(&h);
+                                h = __floats2half2_rn(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5]));
+                                pk.z = *reinterpret_cast<uint32_t*>(&h);
+                                h = __floats2half2_rn(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
+                                pk.w = *reinterpret_cast<uint32_t*>(&h);
+                                sts128(rowp + (((uint32_t)c ^ sw) << 4), pk);
+                            }
+                        } else {
+                            const uint32_t rowp = sbuf + (uint32_t)lane * 128u, sw = (uint32_t)lane & 7u;
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) {
+                                sts128(rowp + (((uint32_t)c ^ sw) << 4), make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]));
+                            }
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (m0 + mt * BM + quad * 32 < a.m) {   // a box wholly past the batch is not issued at all
+                                tma_store_2d(&tmap_y, sbuf, n0 + c0, m0 + mt * BM + quad * 32);
+                            }
+                            bulk_commit_group();
+                        }
+                        ++n_staged;
                     } else if (row_l < rows_valid) {
                         if (a.out_mul != 1.0f) {
 #pragma unroll
@@ -440,6 +494,13 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                             }
                         }
                     }
+                }
+                if (n_staged > 0) {
+                    // the staging tiles must stay in place until the TMA stores have read them
+                    if (lane == 0) {
+                        bulk_wait_group_read<0>();
+                    }
+                    __syncwarp();
                 }
             }
         }
@@ -582,6 +643,21 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     if (cr != CUDA_SUCCESS) {
         return fail("w4a16 gemm: cuTensorMapEncodeTiled failed (%d)", (int)cr);
     }
+    // the outputs as 32 x 32 boxes for the epilogue's TMA stores (f16: 64-byte rows, f32: 128-byte rows)
+    CUtensorMap map_y = map;
+    const bool out16 = out_kind == W4A16_OUT_F16;
+    bool tma_store = tune_gemm_tma_store != 0;
+    if (tma_store) {
+        const cuuint64_t ydims[2] = {(cuuint64_t)l->n, (cuuint64_t)t};
+        const cuuint64_t ystrides[1] = {(cuuint64_t)l->n * (out16 ? 2 : 4)};
+        const cuuint32_t ybox[2] = {32, 32};
+        cr = enc(&map_y, out16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, dst, ydims, ystrides,
+                 ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, out16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                 CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) {
+            return fail("w4a16 gemm: cuTensorMapEncodeTiled failed for the outputs (%d)", (int)cr);
+        }
+    }
     GemmArgs a;
     a.qt = l->qt;
     a.st = (const uint32_t*)l->st;
@@ -589,7 +665,7 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.m = t;
     a.n = l->n;
     a.k = l->k;
-    a.out_f16 = out_kind == W4A16_OUT_F16;
+    a.out_f16 = out16;
     a.n_tiles = (l->n + BN - 1) / BN;
     // Tile shape and K split are chosen together by a small cost model (times in microseconds, fitted to measurements
     // on B200): a CTA takes 0.75 us per k-block with one 128-token block and 0.95 us with two (twice the tokens), 5 us
@@ -656,6 +732,7 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     a.glu = 0;
     a.status = gemm_status;
     a.dbg = dbg_buf;
+    a.tma_store = tma_store ? 1 : 0;
     const int tiles = a.m_tiles * a.n_tiles;
     int n_whole = best.n_whole, ks = best.ks;
     if (ks <= 1) {
@@ -677,15 +754,15 @@ int Dec::gemm(const Lin* l, const void* x, void* dst, int t, int out_kind, cudaS
     const int grid = n_whole + (tiles - n_whole) * ks;
     if (l->group == 128) {
         if (mt == 2) {
-            gemm_w4a16_tc_kernel<128, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, a);
+            gemm_w4a16_tc_kernel<128, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, map_y, a);
         } else {
-            gemm_w4a16_tc_kernel<128, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
+            gemm_w4a16_tc_kernel<128, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, map_y, a);
         }
     } else {
         if (mt == 2) {
-            gemm_w4a16_tc_kernel<32, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, a);
+            gemm_w4a16_tc_kernel<32, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, map_y, a);
         } else {
-            gemm_w4a16_tc_kernel<32, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
+            gemm_w4a16_tc_kernel<32, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, map_y, a);
         }
     }
     cudaError_t e = cudaGetLastError();
@@ -743,18 +820,19 @@ int Dec::gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int 
     a.counters = nullptr;
     a.status = gemm_status;
     a.dbg = nullptr;
+    a.tma_store = 0;
     const int grid = a.m_tiles * a.n_tiles;
     if (l->group == 128) {
         if (mt == 2) {
-            gemm_w4a16_tc_kernel<128, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, a);
+            gemm_w4a16_tc_kernel<128, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, map, a);
         } else {
-            gemm_w4a16_tc_kernel<128, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
+            gemm_w4a16_tc_kernel<128, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, map, a);
         }
     } else {
         if (mt == 2) {
-            gemm_w4a16_tc_kernel<32, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, a);
+            gemm_w4a16_tc_kernel<32, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, map, a);
         } else {
-            gemm_w4a16_tc_kernel<32, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, a);
+            gemm_w4a16_tc_kernel<32, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, map, a);
         }
     }
     cudaError_t e = cudaGetLastError();

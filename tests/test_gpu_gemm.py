@@ -102,6 +102,28 @@ def test_tile_variants_agree_bitwise(dec):
     assert torch.equal(outs[0], outs[1])      # same k order per output element -> same bits
 
 
+@pytest.mark.parametrize("n,k,group,t,out_f16", [(512, 1024, 128, 512, 0), (1024, 2048, 128, 700, 0),
+                                                  (784, 512, 32, 1300, 0), (2048, 2048, 32, 1024, 1),
+                                                  (272, 128, 128, 130, 1), (256, 256, 128, 9, 1), (4864, 4096, 128, 512, 1)])
+def test_tma_store_epilogue_agrees_bitwise_with_per_lane_stores(dec, n, k, group, t, out_f16):
+    # the staged TMA-store epilogue writes the same values as the per-lane stores: ragged last token tile, a last
+    # column chunk cut at n, both output types, and a launch whose last wave is split (those tiles keep their own path)
+    q, s = synth.make_linear(n, k, group, seed=71 + t)
+    dec.upload_lin_g("epi", q, s, n, k, group)
+    x = x_dev(synth.make_acts(t, k, seed=72 + t, scale=1 / np.sqrt(k)))
+    try:
+        dec.set_tuning("gemm_tma_store", 0)
+        lanes = dec.lin_forward("epi", x, t, out_f16=bool(out_f16)).clone()
+        dec.set_tuning("gemm_tma_store", 1)
+        guard = torch.full((t + 64, n), 7.0, device="cuda", dtype=torch.float16 if out_f16 else torch.float32)
+        staged = dec.lin_forward("epi", x, t, dst=guard[:t], out_f16=bool(out_f16))
+    finally:
+        dec.set_tuning("gemm_tma_store", 1)
+    dec.sync()
+    assert torch.equal(lanes, staged)
+    assert bool((guard[t:] == 7.0).all())        # nothing is written past the batch
+
+
 def test_gemm_and_gemv_agree_on_the_same_weights(dec):
     # both kernels read the one resident copy; they differ only by the f16 rounding of the weight
     n, k = 1024, 2048
