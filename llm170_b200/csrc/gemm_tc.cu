@@ -372,6 +372,9 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
                     const int row_l = mt * BM + quad * 32 + lane;
                     const int row = m0 + row_l;
                     const float rw = (a.row_w != nullptr && row_l < rows_valid) ? a.row_w[row] : 1.0f;
+                    // TMA-store path: every box of a dense tile (the tensor map clips at the batch's end); of a grouped
+                    // tile only the boxes whose 32 rows all belong to the tile's expert segment
+                    const bool staged_box = a.tma_store && ks == 1 && (!a.grouped || mt * BM + quad * 32 + 32 <= rows_valid);
                     uint32_t v[32];
                     tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(mt * 256 + c0), v);
                     if (ks > 1) {
@@ -387,6 +390,31 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
                                 }
                             }
                         }
+                    } else if (a.glu && staged_box) {
+                        // as below, through a staging tile of 32 rows x 16 outputs (32-byte rows, no swizzle)
+                        uint32_t pk[8];
+#pragma unroll
+                        for (int i = 0; i < 16; i += 2) {
+                            const __half h0 = silu_mul_f16(__uint_as_float(v[i]) * a.out_mul, __uint_as_float(v[16 + i]) * a.out_mul);
+                            const __half h1 = silu_mul_f16(__uint_as_float(v[i + 1]) * a.out_mul, __uint_as_float(v[17 + i]) * a.out_mul);
+                            pk[i / 2] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+                        }
+                        if (n_staged >= 2) {
+                            if (lane == 0) {
+                                bulk_wait_group_read<1>();
+                            }
+                            __syncwarp();
+                        }
+                        const uint32_t sbuf = base + (uint32_t)dw * 8192u + (uint32_t)(n_staged & 1) * 4096u;
+                        sts128(sbuf + (uint32_t)lane * 32u, make_uint4(pk[0], pk[1], pk[2], pk[3]));
+                        sts128(sbuf + (uint32_t)lane * 32u + 16u, make_uint4(pk[4], pk[5], pk[6], pk[7]));
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&tmap_y, sbuf, (n0 + c0) / 2, m0 + mt * BM + quad * 32);
+                            bulk_commit_group();
+                        }
+                        ++n_staged;
                     } else if (a.glu) {
                         // a 32-column chunk = the gate sums and the up sums of the same 16 outputs
                         if (row_l < rows_valid && c0 < ncols) {
@@ -402,7 +430,7 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
                             o[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                             o[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
                         }
-                    } else if (a.tma_store) {
+                    } else if (staged_box) {
                         // The warp's 32 rows x 32 columns go to a staging tile in the (now idle) operand rings, laid out
                         // with the tensor map's swizzle so that the 16-byte writes of a quarter-warp hit distinct banks,
                         // and leave as one TMA store: whole 128-byte lines instead of 32 scattered half-sectors per
@@ -412,6 +440,12 @@ gemm_w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_co
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
                                 v[i] = __float_as_uint(__uint_as_float(v[i]) * a.out_mul);
+                            }
+                        }
+                        if (a.row_w != nullptr) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                v[i] = __float_as_uint(mul_row_w(__uint_as_float(v[i]), rw));
                             }
                         }
                         if (n_staged >= 2) {
@@ -820,19 +854,34 @@ int Dec::gemm_grouped(const Lin* l, const void* xs, int xs_rows, void* out, int 
     a.counters = nullptr;
     a.status = gemm_status;
     a.dbg = nullptr;
+    // outputs as 32-row boxes for the TMA-store epilogue: [rows][n] f16, or [rows][n/2] f16 after the fused silu(gate)*up
+    CUtensorMap map_y = map;
     a.tma_store = 0;
+    if (tune_gemm_tma_store != 0) {
+        const int n_out = a.glu ? n_per_expert / 2 : n_per_expert;
+        const cuuint64_t ydims[2] = {(cuuint64_t)n_out, (cuuint64_t)xs_rows};
+        const cuuint64_t ystrides[1] = {(cuuint64_t)n_out * 2};
+        const cuuint32_t ybox[2] = {(cuuint32_t)(a.glu ? 16 : 32), 32};
+        cr = enc(&map_y, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, ydims, ystrides, ybox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 a.glu ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) {
+            return fail("w4a16 gemm: cuTensorMapEncodeTiled failed for the outputs (%d)", (int)cr);
+        }
+        a.tma_store = 1;
+    }
     const int grid = a.m_tiles * a.n_tiles;
     if (l->group == 128) {
         if (mt == 2) {
-            gemm_w4a16_tc_kernel<128, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, map, a);
+            gemm_w4a16_tc_kernel<128, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, map_y, a);
         } else {
-            gemm_w4a16_tc_kernel<128, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, map, a);
+            gemm_w4a16_tc_kernel<128, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, map_y, a);
         }
     } else {
         if (mt == 2) {
-            gemm_w4a16_tc_kernel<32, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, map, a);
+            gemm_w4a16_tc_kernel<32, 2><<<grid, NUM_THREADS, Cfg<2>::SMEM, st>>>(map, map_y, a);
         } else {
-            gemm_w4a16_tc_kernel<32, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, map, a);
+            gemm_w4a16_tc_kernel<32, 1><<<grid, NUM_THREADS, Cfg<1>::SMEM, st>>>(map, map_y, a);
         }
     }
     cudaError_t e = cudaGetLastError();
