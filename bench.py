@@ -171,10 +171,67 @@ def run_reference_arm(args, rank: int):
 
 
 # ------------------------------------------------------------------------------------------------
+def upload_synthetic_head(dec, n, k, device):
+    """A seeded N(0, 0.02) lm-head as bf16 bit patterns, made on the device and passed through the host boundary."""
+    import torch
+    gen = torch.Generator(device=device)
+    gen.manual_seed(77)
+    w = (torch.randn((n, k), generator=gen, device=device, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    dec.upload_head(w.view(torch.int16).cpu().numpy().view(np.uint16), n, k)
+
+
+def lm_head(dec, device, st, peaks, g):
+    """The int8 lm-head GEMV (vocabulary x hidden int8 bytes per token: the largest weight stream of a decode step
+    after the layers) at t = 1 and 8, with a parity check of 64 rows against the oracle's lane-order sum."""
+    import torch
+    n, k = synth.LM_HEAD_27B
+    upload_synthetic_head(dec, n, k, device)
+    out = {"vocab": n, "hidden": k, "kernel": None}
+    with torch.cuda.stream(st):
+        for t in (1, 8):
+            gen = torch.Generator(device=device)
+            gen.manual_seed(5 + t)
+            x = torch.randn((t, k), generator=gen, device=device, dtype=torch.float32)
+            y = torch.empty((t, n), device=device, dtype=torch.float32)
+            dec.head_forward(x, t, out=y)
+            st.synchronize()
+            ts = []
+            for _ in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(st)
+                dec.head_forward(x, t, out=y)
+                e1.record(st)
+                e1.synchronize()
+                ts.append(e0.elapsed_time(e1) * 1e-3)
+            sec = float(np.median(ts))
+            nbytes = n * k + n * 4 + t * k * 4 + t * n * 4
+            out[f"t{t}"] = {"us": sec * 1e6, "GB/s": nbytes / sec / 1e9, "frac_of_hbm": nbytes / sec / 1e9 / peaks["hbm_gbs"]}
+            if t == 1:
+                import oracle
+                q, sc = dec.head_unpack()
+                rows = np.linspace(0, n - 1, 64).astype(np.int64)
+                xs = x.cpu().numpy()
+                expect = oracle.head_gemv_i8(q[rows], sc[rows], xs, 1)[0]
+                bound = 1e-5 * (np.abs(xs[0]).astype(np.float64) @ np.abs(q[rows]).astype(np.float64).T) * sc[rows]
+                err = np.abs(y[0].cpu().numpy()[rows].astype(np.float64) - expect)
+                out["parity_64_rows"] = {"ok": bool((err <= bound).all()), "max_err_over_bound": float((err / bound).max())}
+    out["kernel"] = dec.last_kernel()
+    return out
+
+
 def run_case(args, dec, device):
     """ONE small case instead of the benchmark (what the profiler captures in profiles/ run)."""
     import torch
-    if args.case.startswith("moe:"):
+    if args.case.startswith("head:"):
+        T = int(args.case.split(":")[1])
+        n, k = synth.LM_HEAD_27B
+        upload_synthetic_head(dec, n, k, device)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(1)
+        xh = torch.randn((T, k), generator=gen, device=device, dtype=torch.float32)
+        yh = torch.empty((T, n), device=device, dtype=torch.float32)
+        fn = lambda: dec.head_forward(xh, T, out=yh)  # noqa: E731
+    elif args.case.startswith("moe:"):
         T = int(args.case.split(":")[1])
         mo = synth.MOE_35B
         ne, h, f, kk, grp = mo["n_experts"], mo["hidden"], mo["moe_ffn"], mo["top_k"], mo["group"]
@@ -393,6 +450,7 @@ def measure(args, dec, device, rank, world, local_rank, peaks, peak_kind):
         if world == 1:
             roofline_prefill, extras["prefill"] = prefill_sweep(dec, device, st, shapes, L, peaks, g)
             extras["moe_35b_a3b_layer"] = moe_layer(dec, dist, device, st, rank, world, g)
+            extras["lm_head_int8"] = lm_head(dec, device, st, peaks, g)
         else:
             extras["tp_prefill_M4096"] = tp_prefill(dec, dist, device, st, shapes, L, g)
             extras["ep_moe_35b_a3b_layer"] = moe_layer(dec, dist, device, st, rank, world, g)

@@ -184,6 +184,24 @@ W4A16_API int w4a16_lin_forward_x32(w4a16_dec* dec, const char* name, const floa
  * crates/server/src/probes/w4a16/gates.rs:108-138 compares bit for bit. A checking tool, not a fast path. */
 W4A16_API int w4a16_lin_forward_lane(w4a16_dec* dec, const char* name, const void* x16_dev, float* dst_dev, int t,
                                      void* stream);
+
+/* ---- int8 lm-head ------------------------------------------------------------------------- */
+/* W4a16Dec::upload_head (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:1472-1569): w is the bf16 [n][k] matrix
+ * on the host; every row is quantised to int8 with scale = absmax/127 (1 for a zero row) and
+ * q = round-half-away(v / scale) clamped to +-127 -- on the device, bit-identical to the host recipe.
+ * k must be a multiple of 64.  Replaces an earlier lm-head of the decoder. */
+W4A16_API int w4a16_upload_head(w4a16_dec* dec, const void* w_bf16_host, size_t bytes, int n, int k);
+/* head_n / head_k of the decoder (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:1564-1568). */
+W4A16_API int w4a16_head_spec(w4a16_dec* dec, int* n, int* k);
+/* Reads the quantised rows (int8 [n][k], two's complement) and the f32 row scales back; scale_host may be NULL.
+ * For tests of the quantiser; no counterpart in the reference. */
+W4A16_API int w4a16_head_unpack(w4a16_dec* dec, void* q_host, void* scale_host);
+/* head_gemv_launch / head_gemv_t_launch (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/gemv.rs:64-110; kernels
+ * w4a16_gemv_i8, w4a16_gemv_i8_t, crates/backend-gpu/src/rawcuda/assets/head.cu:100-225):
+ * out[t][n] f32 = (sum_k q[n][k] * x[t][k]) * scale[n] for x f32 [t][k] on the device, 1 <= t <= 16.
+ * The sum runs on the tensor cores with x split into two f16 planes (|x| must lie inside the f16 range);
+ * it agrees with the reference's f32 lane sum within 1e-5 of sum_k |q x| * scale (both are f32 sums in different orders). */
+W4A16_API int w4a16_head_forward(w4a16_dec* dec, const float* x32_dev, float* out_dev, int t, void* stream);
 /* W4a16Dec::sk_single_dev (crates/backend-gpu/src/rawcuda/w4a16_dec/kernels/decode.rs:89-127):
  * the decode GEMV on one linear, t in 1..8. */
 W4A16_API int w4a16_sk_single_dev(w4a16_dec* dec, const char* name, const void* x16_dev, void* out_dev, int t,

@@ -48,6 +48,10 @@ _SIGS = {
     "w4a16_lin_forward": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
     "w4a16_lin_forward_x32": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
     "w4a16_lin_forward_lane": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _vp]),
+    "w4a16_upload_head": (_i, [_vp, _vp, C.c_size_t, _i, _i]),
+    "w4a16_head_spec": (_i, [_vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "w4a16_head_unpack": (_i, [_vp, _vp, _vp]),
+    "w4a16_head_forward": (_i, [_vp, _vp, _vp, _i, _vp]),
     "w4a16_sk_single_dev": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
     "w4a16_sk_single_static": (_i, [_vp, C.c_char_p, _vp, _vp, _i, _i, _vp]),
     "w4a16_tp_create": (_i, [_vp, _i, _i, _i, _vp]),

@@ -443,6 +443,9 @@ int w4a16_dec_new(int device, w4a16_dec** out) {
     if (e == cudaSuccess) {
         e = w4::gemm_init_device();
     }
+    if (e == cudaSuccess) {
+        e = w4::head_init_device();
+    }
     if (e != cudaSuccess) {
         g_create_error = std::string("w4a16_dec_new: ") + cudaGetErrorString(e);
         delete dec;
@@ -469,6 +472,10 @@ void w4a16_dec_free(w4a16_dec* dec) {
         d.free_lin(kv.second);
     }
     d.lins.clear();
+    if (d.head_q) {
+        cudaFree(d.head_q);
+        cudaFree(d.head_scale);
+    }
     for (void* p : d.retired) {
         cudaFree(p);
     }

@@ -75,6 +75,10 @@ struct Dec {
     size_t pin_cap = 0;
     void* x16 = nullptr;         // f16 copy of f32 activations (w4a16_lin_forward_x32)
     size_t x16_cap = 0;
+    // int8 lm-head (head.cu): offset-binary bytes [n][k], f32 row scales
+    uint8_t* head_q = nullptr;
+    float* head_scale = nullptr;
+    int head_n = 0, head_k = 0;
     // knobs
     int tune_gemv_stages = 4;
     int tune_gemv_warps = 8;

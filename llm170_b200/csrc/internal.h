@@ -140,6 +140,7 @@ cudaError_t gemv_sk_init_device();
 // ---- gemm_tc.cu ------------------------------------------------------------------------------
 // Raises the dynamic shared-memory limit of the tensor-core GEMM kernels on the current device.
 cudaError_t gemm_init_device();
+cudaError_t head_init_device();
 
 // ---- moe.cu ----------------------------------------------------------------------------------
 struct MoeBufs;

@@ -63,6 +63,9 @@ DENSE_27B = {
     "o_proj": (6144, 5120),
 }
 
+# lm-head of the same 27B-class decoder: (vocabulary rows, hidden).
+LM_HEAD_27B = (151936, 5120)
+
 # 35B-A3B-class MoE layer.
 MOE_35B = {"n_experts": 128, "hidden": 2048, "moe_ffn": 768, "top_k": 8, "group": 32}
 

@@ -196,6 +196,35 @@ class W4a16Dec:
         self._ck(self._L.w4a16_lin_forward_lane(self._h, name.encode(), x16.data_ptr(), dst.data_ptr(), t, _cur_stream()))
         return dst
 
+    # -- int8 lm-head ------------------------------------------------------------------------
+    def upload_head(self, w_bf16: np.ndarray, n: int, k: int):
+        """upload.rs:1472-1569: bf16 [n,k] host matrix (uint16 bit patterns) -> int8 rows + f32 scales on the device."""
+        w = np.ascontiguousarray(w_bf16, dtype=np.uint16)
+        self._ck(self._L.w4a16_upload_head(self._h, w.ctypes.data, w.nbytes, n, k))
+
+    def head_spec(self):
+        n, k = C.c_int(0), C.c_int(0)
+        self._ck(self._L.w4a16_head_spec(self._h, C.byref(n), C.byref(k)))
+        return n.value, k.value
+
+    def head_unpack(self):
+        """The quantised lm-head as (int8 [n,k], f32 [n]) host arrays."""
+        n, k = self.head_spec()
+        q = np.zeros((n, k), np.int8)
+        sc = np.zeros(n, np.float32)
+        self._ck(self._L.w4a16_head_unpack(self._h, q.ctypes.data, sc.ctypes.data))
+        return q, sc
+
+    def head_forward(self, x32: torch.Tensor, t: int = 1, out: torch.Tensor | None = None) -> torch.Tensor:
+        """kernels/gemv.rs:64-110 (head_gemv_launch / head_gemv_t_launch): f32 [t,k] -> f32 logits [t,n]."""
+        n, k = self.head_spec()
+        self._tensor_ok(x32, torch.float32, "x32")
+        if x32.numel() != t * k:
+            raise W4a16Error(f"head_forward: x has {x32.numel()} elements, need {t}x{k}")
+        out = self._out(t, n, False, out)
+        self._ck(self._L.w4a16_head_forward(self._h, x32.data_ptr(), out.data_ptr(), t, _cur_stream()))
+        return out
+
     def sk_single_dev(self, name: str, x16: torch.Tensor, out: torch.Tensor | None = None, t: int = 1,
                       out_f16: bool = False) -> torch.Tensor:
         """kernels/decode.rs:89-127: split-K decode GEMV on one linear."""

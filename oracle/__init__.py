@@ -68,6 +68,10 @@ def lib() -> ctypes.CDLL:
         L.orc_linear_lane_rows.argtypes = [vp, vp, vp, vp] + [c.c_int] * 8
         L.orc_linear_lane.restype = c.c_int
         L.orc_linear_lane.argtypes = [vp, vp, vp, vp] + [c.c_int] * 6
+        L.orc_head_quant.restype = c.c_int
+        L.orc_head_quant.argtypes = [vp, c.c_int, c.c_int, vp, vp]
+        L.orc_head_gemv_i8.restype = c.c_int
+        L.orc_head_gemv_i8.argtypes = [vp, vp, vp, vp, c.c_int, c.c_int, c.c_int]
         _lib = L
     return _lib
 
@@ -227,4 +231,28 @@ def moe_ffn(x_u16, logits, w13_q, w13_s, w2_q, w2_s, top_k: int, group: int, exp
     out = np.zeros((t, h), np.float32)
     for r in range(top_k):
         out = out + contrib[:, r]
+    return out
+
+
+def head_quant(w_bf16, n: int, k: int):
+    """crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:1472-1518: per-row int8 quantisation of the bf16 lm-head
+    (scale = absmax/127, round half away from zero).  Returns (q int8 [n,k], scale f32 [n])."""
+    w = _c(w_bf16, np.uint16).reshape(n, k)
+    q = np.zeros((n, k), np.int8)
+    sc = np.zeros(n, np.float32)
+    if lib().orc_head_quant(_p(w), n, k, _p(q), _p(sc)) != 0:
+        raise ValueError("head_quant: bad shape")
+    return q, sc
+
+
+def head_gemv_i8(q, scale, x32, t: int) -> np.ndarray:
+    """crates/backend-gpu/src/rawcuda/assets/head.cu:100-225 (64 lanes, un-fused f32 products, f64 tree):
+    out f32 [t,n] = (q @ x^T) * scale."""
+    q = _c(q, np.int8)
+    n, k = q.shape
+    x = _c(x32, np.float32).reshape(t, k)
+    sc = _c(scale, np.float32)
+    out = np.zeros((t, n), np.float32)
+    if lib().orc_head_gemv_i8(_p(q), _p(sc), _p(x), _p(out), n, k, t) != 0:
+        raise ValueError("head_gemv_i8: bad shape")
     return out

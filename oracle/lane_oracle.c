@@ -414,3 +414,66 @@ ORC_API int orc_linear_lane(const uint32_t *q, const uint16_t *s, const uint16_t
                             int m, int n, int k, int group, int scale_bf16, int nthreads) {
     return orc_linear_lane_rows(q, s, x, out, m, n, k, group, scale_bf16, 0, n, nthreads);
 }
+
+/* ---- int8 lm-head (crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:1472-1518, assets/head.cu:100-225) ----
+ * Quantiser: per row of a bf16 [n][k] matrix, scale = absmax/127 (1 when the row is zero) and
+ * q = round-half-away-from-zero(v / scale) clamped to [-127, 127] (Rust's f32::round), all in f32. */
+ORC_API int orc_head_quant(const uint16_t *w_bf16, int n, int k, int8_t *q, float *scale) {
+    if (n < 1 || k < 1) {
+        return -1;
+    }
+    for (int r = 0; r < n; ++r) {
+        const uint16_t *row = w_bf16 + (size_t)r * k;
+        float amax = 0.0f;
+        for (int i = 0; i < k; ++i) {
+            float v = fabsf(orc_bf16_to_f32(row[i]));
+            amax = v > amax ? v : amax;
+        }
+        float s = amax > 0.0f ? amax / 127.0f : 1.0f;
+        scale[r] = s;
+        for (int i = 0; i < k; ++i) {
+            float v = roundf(orc_bf16_to_f32(row[i]) / s);
+            v = v < -127.0f ? -127.0f : (v > 127.0f ? 127.0f : v);
+            q[(size_t)r * k + i] = (int8_t)v;
+        }
+    }
+    return 0;
+}
+
+/* GEMV in the order of w4a16_gemv_i8 / w4a16_gemv_i8_t (assets/head.cu:100-225, built with -fmad=false): 64 lanes,
+ * lane l takes the 4-byte words l, l+64, ... of the row and adds its four products one after the other (separate
+ * f32 multiply and add); the 64 lane sums are added in f64 as lanes (l, l+32), then offsets 16, 8, 4, 2, 1;
+ * out = (float)sum * scale.  x is f32 [t][k], out f32 [t][n]. */
+ORC_API int orc_head_gemv_i8(const int8_t *q, const float *scale, const float *x, float *out, int n, int k, int t) {
+    if (n < 1 || k < 4 || k % 4 != 0 || t < 1) {
+        return -1;
+    }
+    const int k4 = k / 4;
+    for (int r = 0; r < t; ++r) {
+        const float *xr = x + (size_t)r * k;
+        for (int o = 0; o < n; ++o) {
+            const int8_t *w = q + (size_t)o * k;
+            double red[64];
+            for (int l = 0; l < 64; ++l) {
+                float acc = 0.0f;
+                for (int i = l; i < k4; i += 64) {
+                    acc += (float)w[4 * i] * xr[4 * i];
+                    acc += (float)w[4 * i + 1] * xr[4 * i + 1];
+                    acc += (float)w[4 * i + 2] * xr[4 * i + 2];
+                    acc += (float)w[4 * i + 3] * xr[4 * i + 3];
+                }
+                red[l] = (double)acc;
+            }
+            for (int l = 0; l < 32; ++l) {
+                red[l] += red[l + 32];
+            }
+            for (int off = 16; off >= 1; off >>= 1) {
+                for (int l = 0; l < off; ++l) {
+                    red[l] += red[l + off];
+                }
+            }
+            out[(size_t)r * n + o] = (float)red[0] * scale[o];
+        }
+    }
+    return 0;
+}

@@ -364,3 +364,35 @@ def test_moe_ffn_equals_stepwise_chain_of_pinned_primitives(orc):
     wd = nib * np.repeat(w13_s[e].view(np.float16).astype(np.float64), group, axis=1)
     exact = (x.view(np.float16).astype(np.float64) @ wd.T).astype(np.float32)
     assert np.array_equal(orc.linear_lane(w13_q[e], w13_s[e], x, t, 2 * f, h, group), exact)
+
+
+# ---- int8 lm-head (no known-answer test of its own in the reference: checked on inputs whose answer is forced) ----
+def test_head_quant_recipe_on_forced_values(orc):
+    # crates/backend-gpu/src/rawcuda/w4a16_dec/upload.rs:1495-1516: scale = absmax/127 (1 for a zero row),
+    # q = round-half-away(v/scale) clamped to +-127
+    def bf16(v):
+        return (np.asarray(v, np.float32).view(np.uint32) >> 16).astype(np.uint16)   # values below are exact in bf16
+    rows = np.zeros((3, 8), np.float32)
+    rows[0] = [127.0, 0.5, 1.5, -2.5, -0.5, 63.5, -126.5, 3.0]     # scale 1: ties go away from zero
+    rows[2] = [0.25, -0.125, 0.0, 0.0625, -0.25, 0.125, 0.0, 0.0]  # scale 0.25/127
+    q, sc = orc.head_quant(bf16(rows), 3, 8)
+    assert sc.tolist() == [1.0, 1.0, np.float32(0.25) / np.float32(127.0)]
+    assert q[0].tolist() == [127, 1, 2, -3, -1, 64, -127, 3]
+    assert not q[1].any()
+    assert q[2].tolist() == [127, -64, 0, 32, -127, 64, 0, 0]      # 63.5 -> 64, 31.75 -> 32
+
+
+def test_head_gemv_lane_order_exact_and_random(orc):
+    # exact case: integers times powers of two, every partial sum exact -> equals float64 arithmetic
+    n, k = 8, 512
+    q = ((np.arange(n * k).reshape(n, k) * 11) % 255 - 127).astype(np.int8)
+    sc = (2.0 ** -(np.arange(n) % 4)).astype(np.float32)
+    x = (2.0 ** ((np.arange(2 * k) % 7) - 3)).astype(np.float32).reshape(2, k)
+    y = orc.head_gemv_i8(q, sc, x, 2)
+    assert np.array_equal(y, ((x.astype(np.float64) @ q.astype(np.float64).T) * sc).astype(np.float32))
+    # random case: the lane order stays within f32 rounding of the exact sum
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((1, k)).astype(np.float32)
+    y = orc.head_gemv_i8(q, sc, x, 1)
+    exact = (x.astype(np.float64) @ q.astype(np.float64).T) * sc
+    assert np.abs(y - exact).max() <= 1e-6 * (np.abs(x).astype(np.float64) @ np.abs(q).astype(np.float64).T * sc).max()
