@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "libw4a16_b200.so")
 HASH = SO + ".srchash"
-SOURCES = ["dec.cu", "repack.cu", "gemv.cu", "gemv_sk.cu", "gemm_tc.cu", "moe.cu", "moe_host.cu", "gemv_static.cu", "loader.cu", "head.cu"]
+SOURCES = ["dec.cu", "repack.cu", "gemv.cu", "gemv_sk.cu", "gemv_rb.cu", "gemm_tc.cu", "moe.cu", "moe_host.cu", "gemv_static.cu", "loader.cu", "head.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall", "--shared", "-cudart", "static",

@@ -198,6 +198,19 @@ int Dec::gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& 
         }
         a.tp = tp;
     }
+    // Up to four tokens of a g128 linear whose weights are at most 24 MB: CTAs that own whole rows, no scratch, no
+    // ticket (gemv_rb.cu).  Its plain loads stream at about 4 TB/s at best (the loads an SM may have in flight bound
+    // them), the persistent form's bulk copies at 6: measured on B200, the row-block form wins while the launch is
+    // short enough for the persistent form's 7 us around its loop to weigh more (qkv 7.0 against 10.5 us, o_proj 8.0
+    // against 9.4; down 18 against 13.8, gate_up equal).
+    const size_t w_bytes = (size_t)a.seg[0].n * a.k / 2;
+    if (tune_gemv_rowblock && gemv_rb_fits(a) && (tune_gemv_rowblock > 1 || w_bytes <= ((size_t)24 << 20))) {
+        c.form = GemvChoice::ROWBLOCK;
+        c.grid_x = gemv_rb_plan(a, sm_count, c.rbw);
+        a.ksplit = 1;
+        snprintf(c.name, sizeof(c.name), "gemv_rb_kernel<%d>", c.rbw);
+        return 0;
+    }
     c.sk = sk_make_plan(a.k, a.group, t, c.grid_x, sm_count, tune_gemv_sk_stages, tune_gemv_sk_prefetch);
     // measured on B200: the persistent form wins up to 4 tokens; at 5..8 its single-CTA sum of a row block costs
     // more than the cluster reduce of the (row block, K split) form
@@ -240,6 +253,9 @@ int Dec::gemv_run(GemvArgs& a, const GemvChoice& c, cudaStream_t st) {
     switch (c.form) {
     case GemvChoice::PERSISTENT:
         e = launch_gemv_sk(a, c.sk, st);
+        break;
+    case GemvChoice::ROWBLOCK:
+        e = launch_gemv_rb(a, c.grid_x, c.rbw, sm_count, st);
         break;
     default:
         e = launch_gemv(a, c.grid_x, st);
@@ -439,6 +455,9 @@ int w4a16_dec_new(int device, w4a16_dec** out) {
         if (e == cudaSuccess) {
             e = w4::gemv_sk_init_device();
         }
+        if (e == cudaSuccess) {
+            e = w4::gemv_rb_init_device();
+        }
     }
     if (e == cudaSuccess) {
         e = w4::gemm_init_device();
@@ -606,6 +625,13 @@ int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
     }
     if (!strcmp(key, "gemv_cluster")) {
         d.tune_gemv_cluster = value != 0;
+        return 0;
+    }
+    if (!strcmp(key, "gemv_rowblock")) {
+        if (value < 0 || value > 2) {
+            return d.fail("w4a16 tuning: gemv_rowblock must be 0, 1 or 2");
+        }
+        d.tune_gemv_rowblock = value;
         return 0;
     }
     if (!strcmp(key, "gemv_persistent")) {

@@ -43,11 +43,12 @@ struct MoeBufs {
 
 // The form of the decode GEMV chosen for a call (Dec::gemv_select).
 struct GemvChoice {
-    enum Form { PERSISTENT, SPLIT } form = SPLIT;
+    enum Form { PERSISTENT, SPLIT, ROWBLOCK } form = SPLIT;
     SkPlan sk{};
-    int grid_x = 0;            // 256-row blocks over all segments
+    int grid_x = 0;            // 256-row blocks over all segments (16-row blocks in the row-block form)
     size_t part_floats = 0;    // partial-sum scratch the launch needs
     size_t tickets = 0;        // arrival tickets the launch needs
+    int rbw = 2;               // row-block form: 16-row blocks per CTA unit
     char name[64] = {0};       // the kernel instantiation, for reports
 };
 
@@ -84,6 +85,7 @@ struct Dec {
     int tune_gemv_warps = 8;
     int tune_gemv_sk_stages = 4;   // most 16 KB ring stages of the persistent GEMV (2..6; fewer when x needs the room)
     int tune_gemv_sk_prefetch = 2; // ring stages the persistent GEMV requests before the previous kernel is complete
+    int tune_gemv_rowblock = 1;    // up to four tokens of a g128 linear run one small CTA per 16-row block (gemv_rb.cu)
     int tune_gemv_persistent = 1;  // dense decode GEMV as two persistent CTAs per SM with equal unit ranges (gemv_sk.cu)
     int tune_gemv_cluster = 1;   // K splits of a row block as a thread-block cluster (DSMEM reduce) when 2 <= ksplit <= 8
     int tune_gemv_subnormal = 1;

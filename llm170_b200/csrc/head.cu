@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(HEAD_THREADS, 1) head_gemv_i8_kernel(const Hea
         const uint4* p0 = reinterpret_cast<const uint4*>(a.q + (size_t)r0 * k) + tq;
         const uint4* p1 = reinterpret_cast<const uint4*>(a.q + (size_t)r1 * k) + tq;
         float ch[4] = {0.f, 0.f, 0.f, 0.f}, cl[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
+#pragma unroll 8
         for (int s = 0; s < nsteps; ++s) {
             // 64 channels: this lane's 16 bytes of row g and of row g+8 (the four lanes of a row cover 64 contiguous bytes)
             const uint4 w0 = __ldg(p0 + s * 4), w1 = __ldg(p1 + s * 4);

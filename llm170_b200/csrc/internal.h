@@ -136,6 +136,10 @@ SkPlan sk_make_plan(int k, int group, int m, int rows, int sm_count, int max_sta
 size_t sk_part_floats(const SkPlan& p);   // scratch for parked partial sums; counters: one per row block
 cudaError_t launch_gemv_sk(const GemvArgs& a, const SkPlan& p, cudaStream_t st);
 cudaError_t gemv_sk_init_device();
+cudaError_t gemv_rb_init_device();
+bool gemv_rb_fits(const GemvArgs& a);
+int gemv_rb_plan(GemvArgs& a, int sm_count, int& rbw);
+cudaError_t launch_gemv_rb(const GemvArgs& a, int total_units, int rbw, int sm_count, cudaStream_t st);
 
 // ---- gemm_tc.cu ------------------------------------------------------------------------------
 // Raises the dynamic shared-memory limit of the tensor-core GEMM kernels on the current device.

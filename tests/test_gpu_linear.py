@@ -303,6 +303,7 @@ def test_debug_timeline_stamps_are_ordered(dec):
     q, s = synth.make_linear(n, k, 128, seed=3)
     dec.upload_lin_g("tl", q, s, n, k, 128)
     x = x_dev(synth.make_acts(1, k, seed=4))
+    dec.set_tuning("gemv_rowblock", 0)            # the timeline is kept by the persistent form
     ref = dec.sk_single_dev("tl", x).clone()
     dec.set_tuning("debug_timeline", 1)
     try:
@@ -317,6 +318,7 @@ def test_debug_timeline_stamps_are_ordered(dec):
         assert torch.equal(y, ref)            # the stamps do not change the result
     finally:
         dec.set_tuning("debug_timeline", 0)
+        dec.set_tuning("gemv_rowblock", 1)
     with pytest.raises(Exception):
         dec.debug_timeline()                  # off again: the call says so
 
@@ -443,3 +445,26 @@ def test_f32_activation_entry_and_multi_segment_above_eight_rows(dec, orc):
         b = dec.lin_forward("q16", x[:t].contiguous(), t)
         dec.sync()
         assert torch.equal(a, b)
+
+
+# The reference's batch-decode and speculative-verify chains call the same two entry points with 2..32 rows
+# (crates/backend-gpu/src/rawcuda/w4a16_dec/chains.rs:315-507: lin_forward / gemv_multi_t_dev at t = slots or t <= 9 for
+# the MTP verify).  Every row count of that band against the lane oracle, through the fused q|k|v call and the single one.
+@pytest.mark.parametrize("t", [2, 3, 4, 5, 7, 8, 9, 12, 32])
+def test_batch_decode_row_counts_vs_lane_oracle(dec, orc, t):
+    k = 1024
+    segs = [("bq", 512), ("bk", 128), ("bv", 144)]
+    xs = synth.make_acts(t, k, seed=300 + t)
+    x = x_dev(xs)
+    qs = {}
+    for i, (nm, n) in enumerate(segs):
+        qs[nm] = synth.make_linear(n, k, 128, seed=310 + i)
+        dec.upload_lin_g(nm, *qs[nm], n, k, 128)
+    outs = dec.sk_multi_dev([nm for nm, _ in segs], x, t=t)
+    dec.sync()
+    for (nm, n), o in zip(segs, outs):
+        expect = orc.linear_lane(qs[nm][0], qs[nm][1], xs, t, n, k, 128)
+        assert np.abs(o.cpu().numpy() - expect).max() <= TOL
+        single = dec.lin_forward(nm, x, t)
+        dec.sync()
+        assert np.abs(single.cpu().numpy() - expect).max() <= TOL
