@@ -203,8 +203,11 @@ int Dec::gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& 
     // them), the persistent form's bulk copies at 6: measured on B200, the row-block form wins while the launch is
     // short enough for the persistent form's 7 us around its loop to weigh more (qkv 7.0 against 10.5 us, o_proj 8.0
     // against 9.4; down 18 against 13.8, gate_up equal).
+    // Long K also favours the persistent form (a warp of the row-block form walks its K range with six k-blocks in
+    // flight: the down shard of two GPUs, K = 8704, ran 17.1 against 14.8 us).
     const size_t w_bytes = (size_t)a.seg[0].n * a.k / 2;
-    if (tune_gemv_rowblock && gemv_rb_fits(a) && (tune_gemv_rowblock > 1 || w_bytes <= ((size_t)24 << 20))) {
+    if (tune_gemv_rowblock && gemv_rb_fits(a) &&
+        (tune_gemv_rowblock > 1 || (w_bytes <= ((size_t)24 << 20) && a.k <= 6144))) {
         c.form = GemvChoice::ROWBLOCK;
         c.grid_x = gemv_rb_plan(a, sm_count, c.rbw);
         a.ksplit = 1;
