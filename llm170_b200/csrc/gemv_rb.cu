@@ -138,13 +138,15 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
     }
     cursor_init(fw);
     cursor_init(fs);
+    if (nk > 0) {               // a warp without a group (fewer groups than warps) only takes part in the sums
 #pragma unroll
-    for (int u = 0; u < RB_U; ++u) {
-        fetch(wq[u]);
-    }
+        for (int u = 0; u < RB_U; ++u) {
+            fetch(wq[u]);
+        }
 #pragma unroll
-    for (int u = 0; u < RB_U / 2; ++u) {
-        fetch_scale(sq[u]);
+        for (int u = 0; u < RB_U / 2; ++u) {
+            fetch_scale(sq[u]);
+        }
     }
 
     // ---- x may be the previous kernel's output: only now wait for it; stage it and its group sums --------------
@@ -223,7 +225,61 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
         tot[r][0] = tot[r][1] = tot[r][2] = tot[r][3] = 0.f;
     }
     int units_done = 0;
-    int crb = rb_first, kin = 0;                                           // first row block of the unit and k-block (inside the warp's range) being multiplied
+    int crb = rb_first;                                                    // first row block of the unit being multiplied
+    // ---- a unit is complete in this warp: the eight warps' sums meet in shared memory -------------------------------
+    auto flush_unit = [&]() {
+        const int buf = units_done & 1;
+        if (t < RB_MAXTOK / 2) {
+#pragma unroll
+            for (int r = 0; r < RBW; ++r) {
+                // nibble units -> values: 2^24 for rows g, 2^20 for rows g+8
+                red[buf][warp][r][g][2 * t] = tot[r][0] * 16777216.f;
+                red[buf][warp][r][g][2 * t + 1] = tot[r][1] * 16777216.f;
+                red[buf][warp][r][g + 8][2 * t] = tot[r][2] * 1048576.f;
+                red[buf][warp][r][g + 8][2 * t + 1] = tot[r][3] * 1048576.f;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < RBW; ++r) {
+            tot[r][0] = tot[r][1] = tot[r][2] = tot[r][3] = 0.f;
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < RBW * TILE_ROWS * a.m) {
+            const int tok = (int)threadIdx.x / (RBW * TILE_ROWS), r32 = (int)threadIdx.x % (RBW * TILE_ROWS);
+            const int r = r32 / TILE_ROWS, row = r32 % TILE_ROWS;
+            if (crb + r < nrb) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < RB_WARPS; ++w) {
+                    v += red[buf][w][r][row][tok];                         // fixed order: the same bits every run
+                }
+                v *= sg.out_mul;
+                const size_t o = (size_t)tok * sg.n + (size_t)(crb + r) * TILE_ROWS + row;
+                if (tp_on) {
+                    // row-parallel shard: the local sum goes to this rank's slot, the exchange below adds the peers'
+                    tp_own_area(a.tp, s_seq)[(size_t)tok * a.tp.max_rows + (size_t)(crb + r) * TILE_ROWS + row] = v;
+                } else if (a.out_f16) {
+                    reinterpret_cast<__half*>(sg.out)[o] = __float2half_rn(v);
+                } else {
+                    reinterpret_cast<float*>(sg.out)[o] = v;
+                }
+            }
+        }
+        if (tp_on) {
+            // all threads: push the unit's sums to every peer, wait (bounded) for theirs, add, store
+            tp_exchange(a, sg, crb, min(RBW, nrb - crb) * TILE_ROWS, &s_seq, &s_abort, (unsigned)total_units);
+        }
+        ++units_done;
+        crb += ustride;
+    };
+    if (nk == 0) {
+        // fewer groups than warps: this warp adds zeros, once per unit, so that the CTA's barriers stay matched
+        for (int j = 0; j < my_units; ++j) {
+            flush_unit();
+        }
+        return;
+    }
+    int kin = 0;                                                           // k-block (inside the warp's range) being multiplied
     for (int base = 0; base < S; base += RB_U) {
 #pragma unroll
         for (int u = 0; u < RB_U; u += 2) {
@@ -290,50 +346,7 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
                     tot[r][3] = fmaf(cg[r][3], sf.y, tot[r][3]);
                 }
                 if (kin + 2 == nk) {
-                    // ---- the unit is complete in this warp: the eight warps' sums meet in shared memory ----------
-                    const int buf = units_done & 1;
-                    if (t < RB_MAXTOK / 2) {
-#pragma unroll
-                        for (int r = 0; r < RBW; ++r) {
-                            // nibble units -> values: 2^24 for rows g, 2^20 for rows g+8
-                            red[buf][warp][r][g][2 * t] = tot[r][0] * 16777216.f;
-                            red[buf][warp][r][g][2 * t + 1] = tot[r][1] * 16777216.f;
-                            red[buf][warp][r][g + 8][2 * t] = tot[r][2] * 1048576.f;
-                            red[buf][warp][r][g + 8][2 * t + 1] = tot[r][3] * 1048576.f;
-                        }
-                    }
-#pragma unroll
-                    for (int r = 0; r < RBW; ++r) {
-                        tot[r][0] = tot[r][1] = tot[r][2] = tot[r][3] = 0.f;
-                    }
-                    __syncthreads();
-                    if ((int)threadIdx.x < RBW * TILE_ROWS * a.m) {
-                        const int tok = (int)threadIdx.x / (RBW * TILE_ROWS), r32 = (int)threadIdx.x % (RBW * TILE_ROWS);
-                        const int r = r32 / TILE_ROWS, row = r32 % TILE_ROWS;
-                        if (crb + r < nrb) {
-                            float v = 0.f;
-#pragma unroll
-                            for (int w = 0; w < RB_WARPS; ++w) {
-                                v += red[buf][w][r][row][tok];             // fixed order: the same bits every run
-                            }
-                            v *= sg.out_mul;
-                            const size_t o = (size_t)tok * sg.n + (size_t)(crb + r) * TILE_ROWS + row;
-                            if (tp_on) {
-                                // row-parallel shard: the local sum goes to this rank's slot, the exchange below adds the peers'
-                                tp_own_area(a.tp, s_seq)[(size_t)tok * a.tp.max_rows + (size_t)(crb + r) * TILE_ROWS + row] = v;
-                            } else if (a.out_f16) {
-                                reinterpret_cast<__half*>(sg.out)[o] = __float2half_rn(v);
-                            } else {
-                                reinterpret_cast<float*>(sg.out)[o] = v;
-                            }
-                        }
-                    }
-                    if (tp_on) {
-                        // all threads: push the unit's sums to every peer, wait (bounded) for theirs, add, store
-                        tp_exchange(a, sg, crb, min(RBW, nrb - crb) * TILE_ROWS, &s_seq, &s_abort, (unsigned)total_units);
-                    }
-                    ++units_done;
-                    crb += ustride;
+                    flush_unit();
                     kin = 0;
                 } else {
                     kin += 2;
@@ -363,10 +376,9 @@ static size_t gemv_rb_smem(const GemvArgs& a) {
     return (size_t)a.m * ((size_t)a.k * 2 + RB_XPAD) + (size_t)(a.k / RB_GROUP) * RB_MAXTOK * sizeof(float);
 }
 
-// Whether the row-block form can take this call: one segment, 128-channel groups, at most four tokens, at least one
-// group per warp, x small enough for two CTAs per SM.
+// Whether the row-block form can take this call: one segment, 128-channel groups, at most four tokens, x small enough for two CTAs per SM.
 bool gemv_rb_fits(const GemvArgs& a) {
-    return a.nseg == 1 && a.group == RB_GROUP && a.m >= 1 && a.m <= RB_MAXTOK && a.k % RB_GROUP == 0 && a.k / RB_GROUP >= RB_WARPS &&
+    return a.nseg == 1 && a.group == RB_GROUP && a.m >= 1 && a.m <= RB_MAXTOK && a.k % RB_GROUP == 0 && a.k / RB_GROUP >= 1 &&
            gemv_rb_smem(a) <= (size_t)100 * 1024;
 }
 

@@ -468,3 +468,21 @@ def test_batch_decode_row_counts_vs_lane_oracle(dec, orc, t):
         single = dec.lin_forward(nm, x, t)
         dec.sync()
         assert np.abs(single.cpu().numpy() - expect).max() <= TOL
+
+
+# The row-block form deals the scale groups of K to eight warps; shapes with fewer groups than warps (the K slices of
+# tensor-parallel shards: o_proj over 8 GPUs has K = 768) leave some warps without a group.
+@pytest.mark.parametrize("n,k", [(512, 768), (272, 128), (1040, 384), (4736, 1152)])
+@pytest.mark.parametrize("t", [1, 3, 4])
+def test_row_block_form_with_fewer_groups_than_warps(dec, orc, n, k, t):
+    q, s = synth.make_linear(n, k, 128, seed=500 + k)
+    dec.upload_lin_g("fewg", q, s, n, k, 128)
+    xs = synth.make_acts(t, k, seed=510 + t)
+    y = dec.sk_single_dev("fewg", x_dev(xs), t=t)
+    dec.sync()
+    assert dec.last_kernel().startswith("gemv_rb_kernel")
+    expect = orc.linear_lane(q, s, xs, t, n, k, 128)
+    assert np.abs(y.cpu().numpy() - expect).max() <= TOL
+    y2 = dec.sk_single_dev("fewg", x_dev(xs), t=t)
+    dec.sync()
+    assert torch.equal(y, y2)
