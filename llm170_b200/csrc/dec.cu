@@ -198,16 +198,16 @@ int Dec::gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& 
         }
         a.tp = tp;
     }
-    // Up to four tokens of a g128 linear whose weights are at most 24 MB: CTAs that own whole rows, no scratch, no
-    // ticket (gemv_rb.cu).  Its plain loads stream at about 4 TB/s at best (the loads an SM may have in flight bound
-    // them), the persistent form's bulk copies at 6: measured on B200, the row-block form wins while the launch is
-    // short enough for the persistent form's 7 us around its loop to weigh more (qkv 7.0 against 10.5 us, o_proj 8.0
-    // against 9.4; down 18 against 13.8, gate_up equal).
-    // Long K also favours the persistent form (a warp of the row-block form walks its K range with six k-blocks in
-    // flight: the down shard of two GPUs, K = 8704, ran 17.1 against 14.8 us).
+    // Up to four tokens of a g128 linear with K <= 6144 and at most 48 MB of weights: CTAs that own whole rows, no
+    // scratch, no ticket (gemv_rb.cu).  Its plain loads stream at about 4 TB/s at best (the loads an SM may have in
+    // flight bound them), the persistent form's bulk copies at 6, and a warp of the row-block form walks its K range
+    // with six k-blocks in flight.  Measured on B200 (us per launch, M = 1, row-block against persistent):
+    //   7168 x 5120 (18 MB) 7.0 / 10.5     5120 x 6144 (16 MB) 8.0 / 9.4      8704 x 5120 (22 MB)  8.3 / 11.3
+    //   5120 x 3072 (8 MB)  5.2 /  8.5     5120 x 4352 (11 MB) 6.9 / 8.8     17408 x 5120 (45 MB) 14.1 / 14.8
+    //   34816 x 5120 (89 MB) 22.5-26.8 / 22.1     5120 x 8704 (22 MB) 12.5 / 10.3     5120 x 17408 (45 MB) 23.8 / 13.9
     const size_t w_bytes = (size_t)a.seg[0].n * a.k / 2;
     if (tune_gemv_rowblock && gemv_rb_fits(a) &&
-        (tune_gemv_rowblock > 1 || (w_bytes <= ((size_t)24 << 20) && a.k <= 6144))) {
+        (tune_gemv_rowblock > 1 || (w_bytes <= ((size_t)48 << 20) && a.k <= 6144))) {
         c.form = GemvChoice::ROWBLOCK;
         c.grid_x = gemv_rb_plan(a, sm_count, c.rbw);
         a.ksplit = 1;

@@ -20,7 +20,8 @@
 // 8 KB bulk copies reach 6 TB/s inside its loop.  Two variants that fed each warp's own shared-memory ring with copies
 // instead were measured and dropped: one bulk copy per 1 KB tile pair (2.5 TB/s on gate_up: the copy engine's cost
 // per copy) and one tensor-map copy per chunk of four k-blocks x two row blocks (3.0 TB/s).  So this form is chosen
-// for SHORT launches only, where the fixed cost of the persistent form weighs more than the streaming rate.
+// for launches of moderate size and K only (Dec::gemv_select), where the fixed cost of the persistent form weighs more
+// than the streaming rate.
 // The price is the activations: every CTA stages all of x (m x k f16) and its group sums in shared memory, from L2,
 // once.  That bounds the form to small m; larger batches keep the other forms.
 #include <cuda_fp16.h>
