@@ -152,7 +152,7 @@ void launch_moe_topk(const float* logits, int* idx, float* wt, int t, int n_exp,
 // histogram -> offsets + m-tile table (tiles of `bm` rows) -> placement of the local experts' slots
 void launch_moe_align(const MoeBufs& b, int ns, int n_exp, int e0, int e1, int bm, cudaStream_t st);
 // the same tables as topk + align for at most 1024 slots, in one launch of one block
-void launch_moe_route_small(const float* logits, const MoeBufs& b, int t, int n_exp, int k, int e0, int e1, int bm,
+int launch_moe_route_small(const float* logits, const MoeBufs& b, int t, int n_exp, int k, int e0, int e1, int bm,
                             cudaStream_t st);
 void launch_moe_gather(const void* x, const MoeBufs& b, int ns, int k, int h, cudaStream_t st);
 void launch_moe_act(const MoeBufs& b, int rows_upper, int ffn, cudaStream_t st);

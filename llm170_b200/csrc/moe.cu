@@ -128,15 +128,17 @@ moe_route_small_kernel(const float* __restrict__ lg, int* __restrict__ idx, floa
                        int* __restrict__ off, int* __restrict__ pos_of_slot, int* __restrict__ slot_of_pos,
                        int* __restrict__ tile_expert, int* __restrict__ tile_row0, int* __restrict__ tile_rows,
                        int* __restrict__ n_tiles, int* __restrict__ n_rows, float* __restrict__ row_w, int t, int n_exp,
-                       int k, int e0, int e1, int bm, int stage_rows) {
+                       int k, int e0, int e1, int bm, int stage_rows, int do_topk) {
     __shared__ int s_rows[1024], s_tiles[1024], s_off[1024], s_cursor[1024];
     extern __shared__ float s_stage[];   // [32 warps][n_exp] when the launch provides it
     const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
     s_rows[tid] = 0;
     s_cursor[tid] = 0;
-    for (int ti = w; ti < t; ti += 32) {
-        topk_of_token(lg + (size_t)ti * n_exp, idx + (size_t)ti * k, wt + (size_t)ti * k, n_exp, k, lane,
-                      stage_rows ? s_stage + (size_t)w * n_exp : nullptr);
+    if (do_topk) {   // a handful of tokens: routed here; more: routed by moe_topk_kernel on many SMs just before
+        for (int ti = w; ti < t; ti += 32) {
+            topk_of_token(lg + (size_t)ti * n_exp, idx + (size_t)ti * k, wt + (size_t)ti * k, n_exp, k, lane,
+                          stage_rows ? s_stage + (size_t)w * n_exp : nullptr);
+        }
     }
     __syncthreads();   // idx / wt of every token are visible to the block
     const int ns = t * k;
@@ -362,12 +364,20 @@ void launch_moe_topk(const float* logits, int* idx, float* wt, int t, int n_exp,
         logits, idx, wt, t, n_exp, k, stage);
 }
 
-void launch_moe_route_small(const float* logits, const MoeBufs& b, int t, int n_exp, int k, int e0, int e1, int bm,
-                            cudaStream_t st) {
+// Returns the number of launches.  Up to eight tokens are routed by the table block itself (one launch); above that
+// one block's 32 warps would route two or more tokens each in turn (27 us at 64 tokens), so the routing runs on
+// many SMs first and the block only builds the tables.
+int launch_moe_route_small(const float* logits, const MoeBufs& b, int t, int n_exp, int k, int e0, int e1, int bm,
+                           cudaStream_t st) {
     const int stage = n_exp <= 256;   // 32 warps x 256 floats = 32 KB beside the 16 KB of tables
-    moe_route_small_kernel<<<1, 1024, stage ? 32 * n_exp * sizeof(float) : 0, st>>>(
+    const int own_topk = t <= 8;
+    if (!own_topk) {
+        launch_moe_topk(logits, b.idx, b.wt, t, n_exp, k, st);
+    }
+    moe_route_small_kernel<<<1, 1024, (stage && own_topk) ? 32 * n_exp * sizeof(float) : 0, st>>>(
         logits, b.idx, b.wt, b.off, b.pos_of_slot, b.slot_of_pos, b.tile_expert, b.tile_row0, b.tile_rows, b.n_tiles, b.n_rows,
-        b.row_w, t, n_exp, k, e0, e1, bm, stage);
+        b.row_w, t, n_exp, k, e0, e1, bm, stage, own_topk);
+    return own_topk ? 1 : 2;
 }
 
 void launch_moe_align(const MoeBufs& b, int ns, int n_exp, int e0, int e1, int bm, cudaStream_t st) {

@@ -114,8 +114,7 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
         }
         if (ns <= 1024) {
             // routing and all dispatch tables in one launch; the first grouped GEMV fetches each row's token itself
-            launch_moe_route_small(logits, mb, t, moe.n_experts, moe.top_k, moe.e0, moe.e1, 8, st);
-            launches += 1;
+            launches += launch_moe_route_small(logits, mb, t, moe.n_experts, moe.top_k, moe.e0, moe.e1, 8, st);
             if (int rc = gemv_grouped(&i13->second, x16, mb.act, 2 * moe.ffn, mb, max_tiles, est_tiles, nullptr, st,
                                       mb.slot_of_pos, moe.top_k)) {
                 return rc;
