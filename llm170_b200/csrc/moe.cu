@@ -31,8 +31,11 @@ constexpr int TOPK_WARPS = 8;
 // like their bit patterns, so the largest p is a max over u32 and the tie-break a min over the indices that hold it.
 // `stage`: optional shared-memory row of n floats owned by this warp; with it the sequential sum is read back by one
 // lane (independent loads, one dependent add each) instead of travelling through n dependent shuffles.
-__device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* __restrict__ idx, float* __restrict__ wt,
-                                              int n, int k, int lane, float* stage = nullptr) {
+// SLOTS = experts per lane the instantiation can hold (n <= 32 * SLOTS): a compile-time bound keeps the lane's values in
+// registers.
+template <int SLOTS>
+__device__ __forceinline__ void topk_of_token_n(const float* __restrict__ l, int* __restrict__ idx, float* __restrict__ wt,
+                                                int n, int k, int lane, float* stage) {
     float mx = -INFINITY;
     for (int i = lane; i < n; i += 32) {
         mx = fmaxf(mx, l[i]);
@@ -41,16 +44,20 @@ __device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* 
     for (int off = 16; off > 0; off >>= 1) {
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     }
-    float pv[32];
-    int cnt = 0;
-    for (int i = lane; i < n; i += 32) {
-        pv[cnt++] = (float)exp((double)(l[i] - mx));
+    float pv[SLOTS];
+    const int cnt = (n - lane + 31) >> 5;   // experts lane, lane + 32, ... below n
+#pragma unroll
+    for (int j = 0; j < SLOTS; ++j) {
+        pv[j] = j < cnt ? (float)exp((double)(l[lane + 32 * j] - mx)) : 0.f;
     }
     // sum in index order, the same on every lane: element e = 32*j + src comes from lane src, slot j
     float sum = 0.f;
     if (stage != nullptr) {
-        for (int j = 0; j < cnt; ++j) {
-            stage[lane + 32 * j] = pv[j];
+#pragma unroll
+        for (int j = 0; j < SLOTS; ++j) {
+            if (j < cnt) {
+                stage[lane + 32 * j] = pv[j];
+            }
         }
         __syncwarp();
         if (lane == 0) {
@@ -62,15 +69,19 @@ __device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* 
         __syncwarp();   // the row may be reused for the warp's next token
     } else {
         const int slots = (n + 31) >> 5;
-        for (int j = 0; j < slots; ++j) {
-            const float mine_j = j < cnt ? pv[j] : 0.f;
-            const int live = min(32, n - 32 * j);
-            for (int src = 0; src < live; ++src) {
-                sum += __shfl_sync(0xffffffffu, mine_j, src);
+#pragma unroll
+        for (int j = 0; j < SLOTS; ++j) {
+            if (j < slots) {
+                const float mine_j = pv[j];
+                const int live = min(32, n - 32 * j);
+                for (int src = 0; src < live; ++src) {
+                    sum += __shfl_sync(0xffffffffu, mine_j, src);
+                }
             }
         }
     }
-    for (int j = 0; j < cnt; ++j) {
+#pragma unroll
+    for (int j = 0; j < SLOTS; ++j) {
         pv[j] = pv[j] / sum;
     }
     unsigned used = 0u;
@@ -78,15 +89,17 @@ __device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* 
     float mine = 0.f;  // lane r keeps the r-th picked p
     for (int r = 0; r < k; ++r) {
         unsigned best = 0u;   // bit pattern of the lane's largest remaining p (p >= 0: patterns order like values)
-        for (int j = 0; j < cnt; ++j) {
-            if (!(used & (1u << j))) {
+#pragma unroll
+        for (int j = 0; j < SLOTS; ++j) {
+            if (j < cnt && !(used & (1u << j))) {
                 best = max(best, __float_as_uint(pv[j]));
             }
         }
         const unsigned top = __reduce_max_sync(0xffffffffu, best);
         unsigned cand = 0xffffffffu;   // lowest index on this lane that holds `top`
-        for (int j = cnt - 1; j >= 0; --j) {
-            if (!(used & (1u << j)) && __float_as_uint(pv[j]) == top) {
+#pragma unroll
+        for (int j = SLOTS - 1; j >= 0; --j) {
+            if (j < cnt && !(used & (1u << j)) && __float_as_uint(pv[j]) == top) {
                 cand = (unsigned)(lane + 32 * j);
             }
         }
@@ -105,6 +118,17 @@ __device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* 
     }
     if (lane < k) {
         wt[lane] = mine / wsum;
+    }
+}
+
+__device__ __forceinline__ void topk_of_token(const float* __restrict__ l, int* __restrict__ idx, float* __restrict__ wt,
+                                              int n, int k, int lane, float* stage = nullptr) {
+    if (n <= 128) {
+        topk_of_token_n<4>(l, idx, wt, n, k, lane, stage);
+    } else if (n <= 256) {
+        topk_of_token_n<8>(l, idx, wt, n, k, lane, stage);
+    } else {
+        topk_of_token_n<32>(l, idx, wt, n, k, lane, stage);
     }
 }
 
