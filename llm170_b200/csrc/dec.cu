@@ -216,8 +216,9 @@ int Dec::gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& 
     }
     c.sk = sk_make_plan(a.k, a.group, t, c.grid_x, sm_count, tune_gemv_sk_stages, tune_gemv_sk_prefetch);
     // measured on B200: the persistent form wins up to 4 tokens; at 5..8 its single-CTA sum of a row block costs
-    // more than the cluster reduce of the (row block, K split) form
-    if (tune_gemv_persistent && c.sk.ctas > 0 && (t <= 4 || tune_gemv_persistent > 1)) {
+    // more than the cluster reduce of the (row block, K split) form -- except for long K (down, K = 17408: 17.6-18.6
+    // against 20.9-21.4 us), where that form's K splits exceed a cluster
+    if (tune_gemv_persistent && c.sk.ctas > 0 && (t <= 4 || tune_gemv_persistent > 1 || a.k >= 8192)) {
         c.form = GemvChoice::PERSISTENT;
         c.part_floats = sk_part_floats(c.sk);
         c.tickets = (size_t)c.grid_x;
