@@ -50,9 +50,9 @@ def main():
             worst = max(worst, e_col, e_row / max(1.0, scale))
             assert e_col <= 2e-3 and e_row <= 2e-3 * max(1.0, scale) * 2
     # row-parallel with the all-reduce fused into the GEMV kernel (peer stores), eager and graph-replayed; the last shape
-    # leaves each of two ranks a K slice of six scale groups, fewer than the row-block form's eight warps
+    # leaves every rank a K slice of six scale groups, fewer than the row-block form's eight warps
     dec.tp_setup(rank, world, max_rows=2048)
-    shapes = [(1024, 2048, 128), (512, 4096, 128), (2048, 1024, 32), (768, 1536, 128)]
+    shapes = [(1024, 2048, 128), (512, 4096, 128), (2048, 1024, 32), (768, 768 * world, 128)]
     lins = []
     for i, (n2, k2, g2) in enumerate(shapes):
         q2, s2 = synth.make_linear(n2, k2, g2, seed=20 + i)
