@@ -41,7 +41,8 @@ constexpr int RB_XPAD = 64;       // bytes added to a token's row of x so that t
 constexpr int RB_GROUP = 128;
 
 // RBW = 16-row blocks per unit (2: a warp multiplies two neighbouring tiles with the same activation fragments, two
-// CTAs per SM;  1: for matrices with few rows, so that every row block gets its own CTA, three CTAs per SM).
+// CTAs per SM;  1: for matrices with fewer row blocks than SMs -- tensor-parallel shards --, so that more CTAs stream,
+// three CTAs per SM).
 // U = k-blocks in flight per warp (registers), of all RBW row blocks.
 // TP: the fused all-reduce of a row-parallel shard (its own instantiation: the exchange costs registers).
 template <int RBW, int RB_U, bool TP>
