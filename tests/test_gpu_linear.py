@@ -486,3 +486,23 @@ def test_row_block_form_with_fewer_groups_than_warps(dec, orc, n, k, t):
     y2 = dec.sk_single_dev("fewg", x_dev(xs), t=t)
     dec.sync()
     assert torch.equal(y, y2)
+
+
+# More units than resident CTAs (a CTA walks two units, its register ring runs on across the boundary), an odd number
+# of row blocks (the last unit holds one), and the 16-row-unit variant for matrices with fewer row blocks than SMs.
+@pytest.mark.parametrize("n,k,t", [(12304, 1024, 1), (12304, 1024, 4), (19200, 256, 2), (1200, 2048, 3), (16, 1024, 1)])
+def test_row_block_form_units_and_edges(dec, orc, n, k, t):
+    q, s = synth.make_linear(n, k, 128, seed=600 + n % 97)
+    dec.upload_lin_g("rbu", q, s, n, k, 128)
+    xs = synth.make_acts(t, k, seed=610 + t)
+    guard = torch.full((t + 1, n), 7.0, device="cuda", dtype=torch.float32)
+    y = dec.sk_single_dev("rbu", x_dev(xs), t=t, out=guard[:t])
+    dec.sync()
+    assert dec.last_kernel().startswith("gemv_rb_kernel")
+    expect = orc.linear_lane(q, s, xs, t, n, k, 128)
+    assert np.abs(y.cpu().numpy() - expect).max() <= TOL
+    assert bool((guard[t:] == 7.0).all())
+    y16 = dec.sk_single_dev("rbu", x_dev(xs), t=t, out_f16=True)
+    dec.sync()
+    assert torch.equal(y16, y.to(torch.float16))
+    dec.drop_lin("rbu")
