@@ -328,7 +328,7 @@ int Dec::gemv(const Lin* const* ls, int nseg, const void* x, void* const* outs, 
 // crates/backend-gpu/src/rawcuda/w4a16_dec/moe/moe_gemv.rs:92-114).
 int Dec::gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert, const MoeBufs& b, int max_tiles,
                       int est_tiles, const float* row_w, cudaStream_t st, const int* x_slot_of_pos,
-                      int x_slots_per_token) {
+                      int x_slots_per_token, bool tables_fresh) {
     if (l->glu_f > 0 && tune_gemv_warps != 8) {
         return fail("w4a16 grouped gemv: the fused gate|up form needs gemv_warps = 8");
     }
@@ -369,7 +369,8 @@ int Dec::gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert,
     a.cons_warps = tune_gemv_warps;
     a.cluster = ks >= 2 ? 1 : 0;
     a.status = gemm_status;
-    a.dbg = nullptr;
+    a.dbg = dbg_buf;
+    a.dbg_seq = (int)(launches % DBG_LAUNCHES);
     a.grouped = 1;
     a.ctas_per_seg = cps;
     a.expert0 = moe.e0;
@@ -380,6 +381,7 @@ int Dec::gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert,
     a.row_w = row_w;
     a.x_slot_of_pos = x_slot_of_pos;
     a.x_slots_per_token = x_slots_per_token;
+    a.tables_fresh = tables_fresh ? 1 : 0;
     a.nrb_w = l->n / TILE_ROWS;
     a.tp = TpComm{};
     a.part = part;

@@ -124,7 +124,7 @@ struct Dec {
     int tp_max_rows = 0;
     int gemv_grouped(const Lin* l, const void* xs, void* out, int n_per_expert, const MoeBufs& b, int max_tiles,
                      int est_tiles, const float* row_w, cudaStream_t st, const int* x_slot_of_pos = nullptr,
-                     int x_slots_per_token = 1);
+                     int x_slots_per_token = 1, bool tables_fresh = false);
     MoeCfg moe;
     MoeBufs mb;
     int ensure_moe(int t, cudaStream_t st);

@@ -65,7 +65,7 @@ struct SmemPlan {
     int off_sc;     // u32 [16 row blocks][groups][8]: this CTA's scale pairs (when sc_staged)
     int sc_staged;  // 1: the scales of the CTA's rows and K range are copied to shared memory up front
     int off_ring;   // stages x STAGE_BYTES, 1024-byte aligned
-    int off_bars;   // xbar, full[stages], empty[stages]
+    int off_bars;   // xbar, full[stages], empty[stages], scbar
     int stages;
     int total;
 };
@@ -83,7 +83,7 @@ __host__ SmemPlan make_plan(int k, int group, int m, int ksplit, int stages) {
     off += ngl * 16 * 4;
     p.off_sc = off;
     const int sc_bytes = ngl * CTA_RB * 32;
-    const int rest = 1024 + p.stages * STAGE_BYTES + (1 + 2 * p.stages) * 8;
+    const int rest = 1024 + p.stages * STAGE_BYTES + (2 + 2 * p.stages) * 8;
     p.sc_staged = sc_bytes <= SC_STAGE_MAX && off + sc_bytes + rest <= GEMV_SMEM_LIMIT;
     if (p.sc_staged) {
         off += sc_bytes;
@@ -92,7 +92,7 @@ __host__ SmemPlan make_plan(int k, int group, int m, int ksplit, int stages) {
     p.off_ring = off;
     off += p.stages * STAGE_BYTES;
     p.off_bars = off;
-    off += (1 + 2 * p.stages) * 8;
+    off += (2 + 2 * p.stages) * 8;
     p.total = off;
     return p;
 }
@@ -127,6 +127,9 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     int rb_w0 = rb_cta0;                                   // ... and within the resident weight matrix
     int row_base = 0;                                      // sorted row of token 0 (grouped mode)
     if (a.grouped) {
+        if (a.tables_fresh) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+        }
         const int ti = (int)blockIdx.x / a.ctas_per_seg;
         if (ti >= *a.num_tiles) {
             return;  // the grid is sized for the worst case; whole clusters leave together
@@ -155,6 +158,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     const uint32_t xbar = sbase + p.off_bars;
     auto full_bar = [&](int s) { return xbar + 8u + 8u * s; };
     auto empty_bar = [&](int s) { return xbar + 8u + 8u * (S + s); };
+    const uint32_t scbar = xbar + 8u + 16u * S;
     volatile int* abort_flag = &s_abort;
     // optional timeline: 8 wall-clock stamps per CTA and launch (diagnostic; a.dbg is null in normal runs)
     const int dbg_cta = (int)(blockIdx.y * gridDim.x + blockIdx.x);
@@ -178,6 +182,7 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         }
         s_abort = 0;
         mbar_init(xbar, 1);
+        mbar_init(scbar, 1);
         for (int s = 0; s < S; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), CONS_WARPS);
@@ -213,20 +218,25 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         }
     };
     const bool is_producer = warp == CONS_WARPS;
-    if (is_producer && lane == 0) {
-        for (int c = 0; c < S && c < nchunks; ++c) {
-            issue_chunk(c, c);
+    if (is_producer) {
+        if (p.sc_staged) {
+            // this CTA's scale pairs, [row block][group][8]: one bulk copy per row block (contiguous along K), requested
+            // first so that nothing queues in front of them; like the weights they do not depend on the previous kernel
+            const int ng_all = a.k / GROUP;
+            const size_t grp_first = (size_t)kb0 * GROUPS_PER_KB / KB_PER_GROUP;
+            if (lane == 0) {
+                mbar_expect_tx(scbar, (uint32_t)(nrbv * ngl * 32));
+            }
+            __syncwarp();
+            if (lane < nrbv) {
+                bulk_load(sbase + p.off_sc + (uint32_t)(lane * ngl * 32), sg.st + ((size_t)(rb_w0 + lane) * ng_all + grp_first) * 8,
+                          (uint32_t)(ngl * 32), scbar);
+            }
         }
-    }
-    if (!is_producer && p.sc_staged) {
-        // this CTA's scale pairs, [row block][group][8], fetched while the previous kernel drains
-        uint4* scs = reinterpret_cast<uint4*>(smem + p.off_sc);
-        const int per_rb = ngl * 2;                     // 16-byte pieces per row block
-        const int ng_all = a.k / GROUP;
-        const size_t grp_first = (size_t)kb0 * GROUPS_PER_KB / KB_PER_GROUP;
-        for (int i = threadIdx.x; i < nrbv * per_rb; i += CONS_WARPS * 32) {
-            const int rb = i / per_rb, rest = i - rb * per_rb;
-            scs[i] = __ldg(reinterpret_cast<const uint4*>(sg.st + ((size_t)(rb_w0 + rb) * ng_all + grp_first) * 8) + rest);
+        if (lane == 0) {
+            for (int c = 0; c < S && c < nchunks; ++c) {
+                issue_chunk(c, c);
+            }
         }
     }
     // Programmatic dependent launch: the weight copies above do not depend on the previous kernel in the
@@ -242,15 +252,19 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
         // this launch's exchange number: read only now, the previous launch advances it as it ends
         s_seq = tp_on ? *reinterpret_cast<volatile unsigned*>(a.tp.seq) + 1u : 0u;
         mbar_expect_tx(xbar, m_loc * halves * 2);
-        for (int tok = 0; tok < m_loc; ++tok) {
-            const uint16_t* xr = x_loc + (size_t)tok * a.k;
+    }
+    if (warp == 0) {
+        // one lane per token: the row lookups of a grouped call are independent loads, not a chain
+        __syncwarp();
+        if (lane < m_loc) {
+            const uint16_t* xr = x_loc + (size_t)lane * a.k;
             if (a.x_slot_of_pos != nullptr) {
                 // the activations were not gathered into sorted order: fetch the token's row
-                xr = a.x + (size_t)(a.x_slot_of_pos[row_base + tok] / a.x_slots_per_token) * a.k;
+                xr = a.x + (size_t)(a.x_slot_of_pos[row_base + lane] / a.x_slots_per_token) * a.k;
             }
-            bulk_load(sbase + tok * p.x_stride * 2, xr + (size_t)kb0 * TILE_K, halves * 2, xbar);
+            bulk_load(sbase + lane * p.x_stride * 2, xr + (size_t)kb0 * TILE_K, halves * 2, xbar);
         }
-        if (stamp) {
+        if (stamp && lane == 0) {
             stamp_now(1);   // the previous kernel of the stream is complete; x requested
         }
     }
@@ -276,8 +290,11 @@ gemv_w4a16_kernel(const GemvArgs a, const SmemPlan p) {
     bool ok = true;
     if (!is_producer) {
         ok = mbar_wait(xbar, 0, abort_flag, a.status, (10 << 16));
+        if (ok && p.sc_staged) {
+            ok = mbar_wait(scbar, 0, abort_flag, a.status, (14 << 16));
+        }
         if (stamp && threadIdx.x == 0) {
-            stamp_now(2);   // x in shared memory
+            stamp_now(2);   // x and scales in shared memory
         }
         if (SUBN && ok) {
             // xsum[grp][tok] = -8 * sum_{k in grp} x[tok][k] for tok < m (entries of tokens >= m stay zero):

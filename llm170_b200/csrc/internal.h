@@ -100,6 +100,8 @@ struct GemvArgs {
                           // f16(silu(f16 gate) * f16 up), n/2 values per token, instead of the n sums
     const int* x_slot_of_pos;   // optional gather: sorted row r reads x row x_slot_of_pos[r] / x_slots_per_token
     int x_slots_per_token;
+    int tables_fresh;     // 1: the launch just before this one wrote the segment table, so the table is read only after the
+                          // dependency wait (with 0 the weights of the segment are requested while that kernel still drains)
     int nrb_w;            // 16-row blocks of the whole resident matrix (tile pitch); 0 = seg n / 16
     TpComm tp;          // fused all-reduce over peers (row-parallel); tp.world <= 1: off
     int* status;        // device word that records the first bounded wait that expired

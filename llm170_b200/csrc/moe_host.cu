@@ -116,7 +116,7 @@ int Dec::moe_ffn(int layer, const float* logits, const void* x16, void* y, int t
             // routing and all dispatch tables in one launch; the first grouped GEMV fetches each row's token itself
             launches += launch_moe_route_small(logits, mb, t, moe.n_experts, moe.top_k, moe.e0, moe.e1, 8, st);
             if (int rc = gemv_grouped(&i13->second, x16, mb.act, 2 * moe.ffn, mb, max_tiles, est_tiles, nullptr, st,
-                                      mb.slot_of_pos, moe.top_k)) {
+                                      mb.slot_of_pos, moe.top_k, /*tables_fresh=*/true)) {
                 return rc;
             }
         } else {
