@@ -205,20 +205,26 @@ int Dec::gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& 
     //   7168 x 5120 (18 MB) 7.0 / 10.5     5120 x 6144 (16 MB) 8.0 / 9.4      8704 x 5120 (22 MB)  8.3 / 11.3
     //   5120 x 3072 (8 MB)  5.2 /  8.5     5120 x 4352 (11 MB) 6.9 / 8.8     17408 x 5120 (45 MB) 14.1 / 14.8
     //   34816 x 5120 (89 MB) 22.5-26.8 / 22.1     5120 x 8704 (22 MB) 12.5 / 10.3     5120 x 17408 (45 MB) 23.8 / 13.9
+    // Every CTA of the row-block form stages all of x, so its time grows with tokens x K (qkv 7.7 / 8.6 / 9.8 us at 1 / 2 /
+    // 4 tokens, o_proj 8.9 / 9.8 / 11.1) where the (row block, K split) cluster form stays flat (9.2 / 9.3 / 9.4 and
+    // 9.1 / 9.3 / 9.5): beyond 11264 token-channels the latter takes over, except where it would lose its cluster reduce.
     const size_t w_bytes = (size_t)a.seg[0].n * a.k / 2;
-    if (tune_gemv_rowblock && gemv_rb_fits(a) &&
-        (tune_gemv_rowblock > 1 || (w_bytes <= ((size_t)48 << 20) && a.k <= 6144))) {
+    const bool rb_shape = w_bytes <= ((size_t)48 << 20) && a.k <= 6144;
+    const bool rb_tokens = allreduce || own_scratch || !tune_gemv_cluster || (size_t)t * a.k <= 11264;
+    const bool rb_ok = tune_gemv_rowblock && gemv_rb_fits(a);
+    if (rb_ok && (tune_gemv_rowblock > 1 || (rb_shape && rb_tokens))) {
         c.form = GemvChoice::ROWBLOCK;
         c.grid_x = gemv_rb_plan(a, sm_count, c.rbw);
         a.ksplit = 1;
         snprintf(c.name, sizeof(c.name), "gemv_rb_kernel<%d>", c.rbw);
         return 0;
     }
+    const bool prefer_split = rb_ok && rb_shape && !rb_tokens && tune_gemv_persistent < 2;
     c.sk = sk_make_plan(a.k, a.group, t, c.grid_x, sm_count, tune_gemv_sk_stages, tune_gemv_sk_prefetch);
     // measured on B200: the persistent form wins up to 4 tokens; at 5..8 its single-CTA sum of a row block costs
     // more than the cluster reduce of the (row block, K split) form -- except for long K (down, K = 17408: 17.6-18.6
     // against 20.9-21.4 us), where that form's K splits exceed a cluster
-    if (tune_gemv_persistent && c.sk.ctas > 0 && (t <= 4 || tune_gemv_persistent > 1 || a.k >= 8192)) {
+    if (tune_gemv_persistent && c.sk.ctas > 0 && !prefer_split && (t <= 4 || tune_gemv_persistent > 1 || a.k >= 8192)) {
         c.form = GemvChoice::PERSISTENT;
         c.part_floats = sk_part_floats(c.sk);
         c.tickets = (size_t)c.grid_x;
