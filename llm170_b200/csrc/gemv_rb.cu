@@ -15,9 +15,14 @@
 //     scratch, no ticket, no wait on any other CTA;
 //   * the first six k-blocks of every warp are requested BEFORE griddepcontrol.wait: while the previous kernel of the
 //     stream drains, the next one already has 48 KB per CTA on the way.
-// Plain loads bound the streaming rate: with the arithmetic removed this kernel reads gate_up at 4.2 TB/s, no faster
-// than with it (the loads an SM may have outstanding, not instructions, are the limit), where the persistent form's
-// 8 KB bulk copies reach 6 TB/s inside its loop.  Two variants that fed each warp's own shared-memory ring with copies
+// What bounds it, measured on gate_up (89 MB) with parts of the kernel switched off: the arithmetic costs 5 us of 24 (at
+// 16 warps per SM -- 128 registers per thread -- every warp issues one instruction in ten cycles), the wait for the
+// previous kernel of the stream 3 us, staging x and the sums over the warps nothing; with all of it removed the kernel
+// reads the matrix in 16.4 us, which is what a bare read loop with the same addresses and residency achieves (18.5 us
+// at 16 warps per SM, 15.1 us at 32; a loop over 8 KB pieces in address order, the persistent form's pattern, 13.0 us).
+// Variants with fewer registers (two or four k-blocks in flight, three or four CTAs per SM) spilled and were slower,
+// 16-row units at four CTAs per SM were slower (more CTAs pay the prologue), prefetching the warp's next tiles into L2
+// before the dependency wait gained 0.2 us.  Two variants that fed each warp's own shared-memory ring with copies
 // instead were measured and dropped: one bulk copy per 1 KB tile pair (2.5 TB/s on gate_up: the copy engine's cost
 // per copy) and one tensor-map copy per chunk of four k-blocks x two row blocks (3.0 TB/s).  So this form is chosen
 // for launches of moderate size and K only (Dec::gemv_select), where the fixed cost of the persistent form weighs more
