@@ -207,10 +207,11 @@ int Dec::gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& 
     //   34816 x 5120 (89 MB) 22.5-26.8 / 22.1     5120 x 8704 (22 MB) 12.5 / 10.3     5120 x 17408 (45 MB) 23.8 / 13.9
     // Every CTA of the row-block form stages all of x, so its time grows with tokens x K (qkv 7.7 / 8.6 / 9.8 us at 1 / 2 /
     // 4 tokens, o_proj 8.9 / 9.8 / 11.1) where the (row block, K split) cluster form stays flat (9.2 / 9.3 / 9.4 and
-    // 9.1 / 9.3 / 9.5): beyond 11264 token-channels the latter takes over, except where it would lose its cluster reduce.
+    // 9.1 / 9.3 / 9.5): beyond 11264 token-channels the latter takes over (not for the fused all-reduce, which would lose
+    // the cluster reduce; the entry point with its own scratch follows the same rule so that it returns the same bits).
     const size_t w_bytes = (size_t)a.seg[0].n * a.k / 2;
     const bool rb_shape = w_bytes <= ((size_t)48 << 20) && a.k <= 6144;
-    const bool rb_tokens = allreduce || own_scratch || !tune_gemv_cluster || (size_t)t * a.k <= 11264;
+    const bool rb_tokens = allreduce || !tune_gemv_cluster || (size_t)t * a.k <= 11264;
     const bool rb_ok = tune_gemv_rowblock && gemv_rb_fits(a);
     if (rb_ok && (tune_gemv_rowblock > 1 || (rb_shape && rb_tokens))) {
         c.form = GemvChoice::ROWBLOCK;

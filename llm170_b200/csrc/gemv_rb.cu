@@ -9,12 +9,16 @@
 // in which no weight byte moves.  Here nothing is shared between CTAs:
 //   * a 16-row x 64-channel tile of the T64 layout is 512 contiguous bytes = one coalesced 16-byte load per lane, and
 //     the tile of the next row block follows it in memory; so the weights need no shared-memory ring, no producer warp
-//     and no barrier: each warp keeps six k-blocks of two row blocks (6 KB) in flight in registers and refills a slot
+//     and no barrier: each warp keeps four k-blocks of two row blocks (4 KB) in flight in registers and refills a slot
 //     as soon as it has been multiplied, across the boundary from one pair of row blocks to the CTA's next one;
 //   * the eight warps' partial sums meet in shared memory (double-buffered: one __syncthreads per 32 rows), no global
 //     scratch, no ticket, no wait on any other CTA;
-//   * the first six k-blocks of every warp are requested BEFORE griddepcontrol.wait: while the previous kernel of the
-//     stream drains, the next one already has 48 KB per CTA on the way.
+//   * the first four k-blocks of every warp are requested BEFORE griddepcontrol.wait: while the previous kernel of the
+//     stream drains, the next one already has 32 KB per CTA on the way;
+//   * what a warp multiplies after x has arrived is on the launch's critical path, and there the chain of MMAs on one
+//     accumulator is what a warp waits for: a group's MMAs therefore alternate between two accumulators per row block
+//     (added when the group closes), and the ring is four k-blocks deep, not six, to leave the registers for it
+//     (qkv 7.7 -> 7.0 us, the gate_up shard of four GPUs 8.3 -> 7.3; four accumulators per row block were slower).
 // What bounds it, measured on gate_up (89 MB) with parts of the kernel switched off: the arithmetic costs 5 us of 24 (at
 // 16 warps per SM -- 128 registers per thread -- every warp issues one instruction in ten cycles), the wait for the
 // previous kernel of the stream 3 us, staging x and the sums over the warps nothing; with all of it removed the kernel
@@ -295,13 +299,16 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
                 const int grp = g0 + kin / 2;
                 // zero-point term of this group: (tokens 2t, 2t+1) x (rows g: 2^-24 per nibble unit, rows g+8: 2^-20)
                 const float2 z = *reinterpret_cast<const float2*>(zl + grp * zk);
-                float cg[RBW][4];
+                // two accumulator chains per row block (words x, z and words y, w): consecutive MMAs of a chain are four
+                // MMAs apart instead of two
+                float cg[RBW][4], ch[RBW][4];
 #pragma unroll
                 for (int r = 0; r < RBW; ++r) {
                     cg[r][0] = z.x;
                     cg[r][1] = z.y;
                     cg[r][2] = 16.f * z.x;
                     cg[r][3] = 16.f * z.y;
+                    ch[r][0] = ch[r][1] = ch[r][2] = ch[r][3] = 0.f;
                 }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -325,7 +332,7 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
 #pragma unroll
                     for (int r = 0; r < RBW; ++r) {
                         nibbles_as_subnormals(wv[r].y, af);
-                        mma16816(cg[r], af, x0.z, x0.w);
+                        mma16816(ch[r], af, x0.z, x0.w);
                     }
 #pragma unroll
                     for (int r = 0; r < RBW; ++r) {
@@ -335,7 +342,14 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
 #pragma unroll
                     for (int r = 0; r < RBW; ++r) {
                         nibbles_as_subnormals(wv[r].w, af);
-                        mma16816(cg[r], af, x1.z, x1.w);
+                        mma16816(ch[r], af, x1.z, x1.w);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < RBW; ++r) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        cg[r][i] += ch[r][i];
                     }
                 }
                 uint32_t s2[RBW];
@@ -366,15 +380,15 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
 }  // namespace
 
 cudaError_t gemv_rb_init_device() {
-    cudaError_t e = cudaFuncSetAttribute(gemv_rb_kernel<2, 6, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemv_rb_kernel<2, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
     if (e == cudaSuccess) {
-        e = cudaFuncSetAttribute(gemv_rb_kernel<2, 6, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        e = cudaFuncSetAttribute(gemv_rb_kernel<2, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
     }
     if (e == cudaSuccess) {
-        e = cudaFuncSetAttribute(gemv_rb_kernel<1, 8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        e = cudaFuncSetAttribute(gemv_rb_kernel<1, 6, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
     }
     if (e == cudaSuccess) {
-        e = cudaFuncSetAttribute(gemv_rb_kernel<1, 8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        e = cudaFuncSetAttribute(gemv_rb_kernel<1, 6, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
     }
     return e;
 }
@@ -421,11 +435,11 @@ cudaError_t launch_gemv_rb(const GemvArgs& a, int total_units, int rbw, int sm_c
     cfg.attrs = attr;
     cfg.numAttrs = na;
     if (a.tp.world > 1) {
-        return rbw == 2 ? cudaLaunchKernelEx(&cfg, gemv_rb_kernel<2, 6, true>, a, total_units)
-                        : cudaLaunchKernelEx(&cfg, gemv_rb_kernel<1, 8, true>, a, total_units);
+        return rbw == 2 ? cudaLaunchKernelEx(&cfg, gemv_rb_kernel<2, 4, true>, a, total_units)
+                        : cudaLaunchKernelEx(&cfg, gemv_rb_kernel<1, 6, true>, a, total_units);
     }
-    return rbw == 2 ? cudaLaunchKernelEx(&cfg, gemv_rb_kernel<2, 6, false>, a, total_units)
-                    : cudaLaunchKernelEx(&cfg, gemv_rb_kernel<1, 8, false>, a, total_units);
+    return rbw == 2 ? cudaLaunchKernelEx(&cfg, gemv_rb_kernel<2, 4, false>, a, total_units)
+                    : cudaLaunchKernelEx(&cfg, gemv_rb_kernel<1, 6, false>, a, total_units);
 }
 
 }  // namespace w4
