@@ -66,6 +66,16 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
     if (a.pdl) {
         asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     }
+    // optional timeline (diagnostic; a.dbg is null in normal runs): wall-clock stamps of thread 0, recomputed from the
+    // arguments at every site so that nothing stays in registers
+    auto stamp_now = [&](int j) {
+        if (a.dbg != nullptr && threadIdx.x == 0 && (int)blockIdx.x < DBG_CTAS) {
+            unsigned long long ns;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+            a.dbg[((size_t)a.dbg_seq * DBG_CTAS + blockIdx.x) * DBG_STAMPS + j] = (long long)ns;
+        }
+    };
+    stamp_now(0);   // CTA entry
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int ngroups = a.k / RB_GROUP;
@@ -161,9 +171,11 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
     }
 
     // ---- x may be the previous kernel's output: only now wait for it; stage it and its group sums --------------
+    stamp_now(6);   // first tiles requested
     if (a.pdl) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }
+    stamp_now(1);   // the previous kernel of the stream is complete
     if (threadIdx.x < 4) {
         zero16[threadIdx.x] = 0;
     }
@@ -222,6 +234,8 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
         }
     }
     __syncthreads();
+    stamp_now(2);   // x and its group sums staged
+    stamp_now(3);
 
     // lanes whose MMA column holds no token read 16 zero bytes, with stride 0: no branch in the loop
     const bool tok_lane = g < a.m;
@@ -375,6 +389,8 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
             }
         }
     }
+    stamp_now(4);
+    stamp_now(5);   // warp 0 is through its last unit (sums stored)
 }
 
 }  // namespace
