@@ -200,11 +200,11 @@ int Dec::gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& 
     }
     // Up to four tokens of a g128 linear with K <= 6144 and at most 48 MB of weights: CTAs that own whole rows, no
     // scratch, no ticket (gemv_rb.cu).  At its 16 warps per SM it streams at 4 to 4.7 TB/s, the persistent form's bulk
-    // copies at 6 inside its loop, and a warp of the row-block form walks its K range with six k-blocks in flight.
+    // copies at 6 inside its loop, and a warp of the row-block form walks its K range with four k-blocks in flight.
     // Measured on B200 (us per launch, M = 1, row-block against persistent):
-    //   7168 x 5120 (18 MB) 7.0 / 10.5     5120 x 6144 (16 MB) 8.0 / 9.4      8704 x 5120 (22 MB)  8.3 / 11.3
-    //   5120 x 3072 (8 MB)  5.2 /  8.5     5120 x 4352 (11 MB) 6.9 / 8.8     17408 x 5120 (45 MB) 14.1 / 14.8
-    //   34816 x 5120 (89 MB) 22.5-26.8 / 22.1     5120 x 8704 (22 MB) 12.5 / 10.3     5120 x 17408 (45 MB) 23.8 / 13.9
+    //   7168 x 5120 (18 MB) 7.0 / 10.6     5120 x 6144 (16 MB) 8.0 / 9.6      17408 x 5120 (45 MB) 12.6 / 14.9
+    //   5120 x 4352 (11 MB) 6.9 /  9.0     5120 x 3072 (8 MB)  5.2 / 8.5       8704 x 5120 (22 MB)  7.3 / 11.3
+    //   34816 x 5120 (89 MB) 22.9 / 22.2   5120 x 8704 (22 MB) 11.1 / 10.6     5120 x 17408 (45 MB) 19.7 / 14.1
     // Every CTA of the row-block form stages all of x, so its time grows with tokens x K (qkv 7.7 / 8.6 / 9.8 us at 1 / 2 /
     // 4 tokens, o_proj 8.9 / 9.8 / 11.1) where the (row block, K split) cluster form stays flat (9.2 / 9.3 / 9.4 and
     // 9.1 / 9.3 / 9.5): beyond 11264 token-channels the latter takes over (not for the fused all-reduce, which would lose
