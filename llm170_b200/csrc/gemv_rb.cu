@@ -75,7 +75,8 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
             a.dbg[((size_t)a.dbg_seq * DBG_CTAS + blockIdx.x) * DBG_STAMPS + j] = (long long)ns;
         }
     };
-    stamp_now(0);   // CTA entry
+    stamp_now(0);   // CTA entry; slots 0..5 as in the other forms (entry, dependency wait over, x staged, loop start, loop
+                    // end, stored), 6 = SM id, 7 = units of this CTA, 8 = first tiles requested
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int ngroups = a.k / RB_GROUP;
@@ -157,6 +158,13 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
     if (my_units == 0) {
         return;                 // more CTAs than units never happens (the grid is at most the unit count)
     }
+    if (a.dbg != nullptr && threadIdx.x == 0 && (int)blockIdx.x < DBG_CTAS) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+        long long* d = a.dbg + ((size_t)a.dbg_seq * DBG_CTAS + blockIdx.x) * DBG_STAMPS;
+        d[6] = smid;
+        d[7] = my_units;
+    }
     cursor_init(fw);
     cursor_init(fs);
     if (nk > 0) {               // a warp without a group (fewer groups than warps) only takes part in the sums
@@ -171,7 +179,7 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
     }
 
     // ---- x may be the previous kernel's output: only now wait for it; stage it and its group sums --------------
-    stamp_now(6);   // first tiles requested
+    stamp_now(8);   // first tiles requested
     if (a.pdl) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
     }

@@ -296,15 +296,18 @@ def test_host_buffer_forward_and_gptq4_gate(dec, orc):
     assert np.array_equal(y, got8)
 
 
-def test_debug_timeline_stamps_are_ordered(dec):
+@pytest.mark.parametrize("rowblock", [0, 1])
+def test_debug_timeline_stamps_are_ordered(dec, rowblock):
     # w4a16_debug_timeline: every CTA of a decode launch stamps entry <= dependency wait <= x staged <= main loop
-    # start <= main loop end <= exit (nanoseconds of the global timer), then its SM id and unit count
+    # start <= main loop end <= exit (nanoseconds of the global timer), then its SM id and unit count; kept by the
+    # persistent form (gemv_rowblock = 0) and by the row-block form alike
     n, k = 2048, 1024
     q, s = synth.make_linear(n, k, 128, seed=3)
     dec.upload_lin_g("tl", q, s, n, k, 128)
     x = x_dev(synth.make_acts(1, k, seed=4))
-    dec.set_tuning("gemv_rowblock", 0)            # the timeline is kept by the persistent form
+    dec.set_tuning("gemv_rowblock", rowblock)
     ref = dec.sk_single_dev("tl", x).clone()
+    assert dec.last_kernel().startswith("gemv_rb_kernel" if rowblock else "gemv_sk_kernel")
     dec.set_tuning("debug_timeline", 1)
     try:
         c0 = dec.launch_count()
