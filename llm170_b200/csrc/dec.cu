@@ -189,6 +189,7 @@ int Dec::gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& 
     a.grouped = 0;
     a.row_w = nullptr;
     a.nrb_w = 0;
+    a.rb_no_units = tune_gemv_rowblock_units ? 0 : 1;
     if (allreduce) {
         if (tp.world < 2 || tp_peer[(tp.rank + 1) % tp.world] == nullptr) {
             return fail("w4a16 allreduce gemv: call w4a16_tp_create and w4a16_tp_connect first");
@@ -211,13 +212,13 @@ int Dec::gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& 
     // the cluster reduce; the entry point with its own scratch follows the same rule so that it returns the same bits).
     const size_t w_bytes = (size_t)a.seg[0].n * a.k / 2;
     const bool rb_shape = w_bytes <= ((size_t)48 << 20) && a.k <= 6144;
-    const bool rb_tokens = allreduce || !tune_gemv_cluster || (size_t)t * a.k <= 11264;
+    const bool rb_tokens = allreduce || !tune_gemv_cluster || (size_t)t * a.k <= 11264 || gemv_ru_fits(a, sm_count);
     const bool rb_ok = tune_gemv_rowblock && gemv_rb_fits(a);
     if (rb_ok && (tune_gemv_rowblock > 1 || (rb_shape && rb_tokens))) {
         c.form = GemvChoice::ROWBLOCK;
         c.grid_x = gemv_rb_plan(a, sm_count, c.rbw);
         a.ksplit = 1;
-        snprintf(c.name, sizeof(c.name), "gemv_rb_kernel<%d>", c.rbw);
+        snprintf(c.name, sizeof(c.name), "%s", gemv_rb_variant(a, c.grid_x, c.rbw, sm_count));
         return 0;
     }
     const bool prefer_split = rb_ok && rb_shape && !rb_tokens && tune_gemv_persistent < 2;
@@ -611,6 +612,10 @@ const char* w4a16_last_kernel(w4a16_dec* dec) { return dec->d.last_kernel.c_str(
 
 int w4a16_set_tuning(w4a16_dec* dec, const char* key, int value) {
     Dec& d = dec->d;
+    if (!strcmp(key, "gemv_rowblock_units")) {
+        d.tune_gemv_rowblock_units = value ? 1 : 0;
+        return 0;
+    }
     if (!strcmp(key, "gemv_stages")) {
         if (value < 2 || value > 8) {
             return d.fail("w4a16 tuning: gemv_stages must be 2..8");

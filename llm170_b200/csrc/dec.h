@@ -82,6 +82,7 @@ struct Dec {
     int head_n = 0, head_k = 0;
     // knobs
     int tune_gemv_stages = 4;
+    int tune_gemv_rowblock_units = 1;  // 1: launches whose 32-row units are all resident at once run the 16-warp variant
     int tune_gemv_warps = 8;
     int tune_gemv_sk_stages = 4;   // most 16 KB ring stages of the persistent GEMV (2..6; fewer when x needs the room)
     int tune_gemv_sk_prefetch = 2; // ring stages the persistent GEMV requests before the previous kernel is complete

@@ -401,6 +401,255 @@ __global__ void __launch_bounds__(RB_THREADS, RBW == 2 ? 2 : 3) gemv_rb_kernel(c
     stamp_now(5);   // warp 0 is through its last unit (sums stored)
 }
 
+// ---- "unit" variant: one unit of 32 rows per CTA, 16 warps ----------------------------------------------------------
+// For launches whose units all fit on the chip at once (at most two CTAs per SM): qkv, o_proj, every tensor-parallel
+// shard.  Such a launch lasts as long as its fullest SM, and an SM with one or two 8-warp CTAs of 128 registers is
+// latency-bound in what it multiplies after x has arrived.  Here K is split over 16 warps, and the weights do not wait
+// in registers: a warp's first group is loaded into registers and all its other groups (and its scales) go to shared
+// memory by asynchronous copies, all requested before the dependency wait.  What is left after the wait is x, the
+// arithmetic out of shared memory with 32 warps per SM at 64 registers, and the sum over the warps.
+constexpr int RU_WARPS = 16;
+constexpr int RU_THREADS = RU_WARPS * 32;
+
+template <bool TP>
+__global__ void __launch_bounds__(RU_THREADS, 2) gemv_ru_kernel(const GemvArgs a, const int total_units) {
+    extern __shared__ __align__(16) unsigned char smem[];   // x rows, group sums | weight slab | scale words
+    __shared__ float red[RU_WARPS][2][TILE_ROWS][RB_MAXTOK];
+    __shared__ __align__(16) uint32_t zero16[4];
+    __shared__ unsigned s_seq;
+    __shared__ int s_abort;
+    if (a.pdl) {
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    }
+    auto stamp_now = [&](int j) {
+        if (a.dbg != nullptr && threadIdx.x == 0 && (int)blockIdx.x < DBG_CTAS) {
+            unsigned long long ns;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(ns));
+            a.dbg[((size_t)a.dbg_seq * DBG_CTAS + blockIdx.x) * DBG_STAMPS + j] = (long long)ns;
+        }
+    };
+    stamp_now(0);   // same slots as the other forms: 6 = SM id, 7 = units of this CTA (one), 8 = first tiles requested
+    if (a.dbg != nullptr && threadIdx.x == 0 && (int)blockIdx.x < DBG_CTAS) {
+        unsigned smid;
+        asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+        long long* d = a.dbg + ((size_t)a.dbg_seq * DBG_CTAS + blockIdx.x) * DBG_STAMPS;
+        d[6] = smid;
+        d[7] = 1;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int ngroups = a.k / RB_GROUP;
+    const int g0 = ngroups * warp / RU_WARPS, g1 = ngroups * (warp + 1) / RU_WARPS;
+    const int ng = g1 - g0;
+    const GemvSeg& sg = a.seg[0];
+    const int nrb = sg.n / TILE_ROWS;
+    const size_t pitch = (size_t)nrb * 32;
+    const int rb = (int)blockIdx.x * 2;
+    const bool second = rb + 1 < nrb;
+    const int off2 = second ? 32 : 0, soff2 = second ? ngroups * 8 : 0;
+    // groups kept in shared memory by the warps before this one: every warp with a group keeps one in registers
+    const int stored_before = ngroups >= RU_WARPS ? g0 - warp : 0;   // below 16 groups no warp has a second one
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t slab = sbase + (uint32_t)a.rb_stash + (uint32_t)stored_before * 2048u + (uint32_t)lane * 16u;
+    const uint32_t scb = sbase + (uint32_t)a.rb_stash2;
+    uint4 wq[2][2];
+    if (ng > 0) {
+        const uint4* p = sg.qt + ((size_t)(2 * g0) * nrb + rb) * 32 + lane;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            wq[h][0] = __ldg(p + h * pitch);
+            wq[h][1] = __ldg(p + h * pitch + off2);
+        }
+        p += 2 * pitch;
+        for (int j = 1; j < ng; ++j) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t dst = slab + (uint32_t)((j - 1) * 2 + h) * 1024u;
+                cp_async_16(dst, p + h * pitch);
+                cp_async_16(dst + 512u, p + h * pitch + off2);
+            }
+            p += 2 * pitch;
+        }
+        // scale words of rows g / g+8: [group][row block][8], 16 lanes per group
+        if (lane < 16) {
+            const int r = lane >> 3, gi = lane & 7;
+            const uint32_t* sp = sg.st + ((size_t)rb * ngroups + g0) * 8 + (r ? soff2 : 0) + gi;
+            for (int j = 0; j < ng; ++j) {
+                cp_async_4(scb + (uint32_t)(((g0 + j) * 2 + r) * 8 + gi) * 4u, sp + (size_t)j * 8);
+            }
+        }
+    }
+    stamp_now(8);
+    if (a.pdl) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+    stamp_now(1);
+    if (threadIdx.x < 4) {
+        zero16[threadIdx.x] = 0;
+    }
+    if (threadIdx.x == 0) {
+        s_seq = TP ? *reinterpret_cast<volatile unsigned*>(a.tp.seq) + 1u : 0u;
+        s_abort = 0;
+    }
+    const int xstride = a.k * 2 + RB_XPAD;
+    float* zs = reinterpret_cast<float*>(smem + (size_t)a.m * xstride);
+    {
+        const int per_tok = a.k / 8;
+        const int total = a.m * per_tok;
+        const uint4* xg = reinterpret_cast<const uint4*>(a.x);
+        constexpr int XB = 2;
+        for (int i0 = 0; i0 < total; i0 += XB * RU_THREADS) {
+            uint4 xr[XB];
+#pragma unroll
+            for (int b = 0; b < XB; ++b) {
+                const int i = i0 + b * RU_THREADS + (int)threadIdx.x;
+                xr[b] = i < total ? __ldg(xg + i) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int b = 0; b < XB; ++b) {
+                const int i = i0 + b * RU_THREADS + (int)threadIdx.x;
+                const bool live = i < total;
+                const uint4 u = xr[b];
+                int tok = 0, c = 0;
+                if (live) {
+                    tok = i / per_tok;
+                    c = i - tok * per_tok;
+                    *reinterpret_cast<uint4*>(smem + (size_t)tok * xstride + (size_t)c * 16) = u;
+                }
+                const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+                const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+                const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&u.z));
+                const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&u.w));
+                float v = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+#pragma unroll
+                for (int off = 8; off > 0; off >>= 1) {
+                    v += __shfl_xor_sync(0xffffffffu, v, off);
+                }
+                if (live && (lane & 15) == 0) {
+                    zs[(c >> 4) * RB_MAXTOK + tok] = -8.f * v * 5.9604644775390625e-08f;
+                }
+            }
+        }
+        for (int i = threadIdx.x; i < ngroups * RB_MAXTOK; i += RU_THREADS) {
+            if ((i & (RB_MAXTOK - 1)) >= a.m) {
+                zs[i] = 0.f;
+            }
+        }
+    }
+    cp_async_wait_all();        // weights: each lane reads back what it copied; scales: other lanes' copies -> the barrier
+    __syncthreads();
+    stamp_now(2);
+    stamp_now(3);
+
+    const bool tok_lane = g < a.m;
+    const unsigned char* xl = tok_lane ? smem + (size_t)g * xstride + t * 16 : reinterpret_cast<const unsigned char*>(zero16);
+    const int xk = tok_lane ? 128 : 0, xh = tok_lane ? 64 : 0;
+    const float* zl = t < RB_MAXTOK / 2 ? zs + 2 * t : reinterpret_cast<const float*>(zero16);
+    const int zk = t < RB_MAXTOK / 2 ? RB_MAXTOK : 0;
+    float tot[2][4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        tot[r][0] = tot[r][1] = tot[r][2] = tot[r][3] = 0.f;
+    }
+    // one scale group (two k-blocks) of both row blocks: w[h][r] = the lane's 16 bytes of tile (k-block h, row block r)
+    auto do_group = [&](int grp, const uint4 (&w)[2][2]) {
+        const float2 z = *reinterpret_cast<const float2*>(zl + grp * zk);
+        float cg[2][4];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            cg[r][0] = z.x;
+            cg[r][1] = z.y;
+            cg[r][2] = 16.f * z.x;
+            cg[r][3] = 16.f * z.y;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int kb = 2 * grp + h;
+            const uint4 x0 = *reinterpret_cast<const uint4*>(xl + kb * xk);
+            const uint4 x1 = *reinterpret_cast<const uint4*>(xl + kb * xk + xh);
+            uint32_t af[4];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                nibbles_as_subnormals(w[h][r].x, af);
+                mma16816(cg[r], af, x0.x, x0.y);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                nibbles_as_subnormals(w[h][r].y, af);
+                mma16816(cg[r], af, x0.z, x0.w);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                nibbles_as_subnormals(w[h][r].z, af);
+                mma16816(cg[r], af, x1.x, x1.y);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                nibbles_as_subnormals(w[h][r].w, af);
+                mma16816(cg[r], af, x1.z, x1.w);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const uint32_t s2 = lds32(scb + (uint32_t)((grp * 2 + r) * 8 + g) * 4u);
+            const float2 sf = __half22float2(*reinterpret_cast<const __half2*>(&s2));
+            tot[r][0] = fmaf(cg[r][0], sf.x, tot[r][0]);
+            tot[r][1] = fmaf(cg[r][1], sf.x, tot[r][1]);
+            tot[r][2] = fmaf(cg[r][2], sf.y, tot[r][2]);
+            tot[r][3] = fmaf(cg[r][3], sf.y, tot[r][3]);
+        }
+    };
+    if (ng > 0) {
+        do_group(g0, wq);
+        for (int j = 1; j < ng; ++j) {
+            uint4 w[2][2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    w[h][r] = lds128(slab + (uint32_t)((j - 1) * 2 + h) * 1024u + (uint32_t)r * 512u);
+                }
+            }
+            do_group(g0 + j, w);
+        }
+    }
+    stamp_now(4);
+    if (t < RB_MAXTOK / 2) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            red[warp][r][g][2 * t] = tot[r][0] * 16777216.f;
+            red[warp][r][g][2 * t + 1] = tot[r][1] * 16777216.f;
+            red[warp][r][g + 8][2 * t] = tot[r][2] * 1048576.f;
+            red[warp][r][g + 8][2 * t + 1] = tot[r][3] * 1048576.f;
+        }
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < 2 * TILE_ROWS * a.m) {
+        const int tok = (int)threadIdx.x / (2 * TILE_ROWS), r32 = (int)threadIdx.x % (2 * TILE_ROWS);
+        const int r = r32 / TILE_ROWS, row = r32 % TILE_ROWS;
+        if (rb + r < nrb) {
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < RU_WARPS; ++w) {
+                v += red[w][r][row][tok];                                  // fixed order: the same bits every run
+            }
+            v *= sg.out_mul;
+            const size_t o = (size_t)tok * sg.n + (size_t)(rb + r) * TILE_ROWS + row;
+            if (TP) {
+                tp_own_area(a.tp, s_seq)[(size_t)tok * a.tp.max_rows + (size_t)(rb + r) * TILE_ROWS + row] = v;
+            } else if (a.out_f16) {
+                reinterpret_cast<__half*>(sg.out)[o] = __float2half_rn(v);
+            } else {
+                reinterpret_cast<float*>(sg.out)[o] = v;
+            }
+        }
+    }
+    if (TP) {
+        tp_exchange(a, sg, rb, min(2, nrb - rb) * TILE_ROWS, &s_seq, &s_abort, (unsigned)total_units);
+    }
+    stamp_now(5);
+}
+
 }  // namespace
 
 cudaError_t gemv_rb_init_device() {
@@ -413,6 +662,12 @@ cudaError_t gemv_rb_init_device() {
     }
     if (e == cudaSuccess) {
         e = cudaFuncSetAttribute(gemv_rb_kernel<1, 6, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+    }
+    if (e == cudaSuccess) {
+        e = cudaFuncSetAttribute(gemv_ru_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    }
+    if (e == cudaSuccess) {
+        e = cudaFuncSetAttribute(gemv_ru_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
     }
     return e;
 }
@@ -427,14 +682,32 @@ bool gemv_rb_fits(const GemvArgs& a) {
            gemv_rb_smem(a) <= (size_t)100 * 1024;
 }
 
-// Units over all segments (seg[].cta0 = first unit of the segment) and the row blocks per unit: one while there are
-// fewer row blocks than SMs (tensor-parallel shards: more CTAs, more loads in flight), else two (measured on o_proj).
+// Shared memory of the 16-warp variant: x and its group sums, the groups beyond each warp's first, the scale words.
+static size_t gemv_ru_smem(const GemvArgs& a, int* off_slab, int* off_sc) {
+    const int ngroups = a.k / RB_GROUP;
+    size_t off = ((size_t)a.m * ((size_t)a.k * 2 + RB_XPAD) + (size_t)ngroups * RB_MAXTOK * sizeof(float) + 15) & ~(size_t)15;
+    *off_slab = (int)off;
+    off += (size_t)(ngroups > RU_WARPS ? ngroups - RU_WARPS : 0) * 2048;
+    *off_sc = (int)off;
+    off += (size_t)ngroups * 2 * 8 * 4;
+    return off;
+}
+
+// The 16-warp variant takes a call whose 32-row units are all resident at once, two CTAs per SM.
+bool gemv_ru_fits(const GemvArgs& a, int sm_count) {
+    int o1, o2;
+    return !a.rb_no_units && gemv_rb_fits(a) && (a.seg[0].n / TILE_ROWS + 1) / 2 <= 2 * sm_count &&
+           gemv_ru_smem(a, &o1, &o2) <= (size_t)100 * 1024;
+}
+
+// Units over all segments (seg[].cta0 = first unit of the segment) and the row blocks per unit: two for the 16-warp
+// variant and for matrices with more row blocks than SMs, else one (more CTAs, more loads in flight).
 int gemv_rb_plan(GemvArgs& a, int sm_count, int& rbw) {
     int nrb = 0;
     for (int i = 0; i < a.nseg; ++i) {
         nrb += a.seg[i].n / TILE_ROWS;
     }
-    rbw = (nrb <= sm_count && gemv_rb_smem(a) <= (size_t)72 * 1024) ? 1 : 2;
+    rbw = (!gemv_ru_fits(a, sm_count) && nrb <= sm_count && gemv_rb_smem(a) <= (size_t)72 * 1024) ? 1 : 2;
     int total = 0;
     for (int i = 0; i < a.nseg; ++i) {
         a.seg[i].cta0 = total;
@@ -443,11 +716,18 @@ int gemv_rb_plan(GemvArgs& a, int sm_count, int& rbw) {
     return total;
 }
 
-cudaError_t launch_gemv_rb(const GemvArgs& a, int total_units, int rbw, int sm_count, cudaStream_t st) {
+// Which kernel a row-block launch runs (also what the library reports as the last kernel's name).
+const char* gemv_rb_variant(const GemvArgs& a, int total_units, int rbw, int sm_count) {
+    (void)total_units;
+    if (rbw == 2 && gemv_ru_fits(a, sm_count)) {
+        return "gemv_ru_kernel";
+    }
+    return rbw == 2 ? "gemv_rb_kernel<2>" : "gemv_rb_kernel<1>";
+}
+
+cudaError_t launch_gemv_rb(const GemvArgs& a_in, int total_units, int rbw, int sm_count, cudaStream_t st) {
+    GemvArgs a = a_in;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(std::min(total_units, (rbw == 2 ? 2 : 3) * sm_count));
-    cfg.blockDim = dim3(RB_THREADS);
-    cfg.dynamicSmemBytes = gemv_rb_smem(a);
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     int na = 0;
@@ -458,6 +738,16 @@ cudaError_t launch_gemv_rb(const GemvArgs& a, int total_units, int rbw, int sm_c
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
+    if (gemv_rb_variant(a, total_units, rbw, sm_count)[6] == 'u') {
+        cfg.gridDim = dim3(total_units);
+        cfg.blockDim = dim3(RU_THREADS);
+        cfg.dynamicSmemBytes = gemv_ru_smem(a, &a.rb_stash, &a.rb_stash2);
+        return a.tp.world > 1 ? cudaLaunchKernelEx(&cfg, gemv_ru_kernel<true>, a, total_units)
+                              : cudaLaunchKernelEx(&cfg, gemv_ru_kernel<false>, a, total_units);
+    }
+    cfg.gridDim = dim3(std::min(total_units, (rbw == 2 ? 2 : 3) * sm_count));
+    cfg.blockDim = dim3(RB_THREADS);
+    cfg.dynamicSmemBytes = gemv_rb_smem(a);
     if (a.tp.world > 1) {
         return rbw == 2 ? cudaLaunchKernelEx(&cfg, gemv_rb_kernel<2, 4, true>, a, total_units)
                         : cudaLaunchKernelEx(&cfg, gemv_rb_kernel<1, 6, true>, a, total_units);

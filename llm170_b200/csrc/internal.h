@@ -102,6 +102,9 @@ struct GemvArgs {
     int x_slots_per_token;
     int tables_fresh;     // 1: the launch just before this one wrote the segment table, so the table is read only after the
                           // dependency wait (with 0 the weights of the segment are requested while that kernel still drains)
+    int rb_no_units;           // row-block form: 1 = never the 16-warp variant (tuning)
+    int rb_stash, rb_stash2;   // row-block form, 16-warp variant: byte offsets of the weight slab and of the scale words in
+                               // dynamic shared memory (set by the launcher)
     int nrb_w;            // 16-row blocks of the whole resident matrix (tile pitch); 0 = seg n / 16
     TpComm tp;          // fused all-reduce over peers (row-parallel); tp.world <= 1: off
     int* status;        // device word that records the first bounded wait that expired
@@ -142,6 +145,10 @@ cudaError_t gemv_rb_init_device();
 bool gemv_rb_fits(const GemvArgs& a);
 int gemv_rb_plan(GemvArgs& a, int sm_count, int& rbw);
 cudaError_t launch_gemv_rb(const GemvArgs& a, int total_units, int rbw, int sm_count, cudaStream_t st);
+// The 16-warp variant of the row-block form takes this call (all units resident at once, shared memory fits).
+bool gemv_ru_fits(const GemvArgs& a, int sm_count);
+// Name of the kernel that launch_gemv_rb runs for this call.
+const char* gemv_rb_variant(const GemvArgs& a, int total_units, int rbw, int sm_count);
 
 // ---- gemm_tc.cu ------------------------------------------------------------------------------
 // Raises the dynamic shared-memory limit of the tensor-core GEMM kernels on the current device.

@@ -307,7 +307,7 @@ def test_debug_timeline_stamps_are_ordered(dec, rowblock):
     x = x_dev(synth.make_acts(1, k, seed=4))
     dec.set_tuning("gemv_rowblock", rowblock)
     ref = dec.sk_single_dev("tl", x).clone()
-    assert dec.last_kernel().startswith("gemv_rb_kernel" if rowblock else "gemv_sk_kernel")
+    assert dec.last_kernel().startswith("gemv_ru_kernel" if rowblock else "gemv_sk_kernel")
     dec.set_tuning("debug_timeline", 1)
     try:
         c0 = dec.launch_count()
@@ -473,22 +473,60 @@ def test_batch_decode_row_counts_vs_lane_oracle(dec, orc, t):
         assert np.abs(single.cpu().numpy() - expect).max() <= TOL
 
 
-# The row-block form deals the scale groups of K to eight warps; shapes with fewer groups than warps (the K slices of
-# tensor-parallel shards: o_proj over 8 GPUs has K = 768) leave some warps without a group.
+# The row-block form deals the scale groups of K to its warps (16 in the variant for launches whose units are all
+# resident at once, 8 otherwise); shapes with fewer groups than warps (the K slices of tensor-parallel shards: o_proj
+# over 8 GPUs has K = 768) leave some warps without a group.
+@pytest.mark.parametrize("units16", [1, 0])
 @pytest.mark.parametrize("n,k", [(512, 768), (272, 128), (1040, 384), (4736, 1152)])
 @pytest.mark.parametrize("t", [1, 3, 4])
-def test_row_block_form_with_fewer_groups_than_warps(dec, orc, n, k, t):
+def test_row_block_form_with_fewer_groups_than_warps(dec, orc, n, k, t, units16):
     q, s = synth.make_linear(n, k, 128, seed=500 + k)
     dec.upload_lin_g("fewg", q, s, n, k, 128)
     xs = synth.make_acts(t, k, seed=510 + t)
-    y = dec.sk_single_dev("fewg", x_dev(xs), t=t)
+    dec.set_tuning("gemv_rowblock_units", units16)
+    try:
+        y = dec.sk_single_dev("fewg", x_dev(xs), t=t)
+        dec.sync()
+        assert dec.last_kernel().startswith("gemv_ru_kernel" if units16 else "gemv_rb_kernel")
+        expect = orc.linear_lane(q, s, xs, t, n, k, 128)
+        assert np.abs(y.cpu().numpy() - expect).max() <= TOL
+        y2 = dec.sk_single_dev("fewg", x_dev(xs), t=t)
+        dec.sync()
+        assert torch.equal(y, y2)
+    finally:
+        dec.set_tuning("gemv_rowblock_units", 1)
+
+
+# The 16-warp variant: each warp's first scale group waits in registers, its other groups and the scale words in
+# shared memory.  Group counts that do not divide by 16 (K = 5120: 40, K = 2176: 17), exactly 16, one more than 16, an odd
+# number of row blocks, every token count, the largest K that fits at two tokens, both output types, guard rows.
+@pytest.mark.parametrize("n,k,t", [(7168, 5120, 1), (7168, 5120, 4), (5120, 6144, 2), (1200, 2176, 3), (2064, 2048, 2),
+                                   (48, 2176, 1), (9472, 1024, 4), (3584, 4352, 2)])
+def test_row_block_16_warp_variant(dec, orc, n, k, t):
+    q, s = synth.make_linear(n, k, 128, seed=700 + n % 89)
+    dec.upload_lin_g("ru", q, s, n, k, 128)
+    xs = synth.make_acts(t, k, seed=710 + t)
+    guard = torch.full((t + 1, n), 7.0, device="cuda", dtype=torch.float32)
+    y = dec.sk_single_dev("ru", x_dev(xs), t=t, out=guard[:t])
     dec.sync()
-    assert dec.last_kernel().startswith("gemv_rb_kernel")
+    assert dec.last_kernel().startswith("gemv_ru_kernel")
     expect = orc.linear_lane(q, s, xs, t, n, k, 128)
     assert np.abs(y.cpu().numpy() - expect).max() <= TOL
-    y2 = dec.sk_single_dev("fewg", x_dev(xs), t=t)
+    assert bool((guard[t:] == 7.0).all())
+    y16 = dec.sk_single_dev("ru", x_dev(xs), t=t, out_f16=True)
     dec.sync()
-    assert torch.equal(y, y2)
+    assert torch.equal(y16, y.to(torch.float16))
+    # without the variant (the 8-warp kernel, or the K-split form beyond 11264 token-channels): the same sums up to
+    # the order in which the parts are added
+    dec.set_tuning("gemv_rowblock_units", 0)
+    try:
+        y8 = dec.sk_single_dev("ru", x_dev(xs), t=t)
+        dec.sync()
+        assert not dec.last_kernel().startswith("gemv_ru_kernel")
+    finally:
+        dec.set_tuning("gemv_rowblock_units", 1)
+    assert float((y8 - y).abs().max()) <= TOL
+    dec.drop_lin("ru")
 
 
 # More units than resident CTAs (a CTA walks two units, its register ring runs on across the boundary), an odd number
@@ -501,7 +539,7 @@ def test_row_block_form_units_and_edges(dec, orc, n, k, t):
     guard = torch.full((t + 1, n), 7.0, device="cuda", dtype=torch.float32)
     y = dec.sk_single_dev("rbu", x_dev(xs), t=t, out=guard[:t])
     dec.sync()
-    assert dec.last_kernel().startswith("gemv_rb_kernel")
+    assert dec.last_kernel().startswith("gemv_rb_kernel" if n > 9472 else "gemv_ru_kernel")
     expect = orc.linear_lane(q, s, xs, t, n, k, 128)
     assert np.abs(y.cpu().numpy() - expect).max() <= TOL
     assert bool((guard[t:] == 7.0).all())
