@@ -85,7 +85,7 @@ W4A16_API const char* w4a16_last_kernel(w4a16_dec* dec);
  * above that; 2 = always persistent; 0 = never), "tp_wait_log2" (16..40, default 31: the fused all-reduce gives up
  * on its peers after 2^n cycles), "gemv_sk_stages" (2..6) and "gemv_sk_prefetch" (0..6): ring
  * stages of the persistent form and how many of them are requested before the previous kernel of the stream is
- * complete; "gemv_rowblock" (1 = default: up to four tokens of a 128-channel-group linear of at most 48 MB and K <= 6144, with tokens x K <= 11264, run on CTAs that own whole rows, without scratch or tickets, and more tokens of such a linear on the (row block, K split) form; 2 = whatever the size; 0 = never); the remaining gemv_* keys tune the (row block, K split) form: "gemv_ksplit" (0 = automatic),
+ * complete; "gemv_rowblock" (1 = default: up to four tokens of a 128-channel-group linear of at most 48 MB and K <= 6144 run on CTAs that own whole rows, without scratch or tickets -- a 16-warp kernel when all 32-row units are resident at once and x fits beside the weights in shared memory, else an 8-warp kernel up to tokens x K <= 11264 and the (row block, K split) form beyond; 2 = whatever the size; 0 = never), "gemv_rowblock_units" (1 = default; 0 = never the 16-warp kernel); the remaining gemv_* keys tune the (row block, K split) form: "gemv_ksplit" (0 = automatic),
  * "gemv_stages" (16 KB weight stages in flight per CTA, 2..8), "gemv_warps" (consumer warps per CTA, 8 or 16), "gemv_cluster" (1 = default: 2..8 K splits of a row
  * block run as a thread-block cluster and reduce through distributed shared memory),
  * "gemv_subnormal" (1 = default arithmetic, 0 = exact nibble-8 operands), "gemm_mt" (128-token blocks per prefill GEMM tile: 0 = automatic, 1, 2), "gemm_ksplit" (K splits of the GEMM tiles: 0 = automatic -- all tiles when they are few, the tiles of an incomplete last wave otherwise; -1 = never; 1..16 = every tile), "gemm_tma_store" (1 = default: whole dense tiles leave through shared memory and TMA stores; 0 = per-lane stores), "debug_timeline" (0/1, see w4a16_debug_timeline), "pdl" (1 = default: kernels are

@@ -210,6 +210,8 @@ int Dec::gemv_select(GemvArgs& a, bool allreduce, bool own_scratch, GemvChoice& 
     // 4 tokens, o_proj 8.9 / 9.8 / 11.1) where the (row block, K split) cluster form stays flat (9.2 / 9.3 / 9.4 and
     // 9.1 / 9.3 / 9.5): beyond 11264 token-channels the latter takes over (not for the fused all-reduce, which would lose
     // the cluster reduce; the entry point with its own scratch follows the same rule so that it returns the same bits).
+    // The 16-warp variant of the row-block form (all units resident at once, x beside the weights in shared memory) has no
+    // such slope -- qkv 6.4 / 6.8 / 8.2 us at 1 / 2 / 4 tokens -- and keeps every call it can take.
     const size_t w_bytes = (size_t)a.seg[0].n * a.k / 2;
     const bool rb_shape = w_bytes <= ((size_t)48 << 20) && a.k <= 6144;
     const bool rb_tokens = allreduce || !tune_gemv_cluster || (size_t)t * a.k <= 11264 || gemv_ru_fits(a, sm_count);

@@ -1,4 +1,6 @@
-// Decode GEMV, "row block" form: a CTA owns ALL of K for 32 rows at a time, its eight warps split K.
+// Decode GEMV, "row block" form: a CTA owns ALL of K for 32 rows at a time, its warps split K.  Two kernels: the 8-warp
+// one described first, which walks any number of units, and a 16-warp variant for launches whose units are all resident
+// at once (further down).
 //
 // Same product and arithmetic as the other decode forms (crates/backend-gpu/src/rawcuda/assets/decode.cu:46-267 is
 // what they replace): mma.sync m16n8k16 with the weight tile as the 16-row operand, the raw nibbles as exact f16
@@ -669,6 +671,7 @@ cudaError_t gemv_rb_init_device() {
     if (e == cudaSuccess) {
         e = cudaFuncSetAttribute(gemv_ru_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
     }
+
     return e;
 }
 
@@ -718,7 +721,6 @@ int gemv_rb_plan(GemvArgs& a, int sm_count, int& rbw) {
 
 // Which kernel a row-block launch runs (also what the library reports as the last kernel's name).
 const char* gemv_rb_variant(const GemvArgs& a, int total_units, int rbw, int sm_count) {
-    (void)total_units;
     if (rbw == 2 && gemv_ru_fits(a, sm_count)) {
         return "gemv_ru_kernel";
     }
@@ -738,13 +740,15 @@ cudaError_t launch_gemv_rb(const GemvArgs& a_in, int total_units, int rbw, int s
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    if (gemv_rb_variant(a, total_units, rbw, sm_count)[6] == 'u') {
+    const char variant = gemv_rb_variant(a, total_units, rbw, sm_count)[6];
+    if (variant == 'u') {
         cfg.gridDim = dim3(total_units);
         cfg.blockDim = dim3(RU_THREADS);
         cfg.dynamicSmemBytes = gemv_ru_smem(a, &a.rb_stash, &a.rb_stash2);
         return a.tp.world > 1 ? cudaLaunchKernelEx(&cfg, gemv_ru_kernel<true>, a, total_units)
                               : cudaLaunchKernelEx(&cfg, gemv_ru_kernel<false>, a, total_units);
     }
+
     cfg.gridDim = dim3(std::min(total_units, (rbw == 2 ? 2 : 3) * sm_count));
     cfg.blockDim = dim3(RB_THREADS);
     cfg.dynamicSmemBytes = gemv_rb_smem(a);
